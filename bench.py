@@ -1,0 +1,387 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized matrix-product hot path on B200.
+
+Workload (``config.workload``): the Qwen2.5-7B-shaped Q4_K_M decode matvec set at batch 1 -- per layer q/o
+3584x3584, k 512x3584 (Q4_K), v 512x3584 (Q6_K), gate/up 18944x3584 (Q4_K), down 3584x18944 (Q6_K), 28 layers,
+plus the 152064x3584 Q4_K LM head: 4,480,401,408 bytes of GGUF blocks per step. A step is one pass over every
+matrix with seeded N(0,1) FP32 activations, quantised on the device exactly as the reference's activation
+quantiser does. The metric is weight GB/s (source GGUF block bytes / time). Weights exceed L2 (126 MB) by 35x,
+so no flush is needed between iterations.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+With N > 1 (launched under torchrun) every matrix is sharded by output rows across the ranks and the output
+slices are all-gathered over NCCL; the same total work is split, so scaling is "strong".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from synapse_b200 import synth  # noqa: E402
+
+METRIC = "k-quant decode matvec weight bandwidth (Qwen2.5-7B Q4_K_M set, batch 1)"
+UNIT = "GB/s"
+WORKLOAD = "qwen2.5-7b q4_k_m decode matvec set, batch 1 (config 2)"
+
+
+def parse_args():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--layers", type=int, default=28, help="layers of the model shape (28 = the full config)")
+    parser.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
+    parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--no-cpu", action="store_true")
+    return parser.parse_args()
+
+
+def model_matrices(layers):
+    """(name, type, rows, columns) of every matrix of one step, in execution order."""
+    out = []
+    per_layer = [m for m in synth.QWEN25_7B_Q4KM if m[0] != "lm_head"]
+    for layer in range(layers):
+        for name, ggml_type, rows, columns, _ in per_layer:
+            out.append((f"blk.{layer}.{name}", ggml_type, rows, columns))
+    name, ggml_type, rows, columns, _ = [m for m in synth.QWEN25_7B_Q4KM if m[0] == "lm_head"][0]
+    out.append((name, ggml_type, rows, columns))
+    return out
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.device_index = device_index
+        self.lines = []
+        self.process = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                                             "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.process = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, start_time, end_time):
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        rows = [line.split(", ") for stamp, line in self.lines if start_time - 0.05 <= stamp <= end_time + 0.15]
+        if not rows:
+            rows = [line.split(", ") for _, line in self.lines[-3:]]
+        clocks, max_clocks, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in rows:
+            if len(row) < 9:
+                continue
+            try:
+                clocks.append(float(row[1]))
+                max_clocks.append(float(row[2]))
+                power.append(float(row[3]))
+            except ValueError:
+                continue
+            for name, value in zip(names, row[5:9]):
+                if value.strip().lower() == "active":
+                    reasons.add(name)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(clocks)), "sm_max_mhz": float(max(max_clocks)), "power_w_max": float(max(power)),
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def measured_peak_hbm():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as handle:
+            return float(json.load(handle)["hbm_gbs"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------------------
+# CPU arm: the reference's own CPU path (restated in oracle/), timed on this host's cores
+# ------------------------------------------------------------------------------------------------------------
+
+def cpu_reference_pass(oracle, sample, xs, threads):
+    """One pass of the reference backend's K-quant product (decode the row, FP32 dot) over the sample."""
+    for (name, ggml_type, rows, columns), weights in sample:
+        oracle.f32_matmul_threads(ggml_type, weights, rows, columns, xs[columns], threads)
+
+
+def cpu_sample(layers=1):
+    """One transformer layer of the workload (149 MB of blocks): a bounded sample of the same matrices."""
+    sample = []
+    for name, ggml_type, rows, columns in model_matrices(layers)[:-1]:
+        sample.append(((name, ggml_type, rows, columns), synth.matrix(ggml_type, rows, columns, seed=1, name=name)))
+    xs = {3584: synth.activations(1, 3584, seed=2), 18944: synth.activations(1, 18944, seed=2)}
+    sample_bytes = sum(rows * synth.row_bytes(t, cols) for (_, t, rows, cols), _ in sample)
+    return sample, xs, sample_bytes
+
+
+def run_cpu_baseline(budget_seconds=12.0):
+    import oracle
+
+    oracle.build()
+    threads = os.cpu_count() or 1
+    sample, xs, sample_bytes = cpu_sample(1)
+    cpu_reference_pass(oracle, sample, xs, threads)  # warm-up
+    passes, start = 0, time.perf_counter()
+    while True:
+        cpu_reference_pass(oracle, sample, xs, threads)
+        passes += 1
+        elapsed = time.perf_counter() - start
+        if elapsed >= budget_seconds or passes >= 200:
+            break
+    return {"value": sample_bytes * passes / elapsed / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{passes} passes over one layer of the workload ({sample_bytes} bytes of Q4_K/Q6_K blocks): decode row + FP32 dot "
+                      f"(the reference backend's K-quant path), rows chunked over {threads} threads"}
+
+
+def run_reference_arm(args):
+    """`--impl reference`: the reference's CPU implementation of the path on the host cores, on a bounded sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+
+    oracle.build()
+    threads = os.cpu_count() or 1
+    sample, xs, sample_bytes = cpu_sample(1)
+    for _ in range(max(args.warmup, 1)):
+        cpu_reference_pass(oracle, sample, xs, threads)
+    start = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_reference_pass(oracle, sample, xs, threads)
+    elapsed = time.perf_counter() - start
+    value = sample_bytes * args.steps / elapsed / 1e9
+    sample_text = (f"each step = one layer of the workload ({sample_bytes} bytes of Q4_K/Q6_K blocks), decode row + FP32 dot "
+                   f"(reference backend K-quant path), {threads} threads")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "sample": sample_text},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample_text},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------------------
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import synapse_b200 as sb
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib = sb.library()
+    lib.probe()
+
+    # ---- weights: every rank holds rows [rank*R/world, (rank+1)*R/world) of every matrix -------------------
+    specs = model_matrices(args.layers)
+    matrices = []
+    total_bytes = 0
+    for index, (name, ggml_type, rows, columns) in enumerate(specs):
+        if rows % world:
+            raise SystemExit(f"{name}: {rows} rows do not split over {world} ranks")
+        shard_rows = rows // world
+        row_bytes = synth.row_bytes(ggml_type, columns)
+        blocks = synth.matrix(ggml_type, rows, columns, seed=100 + index, name=name)
+        shard = blocks[rank * shard_rows * row_bytes:(rank + 1) * shard_rows * row_bytes]
+        matrices.append((name, ggml_type, rows, columns, shard_rows, sb.QuantizedMatrix(shard, ggml_type, shard_rows, columns)))
+        total_bytes += rows * row_bytes
+        del blocks, shard
+
+    # ---- activations (resident) and outputs -----------------------------------------------------------------
+    x_host = {3584: synth.activations(1, 3584, seed=5), 18944: synth.activations(1, 18944, seed=6)}
+    x_dev = {k: torch.from_numpy(v).to(device) for k, v in x_host.items()}
+    scratch = {k: torch.empty(lib.activation_scratch_bytes(1, k) + 256, dtype=torch.uint8, device=device) for k in x_host}
+    out_full = {rows: torch.zeros(rows, dtype=torch.float32, device=device) for rows in {m[2] for m in matrices}}
+    out_shard = {m[4]: torch.zeros(m[4], dtype=torch.float32, device=device) for m in matrices}
+
+    def aligned(tensor):
+        return (tensor.data_ptr() + 255) // 256 * 256
+
+    def step(stream_ptr):
+        """One pass: activations quantised once per distinct input of a layer (as the reference's executor does,
+        Qwen2CpuExecutor.cs:165-185), then every projection on the shared quantised activations."""
+        for name, ggml_type, rows, columns, shard_rows, matrix in matrices:
+            leaf = name.split(".")[-1]
+            if leaf in ("attn_q", "attn_o", "ffn_gate", "ffn_down", "lm_head"):
+                sb.quantize_device(x_dev[columns].data_ptr(), 1, columns, columns, aligned(scratch[columns]),
+                                   lib.activation_scratch_bytes(1, columns), stream_ptr)
+            target = out_shard[shard_rows] if world > 1 else out_full[rows]
+            matrix.matmul_q8_device(aligned(scratch[columns]), 1, target.data_ptr(), shard_rows, stream=stream_ptr)
+            if world > 1:
+                dist.all_gather_into_tensor(out_full[rows], target)
+
+    stream = torch.cuda.Stream(device)
+    graph = None
+    lib.launch_count(reset=True)
+    with torch.cuda.stream(stream):
+        step(stream.cuda_stream)
+    stream.synchronize()
+    launches_per_step = lib.launch_count(reset=True)
+    use_graph = not args.no_graph and world == 1
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step(torch.cuda.current_stream().cuda_stream)
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            step(stream.cuda_stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            run_step()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        time.sleep(0.25)
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        wall_start = time.time()
+        begin.record(stream)
+        for _ in range(args.steps):
+            run_step()
+        end.record(stream)
+        barrier()
+        wall_end = time.time()
+    elapsed_ms = begin.elapsed_time(end)
+    if world > 1:
+        slowest = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
+        dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(slowest.item())
+    clocks = sampler.stop(wall_start, wall_end)
+    ms_per_step = elapsed_ms / args.steps
+    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel: the Q4_K matvec on the gate/up matrices (38 MB each) -------------
+    big = [m for m in matrices if m[0].endswith("ffn_gate") or m[0].endswith("ffn_up")]
+    per_launch_bytes = big[0][4] * synth.row_bytes(big[0][1], big[0][3])
+    durations = []
+    with torch.cuda.stream(stream):
+        for repeat in range(3):
+            for name, ggml_type, rows, columns, shard_rows, matrix in big:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                matrix.matmul_q8_device(aligned(scratch[columns]), 1, out_shard[shard_rows].data_ptr() if world > 1 else out_full[rows].data_ptr(),
+                                        shard_rows, stream=stream.cuda_stream)
+                e1.record(stream)
+                if repeat > 0:
+                    durations.append((e0, e1))
+        stream.synchronize()
+    kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in durations]))
+    peak, peak_kind = measured_peak_hbm()
+    achieved = per_launch_bytes / (kernel_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "matvec_xq8_kernel<Q4_K, T=1> on ffn_gate/ffn_up (18944x3584)", "achieved": achieved,
+                "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                "bytes_per_launch": per_launch_bytes, "us_per_launch": kernel_ms * 1e3, "launches_timed": len(durations)}
+
+    # ---- end to end through the host-pointer C ABI: pinned host x in, host y out, per matrix ----------------
+    e2e = None
+    if not args.no_e2e:
+        host_x = {k: torch.from_numpy(v).pin_memory() for k, v in x_host.items()}
+        host_y = {m[4]: torch.zeros(m[4], dtype=torch.float32).pin_memory() for m in matrices}
+        h2d = sum(4 * m[3] for m in matrices)
+        d2h = sum(4 * m[4] for m in matrices)
+
+        def e2e_step():
+            for name, ggml_type, rows, columns, shard_rows, matrix in matrices:
+                lib.check(lib.raw.syn_b200_matvec(matrix.handle, 0, shard_rows, host_x[columns].data_ptr(), 1, columns,
+                                                  host_y[shard_rows].data_ptr(), shard_rows, sb.MODE_XQ8, sb.EPILOGUE_STORE))
+
+        e2e_steps = max(3, min(args.steps, 10))
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        start = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        barrier()
+        e2e_seconds = time.perf_counter() - start
+        if world > 1:
+            slowest = torch.tensor([e2e_seconds], dtype=torch.float64, device=device)
+            dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+            e2e_seconds = float(slowest.item())
+        e2e = {"value": total_bytes * e2e_steps / e2e_seconds / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": e2e_seconds / e2e_steps * 1e3, "steps": e2e_steps,
+               "api": "syn_b200_matvec (host FP32 activations in, host FP32 outputs out, one call per matrix)"}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = run_cpu_baseline()
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "i8 dot / f32 accumulate",
+                "data": "synthetic",
+                "config": {"workload": WORKLOAD, "layers": args.layers, "matrices": len(matrices), "bytes_per_step": total_bytes,
+                           "activation_contract": "xq8 (Q8_0 activation quantiser reproduced on device)",
+                           "layout": "Q4_K file layout; Q6_K repacked to planes at load", "cuda_graph": bool(graph is not None),
+                           "l2": "weights per step exceed L2 35x, no flush", "parallelism": f"row-shard x{world}" if world > 1 else "single gpu",
+                           "tokens_per_s": 1e3 / ms_per_step},
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+                "gpu_launches": int(launches_per_step * args.steps)}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,188 @@
+/*
+ * synapse_b200 — C ABI of the B200 (sm_100a) CUDA backend for Synapse's quantized matrix products.
+ *
+ * The library stands beside the reference's two native libraries and keeps their conventions
+ * (native/synapse-kernels/src/Features/CpuKernels/ffi.rs, native/synapse-gpu/src/Features/GpuKernels/ffi.rs):
+ *   - every entry point returns an int32 status (0 = OK) and never throws or aborts across the ABI;
+ *   - the caller owns every buffer for the duration of the call, the callee never frees caller memory;
+ *   - a thread-local message describing the last failure is read with syn_b200_last_error;
+ *   - the loader checks syn_b200_abi_version before any other call;
+ *   - a matrix handle must not be used by two threads at once (the reference serialises model calls,
+ *     src/Synapse.Runtime/Features/TextGeneration/Qwen2/Qwen2Model.cs:164);
+ *   - nothing falls back to a CPU path: without a usable sm_100 device calls fail with SYN_B200_UNAVAILABLE.
+ *
+ * Weight blocks are plain GGUF, row-major [rows][columns], accepted unmodified:
+ *   Q8_0 (type 8): 34 B / 32 values; Q4_K (type 12): 144 B / 256 values; Q6_K (type 14): 210 B / 256 values
+ *   (native/synapse-gpu/src/Features/GpuKernels/decoder/encoding.rs:6-10,41-56).
+ */
+#ifndef SYNAPSE_B200_H
+#define SYNAPSE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define SYN_B200_API __attribute__((visibility("default")))
+#else
+#define SYN_B200_API
+#endif
+
+#define SYN_B200_ABI_VERSION 1u
+
+/* Status codes: the reference GPU ABI's (native/synapse-gpu/src/Features/GpuKernels/error.rs:3-16).
+ * The C# side maps 3 to NotSupportedException, 5 to InsufficientMemoryException, the rest to
+ * InvalidOperationException (src/Synapse.Runtime/Features/GpuKernels/NativeGpuLibrary.cs:130-145). */
+#define SYN_B200_OK 0
+#define SYN_B200_NULL_POINTER 1
+#define SYN_B200_INVALID_ARGUMENT 2
+#define SYN_B200_UNAVAILABLE 3
+#define SYN_B200_DEVICE_ERROR 4
+#define SYN_B200_OUT_OF_MEMORY 5
+#define SYN_B200_INTERNAL 6 /* a C++ exception was caught at the ABI (the reference's STATUS_PANIC) */
+
+/* GGML tensor type ids of the accepted encodings. */
+#define SYN_B200_TYPE_Q8_0 8u
+#define SYN_B200_TYPE_Q4_K 12u
+#define SYN_B200_TYPE_Q6_K 14u
+
+/* syn_b200_matrix_create flags. */
+#define SYN_B200_REPACK 1u /* load-time repack into the coalesced planar layout (same byte count) */
+
+/* Activation contract of a product (the reference has three numeric contracts,
+ * docs/ADR/ADR-006-cpu-kernel-backends-and-native-boundary.md:20-24). */
+#define SYN_B200_MODE_XQ8 0u /* activations Q8_0-quantised per 32 exactly as Q8ActivationQuantizer does; integer block dots */
+#define SYN_B200_MODE_XF32 1u /* FP32 activations x exactly dequantised weights (the `reference` backend's contract) */
+
+/* Epilogue of a product (the fused regions of Qwen2ProjectionWork.cs:7-88 and `accumulate` of
+ * native/synapse-gpu/.../cuda/kernels/common.cuh:52-69). */
+#define SYN_B200_EPILOGUE_STORE 0u      /* y = W x */
+#define SYN_B200_EPILOGUE_ACCUMULATE 1u /* y += W x (residual add) */
+
+/* Operand precision of the tensor-core product. */
+#define SYN_B200_GEMM_F16 0u  /* weights and activations rounded to fp16, FP32 accumulation */
+#define SYN_B200_GEMM_BF16 1u /* weights and activations rounded to bf16, FP32 accumulation */
+
+/* Mirrors GpuDeviceInfo (native/synapse-gpu/src/Features/GpuKernels/mod.rs:20-31), 152 bytes. */
+typedef struct syn_b200_device_info {
+    char name[128];                /* NUL-terminated, e.g. "NVIDIA B200 (sm_100)" */
+    uint64_t total_memory_bytes;   /* device memory */
+    uint64_t max_buffer_bytes;     /* largest single allocation the library will try */
+    uint32_t compute_capability;   /* major * 10 + minor */
+    uint32_t multiprocessors;
+} syn_b200_device_info;
+
+typedef struct syn_b200_matrix syn_b200_matrix;
+
+/* Replaces synapse_kernels_abi_version / synapse_gpu_abi_version (ffi.rs:22 / ffi.rs:55-59). */
+SYN_B200_API uint32_t syn_b200_abi_version(void);
+
+/* Replaces synapse_gpu_probe (native/synapse-gpu/.../ffi.rs:61-77): describes the current CUDA device.
+ * SYN_B200_UNAVAILABLE when there is no device or it is not compute capability 10.x. */
+SYN_B200_API int32_t syn_b200_probe(syn_b200_device_info *out);
+
+/* Replaces synapse_gpu_last_error (ffi.rs:89-104): copies the calling thread's last error message (UTF-8,
+ * not terminated) and returns its full length. `buffer` may be null. */
+SYN_B200_API size_t syn_b200_last_error(uint8_t *buffer, size_t capacity);
+
+/* Loads a row-major matrix of GGUF blocks from HOST memory onto the current device. Replaces the weight
+ * upload of the reference CUDA backend (native/synapse-gpu/.../cuda/decoder.rs:59-60) and the view type
+ * Q8Matrix (src/Synapse.Runtime/Features/CpuKernels/Q8Matrix.cs:6-55). The host bytes are not referenced
+ * after the call. `columns` must be a whole number of blocks (decoder/checks.rs:185-190 -> UNAVAILABLE). */
+SYN_B200_API int32_t syn_b200_matrix_create(const void *host_blocks, uint32_t ggml_type, uint64_t rows, uint64_t columns,
+                               uint32_t flags, syn_b200_matrix **out);
+
+/* Same, from blocks that already sit in DEVICE memory (copied device-to-device on `stream`, then repacked). */
+SYN_B200_API int32_t syn_b200_matrix_create_from_device(const void *device_blocks, uint32_t ggml_type, uint64_t rows,
+                                           uint64_t columns, uint32_t flags, void *stream, syn_b200_matrix **out);
+
+/* Releases a matrix; null is ignored (ffi.rs:262-271). */
+SYN_B200_API void syn_b200_matrix_destroy(syn_b200_matrix *matrix);
+
+/* Shape query: any out pointer may be null. `source_bytes` = rows * row bytes of the GGUF encoding. */
+SYN_B200_API int32_t syn_b200_matrix_info(const syn_b200_matrix *matrix, uint32_t *ggml_type, uint64_t *rows,
+                             uint64_t *columns, uint32_t *flags, uint64_t *source_bytes);
+
+/* Q8_0 activation quantiser, HOST buffers. Replaces Q8ActivationQuantizer.QuantizeRow
+ * (src/Synapse.Runtime/Features/CpuKernels/Q8ActivationQuantizer.cs:15-57): per 32 values
+ * scale = max|x|/127, code = round_half_even(x * (1/scale)) with the unrounded scale, stored scale rounded
+ * through fp16. x: tokens rows of in_stride floats; codes: tokens*columns; scales: tokens*columns/32. */
+SYN_B200_API int32_t syn_b200_quantize_q8(const float *x, uint64_t tokens, uint64_t columns, uint64_t in_stride,
+                             int8_t *codes, float *scales);
+
+/* Q8_0-quantised activations x matrix rows, HOST buffers. Replaces synapse_q8_0_matmul
+ * (native/synapse-kernels/src/Features/CpuKernels/ffi.rs:44-54) and Q8MatrixKernel.Multiply
+ * (src/Synapse.Runtime/Features/CpuKernels/Q8MatrixKernel.cs:11-48):
+ *   output[t * output_stride + (r - row_start)] = dot(W[r], A[t]),  r in [row_start, row_start + row_count).
+ * codes: tokens*columns int8; scales: tokens*columns/32 floats; output holds (tokens-1)*stride + row_count
+ * floats and must not alias the inputs. Works for Q8_0, Q4_K and Q6_K matrices. */
+SYN_B200_API int32_t syn_b200_matmul_q8(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
+                           const int8_t *codes, const float *scales, uint64_t tokens, float *output,
+                           uint64_t output_stride);
+
+/* FP32 activations x matrix rows, HOST buffers; quantises in-library when mode is XQ8. Replaces one
+ * projection of the reference GPU step (native/synapse-gpu/.../step/projection.rs:51-72; kernels
+ * cuda/kernels/matmul.cu:79-189) and, in XF32 mode, Q8Operators.Multiply / DecodedRowOperators.Multiply
+ * (src/Synapse.Runtime/Features/GraphExecution/Q8Operators.cs:46-98, DecodedRowOperators.cs:20-41).
+ * Token counts above the matrix-vector limit run on the tensor-core GEMM when mode is XF32. */
+SYN_B200_API int32_t syn_b200_matvec(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count, const float *x,
+                        uint64_t tokens, uint64_t in_stride, float *y, uint64_t out_stride, uint32_t mode,
+                        uint32_t epilogue);
+
+/* Prompt-run product on the tensor cores, HOST buffers: Y[t * out_stride + r] = sum_k W[r][k] X[t][k].
+ * Replaces synapse_q8_gemm (cuda/kernels/matmul.cu:147-189) and the Metal K-quant GEMMs
+ * (metal/shaders/matmul_kquant.metal:227-291). */
+SYN_B200_API int32_t syn_b200_gemm(const syn_b200_matrix *matrix, const float *x, uint64_t tokens, uint64_t in_stride,
+                      float *y, uint64_t out_stride, uint32_t precision);
+
+/* Test hook: the exact integer sub-block dots of the XQ8 contract, HOST buffers.
+ * out[(t*row_count + r) * groups + g]; groups per row = columns/32 (Q8_0), columns/32 (Q4_K, one per
+ * sub-block), columns/16 (Q6_K). The sums are produced by the same device code as syn_b200_matmul_q8. */
+SYN_B200_API int32_t syn_b200_block_dots(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
+                            const int8_t *codes, uint64_t tokens, int32_t *out);
+
+/* ---- Device-resident variants: every pointer is DEVICE memory on the matrix's device; work is queued on
+ * `stream` (a cudaStream_t, null = default stream) and not synchronised. These are what a resident decode
+ * loop calls; they replace the launches of step/projection.rs without the per-step host copies of
+ * cuda/decoder.rs:106-145. ---- */
+
+/* Bytes of device scratch syn_b200_matvec_dev needs in XQ8 mode for `tokens` x `columns` activations
+ * (codes, block scales and 16-value code sums). */
+SYN_B200_API uint64_t syn_b200_activation_scratch_bytes(uint64_t tokens, uint64_t columns);
+
+/* Quantises FP32 device activations into a scratch area laid out by the library. */
+SYN_B200_API int32_t syn_b200_quantize_q8_dev(const float *x, uint64_t tokens, uint64_t columns, uint64_t in_stride,
+                                 void *scratch, uint64_t scratch_bytes, void *stream);
+
+/* y (+)= W[row_start : row_start+row_count] * act, activations taken from a scratch area filled by
+ * syn_b200_quantize_q8_dev with the same tokens/columns. */
+SYN_B200_API int32_t syn_b200_matmul_q8_dev(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
+                               const void *scratch, uint64_t tokens, float *y, uint64_t out_stride,
+                               uint32_t epilogue, void *stream);
+
+/* FP32 device activations x matrix rows. XQ8 mode quantises into `scratch` first (required, at least
+ * syn_b200_activation_scratch_bytes); XF32 mode ignores scratch. */
+SYN_B200_API int32_t syn_b200_matvec_dev(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
+                            const float *x, uint64_t tokens, uint64_t in_stride, float *y, uint64_t out_stride,
+                            uint32_t mode, uint32_t epilogue, void *scratch, uint64_t scratch_bytes,
+                            void *stream);
+
+/* Bytes of device scratch syn_b200_gemm_dev needs for `tokens` x `columns` activations (16-bit operands). */
+SYN_B200_API uint64_t syn_b200_gemm_scratch_bytes(uint64_t tokens, uint64_t columns);
+
+/* Tensor-core product with device buffers. */
+SYN_B200_API int32_t syn_b200_gemm_dev(const syn_b200_matrix *matrix, const float *x, uint64_t tokens, uint64_t in_stride,
+                          float *y, uint64_t out_stride, uint32_t precision, void *scratch,
+                          uint64_t scratch_bytes, void *stream);
+
+/* Number of kernel launches the library has queued from the calling thread since the last reset
+ * (benchmark bookkeeping). Passing a non-zero `reset` clears the counter after reading it. */
+SYN_B200_API uint64_t syn_b200_launch_count(uint32_t reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SYNAPSE_B200_H */

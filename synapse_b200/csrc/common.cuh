@@ -1,0 +1,127 @@
+// Internal declarations shared by the translation units of libsynapse_b200.so (sm_100a only).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <string>
+
+#include "../../include/synapse_b200.h"
+
+namespace syn {
+
+constexpr uint32_t kQ8_0 = SYN_B200_TYPE_Q8_0;
+constexpr uint32_t kQ4_K = SYN_B200_TYPE_Q4_K;
+constexpr uint32_t kQ6_K = SYN_B200_TYPE_Q6_K;
+
+constexpr int kMaxMatvecTokens = 8;  // tokens one matrix-vector launch group handles (cuda/kernels/matmul.cu:112-115)
+
+inline uint64_t block_values(uint32_t type) { return type == kQ8_0 ? 32 : (type == kQ4_K || type == kQ6_K) ? 256 : 0; }
+inline uint64_t block_bytes(uint32_t type) { return type == kQ8_0 ? 34 : type == kQ4_K ? 144 : type == kQ6_K ? 210 : 0; }
+inline uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+// Device-resident weights. `layout` says how `data` is organised.
+enum class Layout : uint32_t {
+    Natural = 0,  // GGUF blocks exactly as in the file, rows contiguous
+    Planar = 1,   // per-field planes, each plane row-major and 16-byte friendly (see repack.cu)
+};
+
+struct PlaneOffsets {
+    // Byte offsets of the planes inside `data` (Planar only).
+    // Q8_0: codes int8 [rows][K], scales half [rows][K/32].
+    // Q6_K: ql [rows][K/2], qh [rows][K/4], scales int8 [rows][K/16], d half [rows][K/256].
+    uint64_t p0 = 0, p1 = 0, p2 = 0, p3 = 0;
+};
+
+}  // namespace syn
+
+struct syn_b200_matrix {
+    uint32_t type = 0;
+    uint32_t flags = 0;
+    uint64_t rows = 0, columns = 0;
+    uint64_t row_bytes = 0;  // of the GGUF encoding
+    int device = 0;
+    syn::Layout layout = syn::Layout::Natural;
+    syn::PlaneOffsets planes;
+    uint8_t *data = nullptr;  // device
+    uint64_t data_bytes = 0;
+    // Staging for the host-pointer entry points, grown on demand, owned by the handle.
+    void *stage = nullptr;
+    uint64_t stage_bytes = 0;
+};
+
+namespace syn {
+
+// Quantised activations in device scratch: codes int8 [T][K], scales float [T][K/32], sums int16 [T][K/16].
+struct ActLayout {
+    uint64_t codes = 0, scales = 0, sums = 0, total = 0;
+};
+inline ActLayout act_layout(uint64_t tokens, uint64_t columns)
+{
+    ActLayout l;
+    l.codes = 0;
+    l.scales = align_up(tokens * columns, 256);
+    l.sums = align_up(l.scales + tokens * (columns / 32) * 4, 256);
+    l.total = align_up(l.sums + tokens * (columns / 16) * 2, 256);
+    return l;
+}
+
+struct ActView {
+    const int8_t *codes;
+    const float *scales;
+    const int16_t *sums;
+};
+inline ActView act_view(const void *scratch, uint64_t tokens, uint64_t columns)
+{
+    ActLayout l = act_layout(tokens, columns);
+    const uint8_t *base = static_cast<const uint8_t *>(scratch);
+    return ActView{reinterpret_cast<const int8_t *>(base + l.codes), reinterpret_cast<const float *>(base + l.scales),
+                   reinterpret_cast<const int16_t *>(base + l.sums)};
+}
+
+struct Error {
+    int32_t status;
+    std::string message;
+};
+
+// Records the message for syn_b200_last_error and returns the status.
+int32_t fail(int32_t status, const std::string &message);
+int32_t cuda_fail(cudaError_t error, const char *what);
+void count_launch();
+int sm_count(int device);
+
+// quantize.cu
+cudaError_t launch_quantize(const float *x, uint64_t tokens, uint64_t columns, uint64_t in_stride, int8_t *codes,
+                            float *scales, int16_t *sums, cudaStream_t stream);
+cudaError_t launch_group_sums(const int8_t *codes, uint64_t count16, int16_t *sums, cudaStream_t stream);
+
+// repack.cu
+uint64_t planar_bytes(uint32_t type, uint64_t rows, uint64_t columns, PlaneOffsets *planes);
+cudaError_t launch_repack(uint32_t type, const uint8_t *natural, uint64_t rows, uint64_t columns, uint8_t *planar,
+                          const PlaneOffsets &planes, cudaStream_t stream);
+
+// matvec.cu
+struct MatvecArgs {
+    const syn_b200_matrix *matrix;
+    uint64_t row_start, row_count;
+    uint64_t tokens;
+    // XQ8: quantised activations; XF32: x with in_stride
+    ActView act;
+    const float *x;
+    uint64_t in_stride;
+    float *y;
+    uint64_t out_stride;
+    uint32_t mode;
+    uint32_t epilogue;
+    int32_t *dump;  // test hook: integer sub-block dots, or null
+};
+cudaError_t launch_matvec(const MatvecArgs &args, cudaStream_t stream);
+
+// gemm_tc.cu
+uint64_t gemm_scratch_bytes(uint64_t tokens, uint64_t columns);
+int32_t launch_gemm(const syn_b200_matrix *matrix, const float *x, uint64_t tokens, uint64_t in_stride, float *y,
+                    uint64_t out_stride, uint32_t precision, void *scratch, uint64_t scratch_bytes, cudaStream_t stream);
+
+}  // namespace syn
