@@ -44,6 +44,10 @@ def parse_args():
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--layers", type=int, default=28, help="layers of the model shape (28 = the full config)")
     parser.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
+    parser.add_argument("--quantize", default="shared", choices=["shared", "fused"],
+                        help="shared: one quantiser launch per distinct layer input, reused by the projections that read it; "
+                             "fused: every product quantises its FP32 input inside the kernel")
+    parser.add_argument("--serial", action="store_true", help="run q/k/v and gate/up one after the other instead of on parallel graph branches")
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--no-cpu", action="store_true")
     return parser.parse_args()
@@ -244,43 +248,85 @@ def main():
     x_host = {3584: synth.activations(1, 3584, seed=5), 18944: synth.activations(1, 18944, seed=6)}
     x_dev = {k: torch.from_numpy(v).to(device) for k, v in x_host.items()}
     scratch = {k: torch.empty(lib.activation_scratch_bytes(1, k) + 256, dtype=torch.uint8, device=device) for k in x_host}
-    out_full = {rows: torch.zeros(rows, dtype=torch.float32, device=device) for rows in {m[2] for m in matrices}}
-    out_shard = {m[4]: torch.zeros(m[4], dtype=torch.float32, device=device) for m in matrices}
+    out_full = {(m[0].split(".")[-1], m[2]): torch.zeros(m[2], dtype=torch.float32, device=device) for m in matrices}
+    out_shard = {(m[0].split(".")[-1], m[4]): torch.zeros(m[4], dtype=torch.float32, device=device) for m in matrices}
 
     def aligned(tensor):
         return (tensor.data_ptr() + 255) // 256 * 256
 
-    def step(stream_ptr):
-        """One pass: activations quantised once per distinct input of a layer (as the reference's executor does,
-        Qwen2CpuExecutor.cs:165-185), then every projection on the shared quantised activations."""
-        for name, ggml_type, rows, columns, shard_rows, matrix in matrices:
-            leaf = name.split(".")[-1]
-            if leaf in ("attn_q", "attn_o", "ffn_gate", "ffn_down", "lm_head"):
-                sb.quantize_device(x_dev[columns].data_ptr(), 1, columns, columns, aligned(scratch[columns]),
-                                   lib.activation_scratch_bytes(1, columns), stream_ptr)
-            target = out_shard[shard_rows] if world > 1 else out_full[rows]
-            matrix.matmul_q8_device(aligned(scratch[columns]), 1, target.data_ptr(), shard_rows, stream=stream_ptr)
-            if world > 1:
-                dist.all_gather_into_tensor(out_full[rows], target)
+    side = [torch.cuda.Stream(device), torch.cuda.Stream(device)]
+
+    def product(entry, stream):
+        name, ggml_type, rows, columns, shard_rows, matrix = entry
+        target = out_shard[(name.split(".")[-1], shard_rows)] if world > 1 else out_full[(name.split(".")[-1], rows)]
+        if args.quantize == "fused":
+            matrix.matvec_device(x_dev[columns].data_ptr(), 1, columns, target.data_ptr(), shard_rows, sb.MODE_XQ8,
+                                 scratch_ptr=aligned(scratch[columns]), scratch_bytes=lib.activation_scratch_bytes(1, columns),
+                                 stream=stream.cuda_stream)
+        else:
+            matrix.matmul_q8_device(aligned(scratch[columns]), 1, target.data_ptr(), shard_rows, stream=stream.cuda_stream)
+        if world > 1:
+            with torch.cuda.stream(stream):
+                dist.all_gather_into_tensor(out_full[(name.split(".")[-1], rows)], target)
+
+    def quantize(columns, stream):
+        if args.quantize == "shared":
+            sb.quantize_device(x_dev[columns].data_ptr(), 1, columns, columns, aligned(scratch[columns]),
+                               lib.activation_scratch_bytes(1, columns), stream.cuda_stream)
+
+    def parallel(entries, main):
+        """Independent products of the same input: the first on the main stream, the others on side streams."""
+        if args.serial or len(entries) == 1:
+            for entry in entries:
+                product(entry, main)
+            return
+        fork = torch.cuda.Event()
+        fork.record(main)
+        for entry, stream in zip(entries[1:], side):
+            stream.wait_event(fork)
+            product(entry, stream)
+        product(entries[0], main)
+        for _, stream in zip(entries[1:], side):
+            join = torch.cuda.Event()
+            join.record(stream)
+            main.wait_event(join)
+
+    def step(main):
+        """One pass. Activations are quantised once per distinct input of a layer (as the reference's executor does,
+        Qwen2CpuExecutor.cs:165-185) or inside each product; q/k/v and gate/up are independent and run on parallel
+        branches of the graph, everything else in stream order."""
+        by_name = {m[0]: m for m in matrices}
+        for layer in range(args.layers):
+            get = lambda leaf: by_name[f"blk.{layer}.{leaf}"]
+            quantize(3584, main)
+            parallel([get("attn_q"), get("attn_k"), get("attn_v")], main)
+            quantize(3584, main)
+            parallel([get("attn_o")], main)
+            quantize(3584, main)
+            parallel([get("ffn_gate"), get("ffn_up")], main)
+            quantize(18944, main)
+            parallel([get("ffn_down")], main)
+        quantize(3584, main)
+        parallel([by_name["lm_head"]], main)
 
     stream = torch.cuda.Stream(device)
     graph = None
     lib.launch_count(reset=True)
     with torch.cuda.stream(stream):
-        step(stream.cuda_stream)
-    stream.synchronize()
+        step(stream)
+    torch.cuda.synchronize()
     launches_per_step = lib.launch_count(reset=True)
     use_graph = not args.no_graph and world == 1
     if use_graph:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            step(torch.cuda.current_stream().cuda_stream)
+            step(torch.cuda.current_stream())
 
     def run_step():
         if graph is not None:
             graph.replay()
         else:
-            step(stream.cuda_stream)
+            step(stream)
 
     def barrier():
         if world > 1:
@@ -314,19 +360,32 @@ def main():
     # ---- roofline of the dominant kernel: the Q4_K matvec on the gate/up matrices (38 MB each) -------------
     big = [m for m in matrices if m[0].endswith("ffn_gate") or m[0].endswith("ffn_up")]
     per_launch_bytes = big[0][4] * synth.row_bytes(big[0][1], big[0][3])
-    durations = []
+    # Every gate/up matrix once per pass (56 x 38 MB, no L2 reuse), launches back to back in stream order; timed with
+    # CUDA events on the launch stream around whole passes, so the figure includes the gaps between launches.
+    def roofline_pass(main):
+        for name, ggml_type, rows, columns, shard_rows, matrix in big:
+            matrix.matmul_q8_device(aligned(scratch[columns]), 1, out_full[(name.split(".")[-1], rows)].data_ptr(), shard_rows,
+                                    stream=main.cuda_stream)
+
     with torch.cuda.stream(stream):
-        for repeat in range(3):
-            for name, ggml_type, rows, columns, shard_rows, matrix in big:
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                matrix.matmul_q8_device(aligned(scratch[columns]), 1, out_shard[shard_rows].data_ptr() if world > 1 else out_full[rows].data_ptr(),
-                                        shard_rows, stream=stream.cuda_stream)
-                e1.record(stream)
-                if repeat > 0:
-                    durations.append((e0, e1))
+        roofline_pass(stream)
         stream.synchronize()
-    kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in durations]))
+    roofline_graph = None
+    if use_graph:
+        roofline_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(roofline_graph, stream=stream):
+            roofline_pass(torch.cuda.current_stream())
+    passes = 5
+    with torch.cuda.stream(stream):
+        roofline_graph.replay() if roofline_graph is not None else roofline_pass(stream)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(passes):
+            roofline_graph.replay() if roofline_graph is not None else roofline_pass(stream)
+        e1.record(stream)
+        stream.synchronize()
+    kernel_ms = e0.elapsed_time(e1) / (passes * len(big))
+    durations = [None] * (passes * len(big))
     peak, peak_kind = measured_peak_hbm()
     achieved = per_launch_bytes / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": "matvec_xq8_kernel<Q4_K, T=1> on ffn_gate/ffn_up (18944x3584)", "achieved": achieved,
@@ -338,6 +397,7 @@ def main():
     if not args.no_e2e:
         host_x = {k: torch.from_numpy(v).pin_memory() for k, v in x_host.items()}
         host_y = {m[4]: torch.zeros(m[4], dtype=torch.float32).pin_memory() for m in matrices}
+        torch.cuda.synchronize()
         h2d = sum(4 * m[3] for m in matrices)
         d2h = sum(4 * m[4] for m in matrices)
 
@@ -374,6 +434,7 @@ def main():
                 "config": {"workload": WORKLOAD, "layers": args.layers, "matrices": len(matrices), "bytes_per_step": total_bytes,
                            "activation_contract": "xq8 (Q8_0 activation quantiser reproduced on device)",
                            "layout": "Q4_K file layout; Q6_K repacked to planes at load", "cuda_graph": bool(graph is not None),
+                           "quantize": args.quantize, "branches": "serial" if args.serial else "q|k|v and gate|up on parallel graph branches",
                            "l2": "weights per step exceed L2 35x, no flush", "parallelism": f"row-shard x{world}" if world > 1 else "single gpu",
                            "tokens_per_s": 1e3 / ms_per_step},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,

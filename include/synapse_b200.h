@@ -178,6 +178,11 @@ SYN_B200_API int32_t syn_b200_gemm_dev(const syn_b200_matrix *matrix, const floa
                           float *y, uint64_t out_stride, uint32_t precision, void *scratch,
                           uint64_t scratch_bytes, void *stream);
 
+/* Number of bounded device-side waits that gave up since the last reset (0 in a healthy run). A kernel whose
+ * wait on one of its own asynchronous copies runs out of patience records it here and still terminates; the
+ * results of that launch are then undefined. No counterpart in the reference. */
+SYN_B200_API uint32_t syn_b200_device_faults(uint32_t reset);
+
 /* Number of kernel launches the library has queued from the calling thread since the last reset
  * (benchmark bookkeeping). Passing a non-zero `reset` clears the counter after reading it. */
 SYN_B200_API uint64_t syn_b200_launch_count(uint32_t reset);

@@ -76,6 +76,7 @@ _EXPORTS = {
     "syn_b200_gemm_scratch_bytes": (c_uint64, [c_uint64, c_uint64]),
     "syn_b200_gemm_dev": (c_int32, [c_void_p, c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32, c_void_p, c_uint64, c_void_p]),
     "syn_b200_launch_count": (c_uint64, [c_uint32]),
+    "syn_b200_device_faults": (c_uint32, [c_uint32]),
 }
 
 
@@ -146,6 +147,10 @@ class NativeB200Library:
 
     def launch_count(self, reset: bool = False) -> int:
         return int(self._h.syn_b200_launch_count(1 if reset else 0))
+
+    def device_faults(self, reset: bool = False) -> int:
+        """Bounded device-side waits that gave up since the last reset; 0 in a healthy run."""
+        return int(self._h.syn_b200_device_faults(1 if reset else 0))
 
     def activation_scratch_bytes(self, tokens: int, columns: int) -> int:
         return int(self._h.syn_b200_activation_scratch_bytes(tokens, columns))

@@ -2,6 +2,7 @@
 // Conventions follow the reference's native libraries (status codes and thread-local last error:
 // native/synapse-gpu/src/Features/GpuKernels/ffi.rs:18-44,89-104; validation before any read:
 // native/synapse-kernels/src/Features/CpuKernels/q8_0.rs:212-246).
+#include <cstdlib>
 #include <exception>
 #include <mutex>
 #include <new>
@@ -35,6 +36,52 @@ int32_t cuda_fail(cudaError_t error, const char *what)
 }
 
 void count_launch() { ++g_launches; }
+
+bool use_pdl()
+{
+    static const bool enabled = std::getenv("SYN_B200_NO_PDL") == nullptr;
+    return enabled;
+}
+
+namespace {
+uint32_t *g_fault_host = nullptr;
+uint32_t *g_fault_device = nullptr;
+std::once_flag g_fault_once;
+}  // namespace
+
+uint32_t *fault_word_device()
+{
+    std::call_once(g_fault_once, [] {
+        void *host = nullptr;
+        if (cudaHostAlloc(&host, 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+            cudaGetLastError();
+            return;
+        }
+        *static_cast<volatile uint32_t *>(host) = 0;
+        void *device = nullptr;
+        if (cudaHostGetDevicePointer(&device, host, 0) != cudaSuccess) {
+            cudaGetLastError();
+            cudaFreeHost(host);
+            return;
+        }
+        g_fault_host = static_cast<uint32_t *>(host);
+        g_fault_device = static_cast<uint32_t *>(device);
+    });
+    return g_fault_device;
+}
+
+uint32_t fault_word_read(bool reset)
+{
+    if (!g_fault_host) {
+        return 0;
+    }
+    volatile uint32_t *word = g_fault_host;
+    const uint32_t value = *word;
+    if (reset) {
+        *word = 0;
+    }
+    return value;
+}
 
 int sm_count(int device)
 {
@@ -178,7 +225,7 @@ int32_t create_matrix(const void *blocks, bool from_device, uint32_t type, uint6
     }
     uint64_t row_bytes = 0, total = 0;
     if (!mul_ok(columns / values, block_bytes(type), &row_bytes) || !mul_ok(rows, row_bytes, &total) ||
-        rows > (1ull << 40) || columns > (1ull << 31)) {
+        rows > (1ull << 31) || columns > (1ull << 31)) {
         return fail(SYN_B200_INVALID_ARGUMENT, "matrix size overflows");
     }
     int device = 0;
@@ -186,6 +233,7 @@ int32_t create_matrix(const void *blocks, bool from_device, uint32_t type, uint6
     if (status != SYN_B200_OK) {
         return status;
     }
+    fault_word_device();  // mapped once here, never during a stream capture
     syn_b200_matrix *m = new syn_b200_matrix();
     m->type = type;
     m->flags = flags;
@@ -268,14 +316,11 @@ int32_t product_dev(const syn_b200_matrix *m, uint64_t row_start, uint64_t row_c
         if (reinterpret_cast<uintptr_t>(scratch) & 255) {
             return fail(SYN_B200_INVALID_ARGUMENT, "activation scratch must be 256-byte aligned");
         }
-        uint8_t *base = static_cast<uint8_t *>(scratch);
-        cudaError_t error = launch_quantize(x, tokens, m->columns, in_stride, reinterpret_cast<int8_t *>(base + layout.codes),
-                                            reinterpret_cast<float *>(base + layout.scales),
-                                            reinterpret_cast<int16_t *>(base + layout.sums), stream);
-        if (error != cudaSuccess) {
-            return cuda_fail(error, "launching the activation quantiser");
-        }
+        // The kernel quantises x itself where it can; the scratch serves the shapes where it cannot.
         args.act = act_view(scratch, tokens, m->columns);
+        args.act_ready = false;
+        args.x = x;
+        args.in_stride = in_stride;
     } else {
         args.x = x;
         args.in_stride = in_stride;
@@ -308,6 +353,8 @@ size_t syn_b200_last_error(uint8_t *buffer, size_t capacity)
     }
     return message.size();
 }
+
+uint32_t syn_b200_device_faults(uint32_t reset) { return fault_word_read(reset != 0); }
 
 uint64_t syn_b200_launch_count(uint32_t reset)
 {
@@ -488,6 +535,7 @@ int32_t syn_b200_matmul_q8_dev(const syn_b200_matrix *matrix, uint64_t row_start
         args.row_count = row_count;
         args.tokens = tokens;
         args.act = act_view(scratch, tokens, matrix->columns);
+        args.act_ready = true;
         args.y = y;
         args.out_stride = out_stride;
         args.mode = SYN_B200_MODE_XQ8;
@@ -617,6 +665,7 @@ int32_t syn_b200_matmul_q8(const syn_b200_matrix *matrix, uint64_t row_start, ui
         args.row_count = row_count;
         args.tokens = tokens;
         args.act = act_view(stage, tokens, K);
+        args.act_ready = true;
         args.y = dy;
         args.out_stride = output_stride;
         args.mode = SYN_B200_MODE_XQ8;
@@ -673,6 +722,7 @@ int32_t syn_b200_block_dots(const syn_b200_matrix *matrix, uint64_t row_start, u
         args.row_count = row_count;
         args.tokens = tokens;
         args.act = act_view(stage, tokens, K);
+        args.act_ready = true;
         args.y = reinterpret_cast<float *>(stage + layout.total + dump_bytes);
         args.out_stride = row_count;
         args.mode = SYN_B200_MODE_XQ8;

@@ -91,6 +91,30 @@ int32_t fail(int32_t status, const std::string &message);
 int32_t cuda_fail(cudaError_t error, const char *what);
 void count_launch();
 int sm_count(int device);
+// True unless SYN_B200_NO_PDL is set: kernels are launched with programmatic stream serialization, so a kernel's
+// prologue and first weight copies overlap the tail of the kernel before it.
+bool use_pdl();
+
+// Launches `kernel` on `stream`, with the programmatic-dependent-launch attribute when enabled.
+template <class... Params, class... Args>
+cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = use_pdl() ? 1 : 0;
+    count_launch();
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+// A host-mapped word that kernels bump when a bounded wait gives up (device pointer; null if it cannot be mapped).
+uint32_t *fault_word_device();
+uint32_t fault_word_read(bool reset);
 
 // quantize.cu
 cudaError_t launch_quantize(const float *x, uint64_t tokens, uint64_t columns, uint64_t in_stride, int8_t *codes,
@@ -107,8 +131,10 @@ struct MatvecArgs {
     const syn_b200_matrix *matrix;
     uint64_t row_start, row_count;
     uint64_t tokens;
-    // XQ8: quantised activations; XF32: x with in_stride
+    // XF32: FP32 activations x with in_stride. XQ8: either ready-made quantised activations in `act`
+    // (act_ready), or FP32 x that the kernel quantises itself; `act` is then scratch for the cases where it cannot.
     ActView act;
+    bool act_ready;
     const float *x;
     uint64_t in_stride;
     float *y;

@@ -1,0 +1,646 @@
+// The quantised-activation (XQ8) matrix-vector kernel and its launcher, instantiated once per weight format in
+// matvec_q8_0.cu / matvec_q4_k.cu / matvec_q6_k.cu.
+//
+// Work split. A row is cut into "units" (the 16 or 64 weights one lane reads per step). A team of W warps covers
+// the row: warp w of the team owns units [(i*W + w)*UPL*32, +UPL*32) for i = 0.., lane l takes unit +j*32 + l.
+// W and UPL depend only on the row length, never on the number of rows or tokens, so a row's FP32 summation
+// order -- lane chain, xor-shuffle tree, then the team's warps in index order -- is the same for every row range
+// and token count (the reference's kernels are batch-invariant in the same way, cuda/kernels/matmul.cu:1-2).
+// When one pass of the team covers the row and a single token is multiplied, each lane keeps its slice of the
+// quantised activations in registers for the whole launch, and the loop body is weight loads + dp4a only.
+// The grid is persistent (a multiple of the SM count); every CTA runs the same number of iterations so the
+// team reduction can use one CTA barrier per iteration with double-buffered partial sums.
+#pragma once
+#include "matvec_formats.cuh"
+
+namespace syn {
+namespace mv {
+
+// Programmatic dependent launch: `pdl_launch_dependents` lets the next kernel of the stream start its prologue
+// as soon as every CTA of this grid has passed this point; `pdl_wait` blocks until the kernel before this one has
+// finished and its writes are visible. A kernel must not read anything an earlier kernel may have written, nor
+// write global memory at all, before `pdl_wait`. Both are no-ops in an ordinary launch.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Shared-memory layout of in-kernel quantised activations for T tokens of K values.
+__host__ __device__ inline uint32_t shared_act_codes_bytes(uint32_t tokens, uint32_t K) { return (tokens * K + 127u) & ~127u; }
+__host__ __device__ inline uint32_t shared_act_side_bytes(uint32_t tokens, uint32_t K) { return (tokens * (K / 8) + 127u) & ~127u; }
+__host__ __device__ inline uint32_t shared_act_bytes(uint32_t tokens, uint32_t K)
+{
+    return shared_act_codes_bytes(tokens, K) + 2 * shared_act_side_bytes(tokens, K);
+}
+
+// The Q8_0 activation quantiser (same arithmetic as quantize.cu, bit for bit) run by the `warps` calling warps of a
+// CTA straight into shared memory. A lane reads four consecutive values (one 128-bit load), so a warp covers four
+// 32-value blocks per load with eight lanes per block; eight loads per lane are in flight to cover the L2 latency.
+template <int T>
+__device__ __forceinline__ void quantize_to_shared(const float *__restrict__ x, uint64_t in_stride, uint32_t K, uint32_t live, uint32_t warp,
+                                                   uint32_t warps, uint32_t lane, const ActShared &dst)
+{
+    constexpr int kDepth = 8;
+    const uint32_t quads = (K + 127) / 128;  // groups of four blocks
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+        const float *xt = x + (uint64_t)min((uint32_t)t, live - 1) * in_stride;
+        for (uint32_t q0 = warp; q0 < quads; q0 += warps * kDepth) {
+            float4 v[kDepth];
+#pragma unroll
+            for (int i = 0; i < kDepth; ++i) {
+                const uint32_t first = (q0 + i * warps) * 128 + lane * 4;
+                v[i] = first < K ? __ldg(reinterpret_cast<const float4 *>(xt + first)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int i = 0; i < kDepth; ++i) {
+                const uint32_t first = (q0 + i * warps) * 128 + lane * 4;
+                float amax = fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
+                amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 2));
+                amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 4));
+                const float scale = __fdiv_rn(amax, 127.0f);
+                const float inverse = scale == 0.0f ? 0.0f : __fdiv_rn(1.0f, scale);
+                const int c0 = __float2int_rn(__fmul_rn(v[i].x, inverse)), c1 = __float2int_rn(__fmul_rn(v[i].y, inverse));
+                const int c2 = __float2int_rn(__fmul_rn(v[i].z, inverse)), c3 = __float2int_rn(__fmul_rn(v[i].w, inverse));
+                int sum = (c0 + c1) + (c2 + c3);
+                sum += __shfl_xor_sync(kFull, sum, 1);
+                sum += __shfl_xor_sync(kFull, sum, 2);
+                if (first < K) {
+                    const uint32_t packed = (uint32_t)(c0 & 0xff) | ((uint32_t)(c1 & 0xff) << 8) | ((uint32_t)(c2 & 0xff) << 16) | ((uint32_t)c3 << 24);
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst.codes + t * K + first), "r"(packed) : "memory");
+                    if ((lane & 3) == 0) {
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst.sums + (t * (K / 16) + first / 16) * 2), "h"((short)sum) : "memory");
+                    }
+                    if ((lane & 7) == 0) {
+                        asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst.scales + (t * (K / 32) + first / 32) * 4), "f"(__half2float(__float2half_rn(scale)))
+                                     : "memory");
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Consumer warps of a CTA for a team of W warps: as many whole teams as fit in eight warps.
+__host__ __device__ constexpr int team_warps(int W) { return (kWarps / W) * W; }
+
+template <class F, int T, int W, int UPL, int R, bool REGS, bool DUMP>
+__global__ void __launch_bounds__(team_warps(W) * 32)
+matvec_xq8_team_kernel(WeightView w, ActView act, uint64_t K, uint64_t rows, uint32_t tokens, float *__restrict__ y,
+                       uint64_t out_stride, uint32_t accumulate, int32_t *__restrict__ dump, uint64_t dump_groups)
+{
+    static_assert(!REGS || T == 1, "register-resident activations are for single-token launches");
+    constexpr int kTeams = kWarps / W;
+    constexpr int kConsumers = team_warps(W);
+    __shared__ float partial[2][kConsumers][R * T];
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warp_in_cta = threadIdx.x >> 5;
+    const uint32_t team_in_cta = warp_in_cta / W;
+    const uint32_t warp_in_team = warp_in_cta % W;
+    const uint64_t team = (uint64_t)blockIdx.x * kTeams + team_in_cta;
+    const uint64_t teams = (uint64_t)gridDim.x * kTeams;
+    const uint64_t token0 = (uint64_t)blockIdx.y * T;
+    const uint32_t live = min((uint32_t)T, tokens - (uint32_t)token0);
+    const uint64_t units = F::units(K);
+    const uint64_t passes = (units + (uint64_t)W * UPL * 32 - 1) / ((uint64_t)W * UPL * 32);
+    const uint64_t iterations = (rows + teams * R - 1) / (teams * R);
+    pdl_launch_dependents();
+    pdl_wait();
+
+    typename F::Act held[REGS ? UPL : 1];
+    if (REGS) {
+#pragma unroll
+        for (int j = 0; j < UPL; ++j) {
+            const uint64_t u = ((uint64_t)warp_in_team * UPL + j) * 32 + lane;
+            F::template load_act<GlobalMem>(act_global(act), K, token0, u < units ? u : units - 1, held[j]);
+        }
+    }
+
+    for (uint64_t it = 0; it < iterations; ++it) {
+        const uint64_t row0 = (it * teams + team) * R;
+        float acc[R][T];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+                acc[r][t] = 0.0f;
+            }
+        }
+        for (uint64_t pass = 0; pass < passes; ++pass) {
+            typename F::W wr[R][UPL];
+            uint64_t u[UPL];
+            bool valid[UPL];
+#pragma unroll
+            for (int j = 0; j < UPL; ++j) {
+                const uint64_t unit = ((pass * W + warp_in_team) * UPL + j) * 32 + lane;
+                valid[j] = unit < units;
+                u[j] = valid[j] ? unit : units - 1;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    F::template load_w<GlobalMem>(w, K, min(row0 + r, rows - 1), u[j], lane, wr[r][j]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < UPL; ++j) {
+#pragma unroll
+                for (int t = 0; t < T; ++t) {
+                    typename F::Act loaded;
+                    if (!REGS) {
+                        F::template load_act<GlobalMem>(act_global(act), K, token0 + min((uint32_t)t, live - 1), u[j], loaded);
+                    }
+                    const typename F::Act &a = REGS ? held[j] : loaded;
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        int32_t *target = DUMP ? dump + ((token0 + t) * rows + min(row0 + r, rows - 1)) * dump_groups : nullptr;
+                        F::template dot<DUMP>(wr[r][j], a, valid[j], u[j], lane, acc[r][t], target);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+                acc[r][t] = warp_sum(acc[r][t]);
+            }
+        }
+        if (W == 1) {
+            if (lane == 0) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+#pragma unroll
+                    for (int t = 0; t < T; ++t) {
+                        if (row0 + r < rows && (uint32_t)t < live) {
+                            float *destination = y + (token0 + t) * out_stride + row0 + r;
+                            *destination = accumulate ? *destination + acc[r][t] : acc[r][t];
+                        }
+                    }
+                }
+            }
+        } else {
+            const uint32_t buffer = (uint32_t)(it & 1);
+            if (lane == 0) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+#pragma unroll
+                    for (int t = 0; t < T; ++t) {
+                        partial[buffer][warp_in_cta][r * T + t] = acc[r][t];
+                    }
+                }
+            }
+            __syncthreads();
+            if (warp_in_team == 0 && lane < R * T) {
+                const uint32_t r = lane / T, t = lane % T;
+                float total = partial[buffer][team_in_cta * W][lane];
+#pragma unroll
+                for (int k = 1; k < W; ++k) {
+                    total += partial[buffer][team_in_cta * W + k][lane];
+                }
+                if (row0 + r < rows && t < live) {
+                    float *destination = y + (token0 + t) * out_stride + row0 + r;
+                    *destination = accumulate ? *destination + total : total;
+                }
+            }
+        }
+    }
+}
+
+
+template <class F, int T, int W, int UPL, int R, bool REGS, bool DUMP>
+cudaError_t launch_team(const MatvecArgs &a, const WeightView &view, uint64_t dump_groups, cudaStream_t stream)
+{
+    constexpr int kTeams = kWarps / W;
+    const uint64_t row_groups = (a.row_count + R - 1) / R;
+    uint64_t ctas = (row_groups + kTeams - 1) / kTeams;
+    // Persistent grid: exactly as many CTAs as the SMs can hold at once for this instantiation.
+    static int resident = 0;
+    if (resident == 0) {
+        int blocks = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, matvec_xq8_team_kernel<F, T, W, UPL, R, REGS, DUMP>, team_warps(W) * 32, 0) !=
+                cudaSuccess || blocks <= 0) {
+            cudaGetLastError();
+            blocks = 2;
+        }
+        resident = blocks;
+    }
+    const uint64_t cap = (uint64_t)sm_count(a.matrix->device) * resident;
+    if (ctas > cap) {
+        ctas = cap;
+    }
+    const dim3 grid((unsigned)ctas, (unsigned)((a.tokens + T - 1) / T));
+    return launch_kernel(matvec_xq8_team_kernel<F, T, W, UPL, R, REGS, DUMP>, grid, dim3(team_warps(W) * 32), 0, stream, view, a.act,
+                         a.matrix->columns, a.row_count, (uint32_t)a.tokens, a.y, a.out_stride,
+                         (uint32_t)(a.epilogue == SYN_B200_EPILOGUE_ACCUMULATE), a.dump, dump_groups);
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Pipelined variant: the same team geometry and arithmetic, but the weights of a row group reach the CTA through
+// a ring of shared-memory stages filled by bulk asynchronous copies (cp.async.bulk, completion on an mbarrier).
+// One extra warp issues the copies; the eight consumer warps wait for a stage, pull their units into registers,
+// hand the stage back, and compute. The copy engine keeps `stages` groups in flight per CTA whatever the
+// consumers are doing, which is what an HBM-bound kernel needs. Every wait is bounded: when it gives up the
+// kernel bumps the host-mapped fault word, stops waiting and still runs to completion (with wrong results).
+// ------------------------------------------------------------------------------------------------------
+
+constexpr int kMaxStages = 8;
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kStageBudget = 100 * 1024;  // dynamic shared memory per CTA, so that two CTAs fit one SM
+
+struct PipeArgs {
+    WeightView global;            // plane bases at the first row of the call
+    uint32_t plane_row_bytes[4];  // bytes of one row in each plane
+    uint32_t plane_offset[4];     // offset of each plane inside a stage
+    uint32_t planes, stages, stage_bytes;
+    uint32_t act_bytes;           // shared memory reserved for in-kernel quantised activations (0 when not fused)
+};
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+    }
+    return false;
+}
+// Weights are read once per launch: mark their lines evict-first so activations and outputs stay in L2.
+__device__ __forceinline__ uint64_t l2_evict_first_policy()
+{
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+                 : "memory");
+}
+template <int THREADS>
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory"); }
+
+template <class F, int T, int W, int UPL, int R, bool REGS, bool FUSED>
+__global__ void __launch_bounds__(team_warps(W) * 32 + 32, F::min_ctas(W))
+matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uint64_t in_stride, uint64_t K, uint64_t rows, uint32_t tokens,
+                       float *__restrict__ y, uint64_t out_stride, uint32_t accumulate, uint32_t *fault)
+{
+    static_assert(!REGS || T == 1, "register-resident activations are for single-token launches");
+    constexpr int kTeams = kWarps / W;
+    constexpr int kConsumers = team_warps(W);
+    constexpr uint64_t G = (uint64_t)kTeams * R;  // rows per stage
+    extern __shared__ __align__(128) uint8_t stage_memory[];
+    __shared__ float partial[2][kConsumers][R * T];
+    __shared__ __align__(8) uint64_t barriers[2 * kMaxStages];  // full[s] then empty[s]
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warp_in_cta = threadIdx.x >> 5;
+    const uint64_t groups = (rows + G - 1) / G;
+    const uint64_t my_groups = groups > blockIdx.x ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t full0 = smem_u32(&barriers[0]), empty0 = smem_u32(&barriers[kMaxStages]);
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.stages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, kConsumers);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    // With in-kernel quantisation the first p.act_bytes of dynamic shared memory hold the activations.
+    uint8_t *const ring = stage_memory + (FUSED ? p.act_bytes : 0);
+
+    if (warp_in_cta == kConsumers) {
+        // Producer warp: one lane streams this CTA's row groups into the ring.
+        if (lane == 0) {
+            const uint8_t *bases[4] = {p.global.p0, p.global.p1, p.global.p2, p.global.p3};
+            const uint64_t policy = l2_evict_first_policy();
+            uint32_t s = 0, round = 0;  // ring slot and how many times the ring has wrapped
+            uint64_t row0 = (uint64_t)blockIdx.x * G;
+            for (uint32_t it = 0; it < my_groups; ++it, row0 += (uint64_t)gridDim.x * G) {
+                if (round > 0 && !mbar_wait(empty0 + 8 * s, (round - 1) & 1) && fault) {
+                    atomicAdd(fault, 1u);
+                }
+                const uint64_t n = min(G, rows - row0);
+                uint32_t total = 0;
+                uint32_t bytes[4];
+                const uint8_t *sources[4];
+#pragma unroll
+                for (int k = 0; k < F::kPlanes; ++k) {
+                    const uint8_t *source = bases[k] + row0 * p.plane_row_bytes[k];
+                    const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(source) & 15);
+                    sources[k] = source - shift;
+                    bytes[k] = (uint32_t)((shift + n * p.plane_row_bytes[k] + 15) & ~(uint64_t)15);
+                    total += bytes[k];
+                }
+                mbar_expect_tx(full0 + 8 * s, total);
+                const uint32_t stage = smem_u32(ring) + s * p.stage_bytes;
+#pragma unroll
+                for (int k = 0; k < F::kPlanes; ++k) {
+                    bulk_copy(stage + p.plane_offset[k], sources[k], bytes[k], full0 + 8 * s, policy);
+                }
+                if (++s == p.stages) {
+                    s = 0;
+                    ++round;
+                }
+            }
+        }
+        return;
+    }
+
+    const uint32_t team_in_cta = warp_in_cta / W;
+    const uint32_t warp_in_team = warp_in_cta % W;
+    const uint64_t token0 = (uint64_t)blockIdx.y * T;
+    const uint32_t live = min((uint32_t)T, tokens - (uint32_t)token0);
+    const uint64_t units = F::units(K);
+    // Register-resident activations imply a single pass over the row (the launcher guarantees it).
+    const uint32_t passes = REGS ? 1u : (uint32_t)((units + (uint64_t)W * UPL * 32 - 1) / ((uint64_t)W * UPL * 32));
+
+    // Weights do not depend on earlier kernels (the producer is already copying them); activations and outputs do.
+    pdl_wait();
+    ActShared shared_act;
+    if (FUSED) {
+        const uint32_t base = smem_u32(stage_memory);
+        shared_act.codes = base;
+        shared_act.scales = base + shared_act_codes_bytes(T, (uint32_t)K);
+        shared_act.sums = shared_act.scales + shared_act_side_bytes(T, (uint32_t)K);
+        quantize_to_shared<T>(x + token0 * in_stride, in_stride, (uint32_t)K, live, warp_in_cta, kConsumers, lane, shared_act);
+        consumer_barrier<kConsumers * 32>();
+    }
+    typename F::Act held[REGS ? UPL : 1];
+    if (REGS) {
+#pragma unroll
+        for (int j = 0; j < UPL; ++j) {
+            const uint64_t u = ((uint64_t)warp_in_team * UPL + j) * 32 + lane;
+            if (FUSED) {
+                F::template load_act<SharedMem>(shared_act, K, 0, u < units ? u : units - 1, held[j]);
+            } else {
+                F::template load_act<GlobalMem>(act_global(act), K, token0, u < units ? u : units - 1, held[j]);
+            }
+        }
+    }
+
+    uint32_t s = 0, phase = 0;
+    uint64_t group_row0 = (uint64_t)blockIdx.x * G;
+    for (uint32_t it = 0; it < my_groups; ++it, group_row0 += (uint64_t)gridDim.x * G) {
+        const uint64_t row0 = group_row0 + (uint64_t)team_in_cta * R;
+        if (!mbar_wait(full0 + 8 * s, phase) && fault && lane == 0) {
+            atomicAdd(fault, 1u);
+        }
+        // The stage holds rows [group_row0, +G) of every plane with the plane's own row pitch; a plane whose rows
+        // are not 16-byte multiples starts `shift` bytes into its slot.
+        SharedView view;
+        view.row_bytes = p.plane_row_bytes[0];
+        {
+            const uint32_t stage = smem_u32(ring) + s * p.stage_bytes;
+            const uint8_t *bases[4] = {p.global.p0, p.global.p1, p.global.p2, p.global.p3};
+            uint32_t local[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int k = 0; k < F::kPlanes; ++k) {
+                const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(bases[k] + group_row0 * p.plane_row_bytes[k]) & 15);
+                local[k] = stage + p.plane_offset[k] + shift;
+            }
+            view.p0 = local[0];
+            view.p1 = local[1];
+            view.p2 = local[2];
+            view.p3 = local[3];
+        }
+        float acc[R][T];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+                acc[r][t] = 0.0f;
+            }
+        }
+        for (uint32_t pass = 0; pass < passes; ++pass) {
+            typename F::W wr[R][UPL];
+            uint64_t u[UPL];
+            bool valid[UPL];
+#pragma unroll
+            for (int j = 0; j < UPL; ++j) {
+                const uint64_t unit = (((uint64_t)pass * W + warp_in_team) * UPL + j) * 32 + lane;
+                valid[j] = unit < units;
+                u[j] = valid[j] ? unit : units - 1;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    F::template load_w<SharedMem>(view, K, (uint64_t)team_in_cta * R + r, u[j], lane, wr[r][j]);
+                }
+            }
+            if (pass + 1 == passes) {
+                // Every unit of this warp is in registers: give the stage back to the producer.
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(empty0 + 8 * s);
+                }
+                if (++s == p.stages) {
+                    s = 0;
+                    phase ^= 1;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < UPL; ++j) {
+#pragma unroll
+                for (int t = 0; t < T; ++t) {
+                    typename F::Act loaded;
+                    if (!REGS) {
+                        if (FUSED) {
+                            F::template load_act<SharedMem>(shared_act, K, (uint32_t)t, u[j], loaded);
+                        } else {
+                            F::template load_act<GlobalMem>(act_global(act), K, token0 + min((uint32_t)t, live - 1), u[j], loaded);
+                        }
+                    }
+                    const typename F::Act &a = REGS ? held[j] : loaded;
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        F::template dot<false>(wr[r][j], a, valid[j], u[j], lane, acc[r][t], nullptr);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+                acc[r][t] = warp_sum(acc[r][t]);
+            }
+        }
+        if (W == 1) {
+            if (lane == 0) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+#pragma unroll
+                    for (int t = 0; t < T; ++t) {
+                        if (row0 + r < rows && (uint32_t)t < live) {
+                            float *destination = y + (token0 + t) * out_stride + row0 + r;
+                            *destination = accumulate ? *destination + acc[r][t] : acc[r][t];
+                        }
+                    }
+                }
+            }
+        } else {
+            const uint32_t buffer = it & 1;
+            if (lane == 0) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+#pragma unroll
+                    for (int t = 0; t < T; ++t) {
+                        partial[buffer][warp_in_cta][r * T + t] = acc[r][t];
+                    }
+                }
+            }
+            consumer_barrier<kConsumers * 32>();
+            if (warp_in_team == 0 && lane < R * T) {
+                const uint32_t r = lane / T, t = lane % T;
+                float total = partial[buffer][team_in_cta * W][lane];
+#pragma unroll
+                for (int k = 1; k < W; ++k) {
+                    total += partial[buffer][team_in_cta * W + k][lane];
+                }
+                if (row0 + r < rows && t < live) {
+                    float *destination = y + (token0 + t) * out_stride + row0 + r;
+                    *destination = accumulate ? *destination + total : total;
+                }
+            }
+        }
+    }
+}
+
+// Lays out a stage for this format and row length; false when a group of rows does not fit the stage budget.
+template <class F, int W, int R>
+bool plan_pipe(const MatvecArgs &a, const WeightView &view, uint32_t act_bytes, PipeArgs &p)
+{
+    constexpr uint64_t G = (uint64_t)(kWarps / W) * R;
+    p.global = view;
+    p.planes = F::kPlanes;
+    F::plane_row_bytes(a.matrix->columns, a.matrix->row_bytes, p.plane_row_bytes);
+    uint64_t offset = 0;
+    for (int k = 0; k < F::kPlanes; ++k) {
+        p.plane_offset[k] = (uint32_t)offset;
+        offset += align_up(G * p.plane_row_bytes[k] + 16, 128);
+    }
+    for (int k = F::kPlanes; k < 4; ++k) {
+        p.plane_offset[k] = 0;
+        p.plane_row_bytes[k] = 0;
+    }
+    if (act_bytes >= kStageBudget || offset > (kStageBudget - act_bytes) / 2) {
+        return false;
+    }
+    p.act_bytes = act_bytes;
+    p.stage_bytes = (uint32_t)offset;
+    uint64_t stages = (kStageBudget - act_bytes) / offset;
+    p.stages = (uint32_t)(stages > kMaxStages ? kMaxStages : stages);
+    return true;
+}
+
+template <class F, int T, int W, int UPL, int R, bool REGS, bool FUSED>
+cudaError_t launch_pipe(const MatvecArgs &a, const PipeArgs &p, cudaStream_t stream)
+{
+    constexpr uint64_t G = (uint64_t)(kWarps / W) * R;
+    auto kernel = matvec_xq8_pipe_kernel<F, T, W, UPL, R, REGS, FUSED>;
+    const uint32_t dynamic = p.act_bytes + p.stages * p.stage_bytes;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStageBudget);
+        if (error != cudaSuccess) {
+            return error;
+        }
+        configured = true;
+    }
+    // F::kCtasPerSm CTAs per SM. Where that is one, the kernel is still built so that two fit (registers and
+    // shared memory): the second slot is for the next kernel of the stream, which starts copying its first stages
+    // while this one is still running.
+    uint64_t ctas = (a.row_count + G - 1) / G;
+    const uint64_t cap = (uint64_t)sm_count(a.matrix->device) * F::kCtasPerSm;
+    if (ctas > cap) {
+        ctas = cap;
+    }
+    const dim3 grid((unsigned)ctas, (unsigned)((a.tokens + T - 1) / T));
+    return launch_kernel(kernel, grid, dim3(team_warps(W) * 32 + 32), dynamic, stream, p, a.act, a.x, a.in_stride, a.matrix->columns, a.row_count,
+                         (uint32_t)a.tokens, a.y, a.out_stride, (uint32_t)(a.epilogue == SYN_B200_EPILOGUE_ACCUMULATE), fault_word_device());
+}
+
+template <class F, int W, int UPL>
+cudaError_t launch_tokens(const MatvecArgs &a, const WeightView &view, bool one_pass, uint64_t dump_groups, cudaStream_t stream)
+{
+    constexpr int R = F::kRows;
+    if (a.dump) {
+        return launch_team<F, 1, W, UPL, 1, false, true>(a, view, dump_groups, stream);
+    }
+    PipeArgs pipe;
+    const uint32_t K32 = (uint32_t)a.matrix->columns;
+    if (a.tokens <= 2 && !a.act_ready && plan_pipe<F, W, R>(a, view, shared_act_bytes((uint32_t)a.tokens, K32), pipe)) {
+        // FP32 activations in: the kernel quantises them itself.
+        if (a.tokens <= 1) {
+            return one_pass ? launch_pipe<F, 1, W, UPL, R, true, true>(a, pipe, stream) : launch_pipe<F, 1, W, UPL, R, false, true>(a, pipe, stream);
+        }
+        return launch_pipe<F, 2, W, UPL, R, false, true>(a, pipe, stream);
+    }
+    if (!a.act_ready) {
+        // Shapes the pipelined kernel does not take: quantise into the caller's scratch first.
+        cudaError_t error = launch_quantize(a.x, a.tokens, a.matrix->columns, a.in_stride, const_cast<int8_t *>(a.act.codes),
+                                            const_cast<float *>(a.act.scales), const_cast<int16_t *>(a.act.sums), stream);
+        if (error != cudaSuccess) {
+            return error;
+        }
+    }
+    if (a.tokens <= 2 && plan_pipe<F, W, R>(a, view, 0, pipe)) {
+        if (a.tokens <= 1) {
+            return one_pass ? launch_pipe<F, 1, W, UPL, R, true, false>(a, pipe, stream) : launch_pipe<F, 1, W, UPL, R, false, false>(a, pipe, stream);
+        }
+        return launch_pipe<F, 2, W, UPL, R, false, false>(a, pipe, stream);
+    }
+    // Token group size: the smallest of 1, 2, 4, 8 that holds the tokens (step/projection.rs:82-87).
+    if (a.tokens <= 1) {
+        return one_pass ? launch_team<F, 1, W, UPL, R, true, false>(a, view, 0, stream)
+                        : launch_team<F, 1, W, UPL, R, false, false>(a, view, 0, stream);
+    }
+    if (a.tokens == 2) {
+        return launch_team<F, 2, W, UPL, R, false, false>(a, view, 0, stream);
+    }
+    if (a.tokens <= 4) {
+        return launch_team<F, 4, W, UPL, R, false, false>(a, view, 0, stream);
+    }
+    return launch_team<F, 8, W, UPL, 1, false, false>(a, view, 0, stream);
+}
+
+// Team shape from the row length alone: the fewest warps that cover the row in one pass with F::kMaxUpl units per
+// lane (one unit per lane when the row is short enough); eight warps making several passes for very long rows.
+template <class F>
+cudaError_t launch_format(const MatvecArgs &a, const WeightView &view, uint64_t units, uint64_t dump_groups, cudaStream_t stream)
+{
+    constexpr int U = F::kMaxUpl;
+    if (units <= 32) {
+        return launch_tokens<F, 1, 1>(a, view, true, dump_groups, stream);
+    }
+    switch ((units + 32 * U - 1) / (32 * U)) {
+    case 1: return launch_tokens<F, 1, U>(a, view, true, dump_groups, stream);
+    case 2: return launch_tokens<F, 2, U>(a, view, true, dump_groups, stream);
+    case 3: return launch_tokens<F, 3, U>(a, view, true, dump_groups, stream);
+    case 4: return launch_tokens<F, 4, U>(a, view, true, dump_groups, stream);
+    case 5: return launch_tokens<F, 5, U>(a, view, true, dump_groups, stream);
+    case 6: return launch_tokens<F, 6, U>(a, view, true, dump_groups, stream);
+    case 7: return launch_tokens<F, 7, U>(a, view, true, dump_groups, stream);
+    case 8: return launch_tokens<F, 8, U>(a, view, true, dump_groups, stream);
+    default: return launch_tokens<F, 8, U>(a, view, false, dump_groups, stream);
+    }
+}
+
+}  // namespace mv
+}  // namespace syn

@@ -16,6 +16,8 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
 quantize_q8_kernel(const float *__restrict__ x, uint64_t blocks_per_row, uint64_t total_blocks, uint64_t in_stride,
                    int8_t *__restrict__ codes, float *__restrict__ scales, int16_t *__restrict__ sums)
 {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t lane = threadIdx.x & 31;
     uint64_t block = (uint64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     const uint64_t stride = (uint64_t)gridDim.x * kWarpsPerCta;
@@ -49,6 +51,8 @@ quantize_q8_kernel(const float *__restrict__ x, uint64_t blocks_per_row, uint64_
 // Sums of 16 codes for activations that arrive already quantised.
 __global__ void group_sums_kernel(const int8_t *__restrict__ codes, uint64_t count16, int16_t *__restrict__ sums)
 {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     uint64_t g = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (; g < count16; g += stride) {
@@ -72,10 +76,8 @@ cudaError_t launch_quantize(const float *x, uint64_t tokens, uint64_t columns, u
     if (grid > 148 * 8) {
         grid = 148 * 8;
     }
-    quantize_q8_kernel<<<(unsigned)grid, kWarpsPerCta * 32, 0, stream>>>(x, blocks_per_row, total, in_stride, codes,
-                                                                         scales, sums);
-    count_launch();
-    return cudaGetLastError();
+    return launch_kernel(quantize_q8_kernel, dim3((unsigned)grid), dim3(kWarpsPerCta * 32), 0, stream, x, blocks_per_row, total, in_stride,
+                         codes, scales, sums);
 }
 
 cudaError_t launch_group_sums(const int8_t *codes, uint64_t count16, int16_t *sums, cudaStream_t stream)
@@ -84,9 +86,7 @@ cudaError_t launch_group_sums(const int8_t *codes, uint64_t count16, int16_t *su
     if (grid > 148 * 8) {
         grid = 148 * 8;
     }
-    group_sums_kernel<<<(unsigned)grid, 256, 0, stream>>>(codes, count16, sums);
-    count_launch();
-    return cudaGetLastError();
+    return launch_kernel(group_sums_kernel, dim3((unsigned)grid), dim3(256), 0, stream, codes, count16, sums);
 }
 
 }  // namespace syn
