@@ -1,15 +1,494 @@
-// Prompt-run product on the tensor cores (placeholder until the tcgen05 kernel lands): reports UNAVAILABLE so
-// that no caller can mistake a missing kernel for a result.
+// Prompt-run product on the 5th-generation tensor cores: Y[t][r] = sum_k W[r][k] * X[t][k] for quantised W and
+// many tokens. Replaces synapse_q8_gemm (cuda/kernels/matmul.cu:147-189) and the Metal K-quant GEMMs
+// (metal/shaders/matmul_kquant.metal:227-291), which dequantise into shared memory and multiply with FP32 FMAs.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warps 0-3   epilogue  tcgen05.ld the FP32 accumulator out of tensor memory, scale, store Y
+//   warps 4-11  dequant   read GGUF blocks (L2, one k step ahead), unpack to fp16 with packed-half arithmetic, write
+//                         the B operand tile into shared memory in the 128-byte-swizzled K-major layout the MMA reads
+//   warp  12    loader    bulk-copies the A operand tile (activations, converted and pre-swizzled by a pre-pass)
+//   warp  13    MMA       one lane issues tcgen05.mma (M=128 tokens, N=256 or 128 weight rows, K=16) and commits
+// Tokens are the MMA's M so that the expensive operand to move, the 16-bit activations, is read once per 256 weight
+// rows. The accumulator (128 lanes x 256 columns FP32) is double-buffered in the 512 columns of tensor memory, so
+// the epilogue of one tile overlaps the MMAs of the next. Operands are fp16 (weights carry a 2^8 prescale so that
+// small block scales stay out of the fp16 subnormal range; the epilogue removes it exactly).
+//
+// Every mbarrier wait is bounded: when one gives up the kernel bumps the host-mapped fault word and carries on to
+// completion (with wrong results) instead of hanging, and the tensor memory it holds is always released.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace syn {
 
-uint64_t gemm_scratch_bytes(uint64_t tokens, uint64_t columns) { return align_up(tokens * columns * 2, 256); }
+namespace {
 
-int32_t launch_gemm(const syn_b200_matrix *, const float *, uint64_t, uint64_t, float *, uint64_t, uint32_t, void *, uint64_t,
-                    cudaStream_t)
+constexpr int kTileTokens = 128;  // MMA M
+constexpr int kMaxTileRows = 256; // MMA N: 256, or 128 when that is needed to give every SM a tile
+constexpr int kTileK = 64;        // one 128-byte swizzle row of fp16
+constexpr int kStages = 4;
+constexpr uint32_t kTileABytes = kTileTokens * kTileK * 2;     // 16 KB
+constexpr uint32_t kTileBBytes = kMaxTileRows * kTileK * 2;    // 32 KB
+constexpr uint32_t kStageBytes = kTileABytes + kTileBBytes;
+constexpr uint32_t kDequantWarps = 8;
+constexpr uint32_t kLoaderWarp = 4 + kDequantWarps, kMmaWarp = kLoaderWarp + 1;
+constexpr uint32_t kGemmThreads = (kMmaWarp + 1) * 32;
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr float kPrescale = 256.0f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
 {
-    return fail(SYN_B200_UNAVAILABLE, "the tensor-core product is not part of this build");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, uint32_t *fault)
+{
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) {
+            return;
+        }
+    }
+    if (fault) {
+        atomicAdd(fault, 1u);
+    }
+}
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
+                 "r"(bar)
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows, 128-byte swizzle: 8-row groups are 1024
+// bytes apart (stride byte offset), the leading byte offset is the canonical 1, descriptor version 1 (Blackwell).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t address)
+{
+    return (uint64_t)((address & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16 instruction descriptor: FP32 accumulator, fp16 A and B, both K-major, N weight rows, M = 128 tokens.
+constexpr uint32_t instr_desc(int n) { return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTileTokens >> 4) << 24); }
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Position of 16-byte chunk `c` of row `r` inside a 128-byte-swizzled tile.
+__device__ __forceinline__ uint32_t swizzled(uint32_t r, uint32_t c) { return r * 128u + ((c ^ (r & 7u)) << 4); }
+
+// ------------------------------------------------------------------------------------------------------
+// Pre-pass: FP32 activations -> fp16 A-operand tiles, [token tile][k tile][128 tokens][64 values], each tile stored
+// exactly as it will sit in shared memory (128-byte swizzle). Inside every group of four values the order is
+// (0, 2, 1, 3): that is the order in which the dequantiser's packed-half unpacking produces weights, and the MMA
+// only needs A and B to agree on the order of k. Tokens past the end are zero.
+// ------------------------------------------------------------------------------------------------------
+
+__global__ void convert_activations_kernel(const float *__restrict__ x, uint64_t tokens, uint64_t in_stride, uint32_t k_tiles,
+                                           uint32_t token_tiles, uint8_t *__restrict__ tiles)
+{
+    const uint64_t chunks = (uint64_t)token_tiles * k_tiles * kTileTokens * 8;
+    for (uint64_t index = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; index < chunks; index += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t c = (uint32_t)(index & 7);
+        const uint32_t n = (uint32_t)((index >> 3) & (kTileTokens - 1));
+        const uint64_t tile = index >> 10;  // 128 tokens * 8 chunks
+        const uint32_t kt = (uint32_t)(tile % k_tiles);
+        const uint64_t tt = tile / k_tiles;
+        const uint64_t token = tt * kTileTokens + n;
+        uint4 out = make_uint4(0, 0, 0, 0);
+        if (token < tokens) {
+            const float *source = x + token * in_stride + (uint64_t)kt * kTileK + c * 8;
+            const float4 lo = __ldg(reinterpret_cast<const float4 *>(source));
+            const float4 hi = __ldg(reinterpret_cast<const float4 *>(source + 4));
+            const __half2 h0 = __floats2half2_rn(lo.x, lo.z), h1 = __floats2half2_rn(lo.y, lo.w);
+            const __half2 h2 = __floats2half2_rn(hi.x, hi.z), h3 = __floats2half2_rn(hi.y, hi.w);
+            out = make_uint4(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1),
+                             *reinterpret_cast<const uint32_t *>(&h2), *reinterpret_cast<const uint32_t *>(&h3));
+        }
+        *reinterpret_cast<uint4 *>(tiles + tile * kTileABytes + swizzled(n, c)) = out;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Dequantisers: one thread turns 64 consecutive weights of one row (one k tile) into eight 16-byte chunks of fp16,
+// in the (0, 2, 1, 3) order, times the 2^8 prescale.
+// ------------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
+
+// 6-bit scale and min of sub-block j of a Q4_K super-block (ScaleMinK4, GgufKQuantBlocks.cs:149-153).
+__device__ __forceinline__ void q4k_scale_min(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t j, uint32_t &sc, uint32_t &mn)
+{
+    const uint32_t shift = 8 * (j & 3);
+    if (j < 4) {
+        sc = (w0 >> shift) & 63;
+        mn = (w1 >> shift) & 63;
+    } else {
+        sc = ((w2 >> shift) & 0xF) | (((w0 >> shift) >> 2) & 0x30);
+        mn = (((w2 >> shift) >> 4) & 0xF) | (((w1 >> shift) >> 2) & 0x30);
+    }
+}
+
+struct DequantQ4K {
+    struct Raw {
+        uint4 header, q0, q1;
+    };
+    // `row` points at the row's first super-block; k tile `kt` is chunk kt%4 of super-block kt/4.
+    static __device__ __forceinline__ void load(const uint8_t *row, uint32_t kt, Raw &raw)
+    {
+        const uint8_t *block = row + (uint64_t)(kt >> 2) * 144;
+        raw.header = __ldg(reinterpret_cast<const uint4 *>(block));
+        raw.q0 = __ldg(reinterpret_cast<const uint4 *>(block + 16 + (kt & 3) * 32));
+        raw.q1 = __ldg(reinterpret_cast<const uint4 *>(block + 32 + (kt & 3) * 32));
+    }
+    // Chunks 4*half .. 4*half+3 of the k tile: half 0 = the low nibbles (sub-block 2c), half 1 = the high nibbles
+    // (sub-block 2c+1), where c = kt%4.
+    static __device__ __forceinline__ void expand(const Raw &raw, uint32_t kt, uint32_t half, uint4 (&out)[4])
+    {
+        const float d = __half2float(__ushort_as_half((unsigned short)(raw.header.x & 0xffff))) * kPrescale;
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(raw.header.x >> 16))) * kPrescale;
+        uint32_t sc, mn;
+        q4k_scale_min(raw.header.y, raw.header.z, raw.header.w, 2 * (kt & 3) + half, sc, mn);
+        // value = (d*sc) * q - dmin*m; the high nibbles are used in place as 16*q, so their scale is divided by 16
+        const __half2 a = __float2half2_rn(d * (float)sc * (half ? 0.0625f : 1.0f)), b = __float2half2_rn(-dmin * (float)mn);
+        const __half2 k1024 = __float2half2_rn(1024.0f);
+        const uint32_t mask = half ? 0x00F000F0u : 0x000F000Fu;
+        const uint32_t words[8] = {raw.q0.x, raw.q0.y, raw.q0.z, raw.q0.w, raw.q1.x, raw.q1.y, raw.q1.z, raw.q1.w};
+        uint32_t v[16];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            // 0x6400 | n is the fp16 number 1024 + n: exact integers without a conversion instruction
+            v[2 * j] = h2_bits(__hfma2(__hsub2(bits_h2((words[j] & mask) | 0x64006400u), k1024), a, b));
+            v[2 * j + 1] = h2_bits(__hfma2(__hsub2(bits_h2(((words[j] >> 8) & mask) | 0x64006400u), k1024), a, b));
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            out[c] = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+        }
+    }
+};
+
+// ------------------------------------------------------------------------------------------------------
+// The GEMM kernel
+// ------------------------------------------------------------------------------------------------------
+
+struct GemmArgs {
+    const uint8_t *weights;  // file-layout rows
+    uint64_t row_bytes;
+    uint64_t rows, tokens;
+    uint32_t k_tiles, row_tiles, token_tiles;
+    const uint8_t *x_tiles;  // converted activations
+    float *y;
+    uint64_t out_stride;
+    uint32_t *fault;
+};
+
+template <class Dequant, int N>
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
+{
+    static_assert(N == 128 || N == 256, "the weight-row tile is 128 or 256");
+    constexpr uint32_t kTileRows = N;
+    extern __shared__ __align__(1024) uint8_t shared_raw[];
+    // the dynamic window is only guaranteed 16-byte alignment; the swizzle needs 1024
+    uint8_t *stages = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(shared_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t barriers[2 * kStages + 4];  // full[s], empty[s], acc_full[2], acc_empty[2]
+    __shared__ uint32_t tmem_slot;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t full0 = smem_u32(&barriers[0]), empty0 = smem_u32(&barriers[kStages]);
+    const uint32_t acc_full0 = smem_u32(&barriers[2 * kStages]), acc_empty0 = smem_u32(&barriers[2 * kStages + 2]);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full0 + 8 * s, 1 + kDequantWarps);  // the loader's expect_tx arrival + one arrival per dequant warp
+            mbar_init(empty0 + 8 * s, 1);     // tcgen05.commit
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full0 + 8 * b, 1);   // tcgen05.commit
+            mbar_init(acc_empty0 + 8 * b, 4);  // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    const uint64_t tiles = (uint64_t)a.row_tiles * a.token_tiles;
+
+    if (warp == kLoaderWarp) {
+        // ---- loader: the activation tile of every (tile, k step) --------------------------------------
+        if (lane == 0) {
+            uint32_t s = 0, round = 0;
+            for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+                const uint64_t tt = tile / a.row_tiles;
+                for (uint32_t kt = 0; kt < a.k_tiles; ++kt) {
+                    if (round > 0) {
+                        mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.fault);
+                    }
+                    mbar_expect_tx(full0 + 8 * s, kTileABytes);
+                    bulk_copy(smem_u32(stages + s * kStageBytes), a.x_tiles + (tt * a.k_tiles + kt) * kTileABytes, kTileABytes, full0 + 8 * s);
+                    if (++s == kStages) {
+                        s = 0;
+                        ++round;
+                    }
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ---- MMA issuer -----------------------------------------------------------------------------------
+        if (lane == 0) {
+            uint32_t s = 0, phase = 0, local = 0;
+            for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+                const uint32_t acc = local & 1;
+                if (local >= 2) {
+                    mbar_wait(acc_empty0 + 8 * acc, ((local >> 1) - 1) & 1, a.fault);
+                }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * kMaxTileRows;
+                for (uint32_t kt = 0; kt < a.k_tiles; ++kt) {
+                    mbar_wait(full0 + 8 * s, phase, a.fault);
+                    tc_fence_after();
+                    const uint32_t stage = smem_u32(stages + s * kStageBytes);
+                    const uint64_t desc_a = smem_desc(stage), desc_b = smem_desc(stage + kTileABytes);
+#pragma unroll
+                    for (uint32_t k = 0; k < kTileK / 16; ++k) {
+                        // 16 fp16 = 32 bytes further along the swizzled row: +2 in the descriptor's 16-byte units
+                        umma_f16(tmem_d, desc_a + 2 * k, desc_b + 2 * k, instr_desc(N), (kt | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
+                    if (++s == kStages) {
+                        s = 0;
+                        phase ^= 1;
+                    }
+                }
+                umma_commit(acc_full0 + 8 * acc);  // the accumulator is complete once every MMA above has finished
+            }
+        }
+    } else if (warp >= 4) {
+        // ---- dequant warps: 256 threads over the tile's N rows; with N = 128 two threads share a row, one nibble
+        // half (four of the eight 16-byte chunks) each. The raw blocks of the next k step are fetched before the
+        // current ones are expanded, so the L2 latency is off the critical path.
+        const uint32_t dq = threadIdx.x - 128;
+        const uint32_t r = dq % kTileRows, part = dq / kTileRows;  // part is 0 when N = 256
+        constexpr uint32_t kParts = 256 / kTileRows;               // threads per row
+        uint32_t s = 0, round = 0;
+        typename Dequant::Raw next;
+        uint64_t tile = blockIdx.x;
+        const uint8_t *row = nullptr;
+        if (tile < tiles) {
+            row = a.weights + min((tile % a.row_tiles) * kTileRows + r, a.rows - 1) * a.row_bytes;
+            Dequant::load(row, 0, next);
+        }
+        for (; tile < tiles; tile += gridDim.x) {
+            for (uint32_t kt = 0; kt < a.k_tiles; ++kt) {
+                const typename Dequant::Raw raw = next;
+                if (kt + 1 < a.k_tiles) {
+                    Dequant::load(row, kt + 1, next);
+                } else if (tile + gridDim.x < tiles) {
+                    row = a.weights + min(((tile + gridDim.x) % a.row_tiles) * kTileRows + r, a.rows - 1) * a.row_bytes;
+                    Dequant::load(row, 0, next);
+                }
+                uint4 v[2][4];
+                if (kParts == 1) {
+                    Dequant::expand(raw, kt, 0, v[0]);
+                    Dequant::expand(raw, kt, 1, v[1]);
+                } else {
+                    Dequant::expand(raw, kt, part, v[0]);
+                }
+                if (round > 0) {
+                    mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.fault);
+                }
+                uint8_t *tile_b = stages + s * kStageBytes + kTileABytes;
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c) {
+                    if (kParts == 1) {
+                        *reinterpret_cast<uint4 *>(tile_b + swizzled(r, c)) = v[0][c];
+                        *reinterpret_cast<uint4 *>(tile_b + swizzled(r, 4 + c)) = v[1][c];
+                    } else {
+                        *reinterpret_cast<uint4 *>(tile_b + swizzled(r, 4 * part + c)) = v[0][c];
+                    }
+                }
+                // make the generic-proxy stores visible to the tensor core's (async proxy) reads
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(full0 + 8 * s);
+                }
+                if (++s == kStages) {
+                    s = 0;
+                    ++round;
+                }
+            }
+        }
+    } else {
+        // ---- epilogue warps: warp q owns accumulator lanes (tokens) 32q .. 32q+31 ----------------------
+        uint32_t local = 0;
+        for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+            const uint32_t acc = local & 1;
+            const uint64_t row0 = (tile % a.row_tiles) * kTileRows;
+            const uint64_t token = (tile / a.row_tiles) * kTileTokens + warp * 32 + lane;
+            mbar_wait(acc_full0 + 8 * acc, (local >> 1) & 1, a.fault);
+            tc_fence_after();
+            float *destination = a.y + token * a.out_stride + row0;
+#pragma unroll 1
+            for (uint32_t c = 0; c < kTileRows / 32; ++c) {
+                uint32_t v[32];
+                tmem_load32(tmem_base + ((warp * 32) << 16) + acc * kMaxTileRows + c * 32, v);
+                if (token < a.tokens) {
+                    if (row0 + c * 32 + 32 <= a.rows && ((reinterpret_cast<uintptr_t>(destination) & 15) == 0)) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            reinterpret_cast<float4 *>(destination + c * 32)[i] =
+                                make_float4(__uint_as_float(v[4 * i]) * (1.0f / kPrescale), __uint_as_float(v[4 * i + 1]) * (1.0f / kPrescale),
+                                            __uint_as_float(v[4 * i + 2]) * (1.0f / kPrescale), __uint_as_float(v[4 * i + 3]) * (1.0f / kPrescale));
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (row0 + c * 32 + i < a.rows) {
+                                destination[c * 32 + i] = __uint_as_float(v[i]) * (1.0f / kPrescale);
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(acc_empty0 + 8 * acc);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    }
+}
+
+constexpr uint32_t kGemmSharedBytes = kStages * kStageBytes + 1024;
+
+}  // namespace
+
+uint64_t gemm_scratch_bytes(uint64_t tokens, uint64_t columns)
+{
+    const uint64_t token_tiles = (tokens + kTileTokens - 1) / kTileTokens;
+    const uint64_t k_tiles = (columns + kTileK - 1) / kTileK;
+    return align_up(token_tiles * k_tiles * kTileABytes, 256);
+}
+
+int32_t launch_gemm(const syn_b200_matrix *m, const float *x, uint64_t tokens, uint64_t in_stride, float *y, uint64_t out_stride,
+                    uint32_t precision, void *scratch, uint64_t scratch_bytes, cudaStream_t stream)
+{
+    if (precision != SYN_B200_GEMM_F16) {
+        return fail(SYN_B200_INVALID_ARGUMENT, "only the fp16-operand tensor-core product is built (precision " + std::to_string(precision) + ")");
+    }
+    if (m->type != kQ4_K || m->layout != Layout::Natural) {
+        return fail(SYN_B200_UNAVAILABLE, "the tensor-core product is built for Q4_K matrices only (type " + std::to_string(m->type) + ")");
+    }
+    if (in_stride < m->columns || in_stride % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15)) {
+        return fail(SYN_B200_INVALID_ARGUMENT, "device activations must be 16-byte aligned with a stride that covers the row and is a multiple of 4 floats");
+    }
+    const uint64_t need = gemm_scratch_bytes(tokens, m->columns);
+    if (!scratch || scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255)) {
+        return fail(SYN_B200_INVALID_ARGUMENT, "tensor-core scratch must be 256-byte aligned and hold " + std::to_string(need) + " bytes");
+    }
+    GemmArgs a{};
+    a.weights = m->data;
+    a.row_bytes = m->row_bytes;
+    a.rows = m->rows;
+    a.tokens = tokens;
+    a.k_tiles = (uint32_t)(m->columns / kTileK);
+    a.token_tiles = (uint32_t)((tokens + kTileTokens - 1) / kTileTokens);
+    // 256-row tiles unless that leaves SMs without a tile and 128-row tiles would not
+    const uint64_t sms = (uint64_t)sm_count(m->device);
+    const uint64_t tiles256 = ((m->rows + 255) / 256) * a.token_tiles;
+    const int n = tiles256 >= sms ? 256 : 128;
+    a.row_tiles = (uint32_t)((m->rows + n - 1) / n);
+    a.x_tiles = static_cast<const uint8_t *>(scratch);
+    a.y = y;
+    a.out_stride = out_stride;
+    a.fault = fault_word_device();
+
+    const uint64_t chunks = (uint64_t)a.token_tiles * a.k_tiles * kTileTokens * 8;
+    uint64_t blocks = (chunks + 255) / 256;
+    if (blocks > sms * 16) {
+        blocks = sms * 16;
+    }
+    convert_activations_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, tokens, in_stride, a.k_tiles, a.token_tiles, static_cast<uint8_t *>(scratch));
+    count_launch();
+    cudaError_t error = cudaGetLastError();
+    if (error != cudaSuccess) {
+        return cuda_fail(error, "launching the activation conversion");
+    }
+    static bool configured = false;
+    if (!configured) {
+        error = cudaFuncSetAttribute(gemm_tc_kernel<DequantQ4K, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSharedBytes);
+        if (error == cudaSuccess) {
+            error = cudaFuncSetAttribute(gemm_tc_kernel<DequantQ4K, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSharedBytes);
+        }
+        if (error != cudaSuccess) {
+            return cuda_fail(error, "configuring the tensor-core kernel");
+        }
+        configured = true;
+    }
+    uint64_t ctas = (uint64_t)a.row_tiles * a.token_tiles;
+    if (ctas > sms) {
+        ctas = sms;
+    }
+    if (n == 256) {
+        gemm_tc_kernel<DequantQ4K, 256><<<(unsigned)ctas, kGemmThreads, kGemmSharedBytes, stream>>>(a);
+    } else {
+        gemm_tc_kernel<DequantQ4K, 128><<<(unsigned)ctas, kGemmThreads, kGemmSharedBytes, stream>>>(a);
+    }
+    count_launch();
+    error = cudaGetLastError();
+    if (error != cudaSuccess) {
+        return cuda_fail(error, "launching the tensor-core kernel");
+    }
+    return SYN_B200_OK;
 }
 
 }  // namespace syn

@@ -196,6 +196,7 @@ struct Q8PlanarXq8 {
     static void plane_row_bytes(uint64_t K, uint64_t, uint32_t *out) { out[0] = (uint32_t)K; out[1] = (uint32_t)(K / 16); }
     static constexpr int kMaxUpl = 2, kRows = 2, kCtasPerSm = SYN_DEFAULT_CTAS;
     static constexpr int min_ctas(int) { return 2; }
+    static constexpr int ctas_per_sm(int) { return kCtasPerSm; }
     static __device__ __forceinline__ uint64_t units(uint64_t K) { return K / 16; }
     template <class M>
     static __device__ __forceinline__ void load_act(const ActPtrT<typename M::pointer> &a, uint64_t K_, uint64_t t_, uint64_t u_, Act &out)
@@ -237,6 +238,7 @@ struct Q8NaturalXq8 {
     static constexpr int kPlanes = 1;
     static constexpr int kMaxUpl = 2, kRows = 2, kCtasPerSm = SYN_DEFAULT_CTAS;
     static constexpr int min_ctas(int) { return 2; }
+    static constexpr int ctas_per_sm(int) { return kCtasPerSm; }
     static void plane_row_bytes(uint64_t, uint64_t row_bytes, uint32_t *out) { out[0] = (uint32_t)row_bytes; }
     static __device__ __forceinline__ uint64_t units(uint64_t K) { return K / 32; }
     template <class M>
@@ -316,8 +318,12 @@ struct Q4KXq8 {
 #ifndef SYN_Q4K_ROWS
 #define SYN_Q4K_ROWS 2
 #endif
-    static constexpr int kMaxUpl = 1, kRows = SYN_Q4K_ROWS, kCtasPerSm = 1;
+#ifndef SYN_Q4K_CTAS
+#define SYN_Q4K_CTAS 1
+#endif
+    static constexpr int kMaxUpl = 1, kRows = SYN_Q4K_ROWS, kCtasPerSm = SYN_Q4K_CTAS;
     static constexpr int min_ctas(int) { return 2; }
+    static constexpr int ctas_per_sm(int) { return kCtasPerSm; }
     static void plane_row_bytes(uint64_t, uint64_t row_bytes, uint32_t *out) { out[0] = (uint32_t)row_bytes; }
     static __device__ __forceinline__ uint64_t units(uint64_t K) { return K / 128; }
     template <class M>
@@ -478,9 +484,10 @@ struct Q6KPlanarXq8 {
     using Act = Q6KAct;
     using W = Q6KW;
     static constexpr int kPlanes = 4;
-    static constexpr int kMaxUpl = 2, kRows = 2, kCtasPerSm = 1;
-    // Uncapped registers for single-warp teams (short rows), room for the next kernel's CTA otherwise.
+    static constexpr int kMaxUpl = 2, kRows = 2;
+    // Single-warp teams (short rows): uncapped registers, one CTA per SM. Wider teams: two CTAs per SM.
     static constexpr int min_ctas(int W) { return W == 1 ? 1 : 2; }
+    static constexpr int ctas_per_sm(int W) { return W == 1 ? 1 : 2; }
     static void plane_row_bytes(uint64_t K, uint64_t, uint32_t *out)
     {
         out[0] = (uint32_t)(K / 2);
@@ -524,6 +531,7 @@ struct Q6KNaturalXq8 {
     static constexpr int kPlanes = 1;
     static constexpr int kMaxUpl = 2, kRows = 2, kCtasPerSm = SYN_DEFAULT_CTAS;
     static constexpr int min_ctas(int) { return 2; }
+    static constexpr int ctas_per_sm(int) { return kCtasPerSm; }
     static void plane_row_bytes(uint64_t, uint64_t row_bytes, uint32_t *out) { out[0] = (uint32_t)row_bytes; }
     static __device__ __forceinline__ uint64_t units(uint64_t K) { return K / 64; }
     template <class M>

@@ -567,7 +567,7 @@ cudaError_t launch_pipe(const MatvecArgs &a, const PipeArgs &p, cudaStream_t str
     // shared memory): the second slot is for the next kernel of the stream, which starts copying its first stages
     // while this one is still running.
     uint64_t ctas = (a.row_count + G - 1) / G;
-    const uint64_t cap = (uint64_t)sm_count(a.matrix->device) * F::kCtasPerSm;
+    const uint64_t cap = (uint64_t)sm_count(a.matrix->device) * F::ctas_per_sm(W);
     if (ctas > cap) {
         ctas = cap;
     }

@@ -1,0 +1,59 @@
+"""GPU parity of the tensor-core prompt-run product against the reference backend's FP32 result (oracle O5).
+
+Operands are rounded to fp16 before the multiply (three roundings of 2^-12 relative RMS per term), so the gates
+are magnitude-normalised like the reference's own (native/synapse-kernels/tests/Features/CpuKernels/q8_0_tests.rs:116):
+RMS of |y - exact| / sum|term| <= 1.5e-3 / sqrt(K) (2.5e-5 at K = 3584; random rounding errors of K terms grow as
+sqrt(K) while sum|term| grows as K) and worst case <= 5x that, plus the reference's GPU-vs-reference criterion, worst
+error <= 0.2 % of the output range of the token (tests/Synapse.IntegrationTests/Features/GpuKernels/MetalBackendTests.cs:59-60).
+The share of outputs that also meet |a-b| <= 1e-5 + 1e-3*|b| is reported, not asserted.
+"""
+import numpy as np
+import pytest
+
+import synapse_b200 as sb
+from synapse_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+CASES = [  # type, rows, columns, tokens
+    (sb.Q4_K, 512, 3584, 128), (sb.Q4_K, 256, 256, 1), (sb.Q4_K, 300, 1024, 7), (sb.Q4_K, 1024, 8192, 200),
+    (sb.Q4_K, 128, 28672, 33), (sb.Q4_K, 3584, 3584, 300),
+]
+
+
+@pytest.mark.parametrize("ggml_type,rows,columns,tokens", CASES)
+def test_tensor_core_product_tracks_the_reference_backend(oracle, ggml_type, rows, columns, tokens):
+    weights = synth.matrix(ggml_type, rows, columns, seed=51)
+    x = synth.activations(tokens, columns, seed=52)
+    with sb.QuantizedMatrix(weights, ggml_type, rows, columns) as matrix:
+        y = matrix.gemm(x)
+        assert sb.library().device_faults() == 0
+    check = min(tokens, 16)  # the FP64 evaluation is the slow part; every token tile is still covered below
+    picks = np.unique(np.linspace(0, tokens - 1, check).astype(int))
+    exact, magnitude = oracle.f32_exact(ggml_type, weights, rows, columns, x[picks])
+    error = np.abs(y[picks].astype(np.float64) - exact)
+    normalised = error / magnitude
+    bound = 1.5e-3 / np.sqrt(columns)
+    rms = np.sqrt(np.mean(normalised ** 2))
+    assert rms <= bound and normalised.max() <= 5 * bound, f"normalised error rms {rms:.3e} max {normalised.max():.3e} (bound {bound:.3e})"
+    span = exact.max(axis=1, keepdims=True) - exact.min(axis=1, keepdims=True)
+    assert np.all(error <= 2e-3 * span), f"worst error is {np.max(error / span):.3e} of the output range"
+    want = oracle.f32_matmul_threads(ggml_type, weights, rows, columns, x[picks], 8)
+    inside = np.mean(np.abs(y[picks] - want) <= 1e-5 + 1e-3 * np.abs(want))
+    print(f"rows {rows} cols {columns} tokens {tokens}: normalised error rms {rms:.2e} max {normalised.max():.2e}, {inside:.1%} inside 1e-3 rel")
+    # every token tile was written
+    assert np.all(np.isfinite(y)) and np.all(np.abs(y).sum(axis=1) > 0)
+
+
+def test_tensor_core_product_respects_strides_and_leaves_gaps_alone():
+    rows, columns, tokens = 256, 512, 5
+    weights = synth.matrix(sb.Q4_K, rows, columns, seed=61)
+    x = synth.activations(tokens, columns, seed=62)
+    lib = sb.library()
+    with sb.QuantizedMatrix(weights, sb.Q4_K, rows, columns) as matrix:
+        dense = matrix.gemm(x)
+        strided = np.full((tokens, rows + 8), 12345.0, np.float32)
+        lib.check(lib.raw.syn_b200_gemm(matrix.handle, x.ctypes.data, tokens, columns, strided.ctypes.data, rows + 8, sb.GEMM_F16))
+        assert np.array_equal(strided[:, :rows], dense) and np.all(strided[:, rows:] == 12345.0)
+        assert lib.raw.syn_b200_gemm(matrix.handle, x.ctypes.data, tokens, columns, strided.ctypes.data, rows - 1, sb.GEMM_F16) == 2
+        assert lib.raw.syn_b200_gemm(matrix.handle, x.ctypes.data, tokens, columns, strided.ctypes.data, rows + 8, 7) == 2
