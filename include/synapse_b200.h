@@ -170,6 +170,22 @@ SYN_B200_API int32_t syn_b200_matvec_dev(const syn_b200_matrix *matrix, uint64_t
                             uint32_t mode, uint32_t epilogue, void *scratch, uint64_t scratch_bytes,
                             void *stream);
 
+/* Same product as syn_b200_matvec_dev in XQ8 mode, for callers that cannot allocate device memory (a decode thread
+ * that must not take the allocator's lock, a plugin with a fixed memory budget, a guest in someone else's CUDA
+ * context): the scratch for the quantised activations is a fixed array inside the library image, so the call needs
+ * nothing beyond the caller's x and y and makes no CUDA allocation. Limits: tokens * columns must not exceed
+ * syn_b200_matvec_static_capacity() (262144 values, e.g. 8 tokens of 32768), else SYN_B200_INVALID_ARGUMENT; every
+ * call on a device shares the one array (about 328 KB per device, held until the process exits), so two calls that
+ * overlap on the GPU race and must be ordered by the caller; the array keeps the last call's contents, which is
+ * harmless because each call rewrites what it reads. The first call on a device resolves the array's device address
+ * (cudaGetSymbolAddress): make that call outside any stream capture. No counterpart in the reference. */
+SYN_B200_API int32_t syn_b200_matvec_static(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
+                                            const float *x, uint64_t tokens, uint64_t in_stride, float *y,
+                                            uint64_t out_stride, uint32_t epilogue, void *stream);
+
+/* Largest tokens * columns syn_b200_matvec_static accepts. */
+SYN_B200_API uint64_t syn_b200_matvec_static_capacity(void);
+
 /* Bytes of device scratch syn_b200_gemm_dev needs for `tokens` x `columns` activations (16-bit operands). */
 SYN_B200_API uint64_t syn_b200_gemm_scratch_bytes(uint64_t tokens, uint64_t columns);
 

@@ -73,6 +73,8 @@ _EXPORTS = {
     "syn_b200_quantize_q8_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_uint64, c_void_p, c_uint64, c_void_p]),
     "syn_b200_matmul_q8_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, c_uint32, c_void_p]),
     "syn_b200_matvec_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32, c_uint32, c_void_p, c_uint64, c_void_p]),
+    "syn_b200_matvec_static": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32, c_void_p]),
+    "syn_b200_matvec_static_capacity": (c_uint64, []),
     "syn_b200_gemm_scratch_bytes": (c_uint64, [c_uint64, c_uint64]),
     "syn_b200_gemm_dev": (c_int32, [c_void_p, c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32, c_void_p, c_uint64, c_void_p]),
     "syn_b200_launch_count": (c_uint64, [c_uint32]),
@@ -330,6 +332,15 @@ class QuantizedMatrix:
         row_count = self.rows - row_start if row_count is None else row_count
         self._lib.check(self._lib.raw.syn_b200_matvec_dev(self.handle, row_start, row_count, x_ptr, tokens, in_stride, y_ptr,
                                                          out_stride, mode, epilogue, scratch_ptr, scratch_bytes, stream))
+
+    def matvec_static(self, x_ptr: int, tokens: int, in_stride: int, y_ptr: int, out_stride: int, epilogue: int = EPILOGUE_STORE,
+                      stream: int = 0, row_start: int = 0, row_count: int | None = None) -> None:
+        """The quantised-activation product for callers that cannot allocate device memory: the scratch is a fixed
+        array inside the library (at most ``syn_b200_matvec_static_capacity()`` activation values per call; calls that
+        overlap on the GPU race on it)."""
+        row_count = self.rows - row_start if row_count is None else row_count
+        self._lib.check(self._lib.raw.syn_b200_matvec_static(self.handle, row_start, row_count, x_ptr, tokens, in_stride, y_ptr, out_stride,
+                                                            epilogue, stream))
 
     def matmul_q8_device(self, scratch_ptr: int, tokens: int, y_ptr: int, out_stride: int, epilogue: int = EPILOGUE_STORE,
                          stream: int = 0, row_start: int = 0, row_count: int | None = None) -> None:
