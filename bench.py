@@ -29,7 +29,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-from synapse_b200 import synth  # noqa: E402
+from synapse_b200 import sharding, synth  # noqa: E402
 
 METRIC = "k-quant decode matvec weight bandwidth (Qwen2.5-7B Q4_K_M set, batch 1)"
 UNIT = "GB/s"
@@ -234,12 +234,11 @@ def main():
     matrices = []
     total_bytes = 0
     for index, (name, ggml_type, rows, columns) in enumerate(specs):
-        if rows % world:
-            raise SystemExit(f"{name}: {rows} rows do not split over {world} ranks")
-        shard_rows = rows // world
+        _, shard_rows = sharding.shard_rows(rows, world, rank)
+        offset, count = sharding.shard_bytes(ggml_type, rows, columns, world, rank)
         row_bytes = synth.row_bytes(ggml_type, columns)
         blocks = synth.matrix(ggml_type, rows, columns, seed=100 + index, name=name)
-        shard = blocks[rank * shard_rows * row_bytes:(rank + 1) * shard_rows * row_bytes]
+        shard = blocks[offset:offset + count]
         matrices.append((name, ggml_type, rows, columns, shard_rows, sb.QuantizedMatrix(shard, ggml_type, shard_rows, columns)))
         total_bytes += rows * row_bytes
         del blocks, shard
@@ -267,7 +266,7 @@ def main():
             matrix.matmul_q8_device(aligned(scratch[columns]), 1, target.data_ptr(), shard_rows, stream=stream.cuda_stream)
         if world > 1:
             with torch.cuda.stream(stream):
-                dist.all_gather_into_tensor(out_full[(name.split(".")[-1], rows)], target)
+                sharding.gather_outputs(target, out_full[(name.split(".")[-1], rows)])
 
     def quantize(columns, stream):
         if args.quantize == "shared":
@@ -276,7 +275,7 @@ def main():
 
     def parallel(entries, main):
         """Independent products of the same input: the first on the main stream, the others on side streams."""
-        if args.serial or len(entries) == 1:
+        if args.serial or world > 1 or len(entries) == 1:
             for entry in entries:
                 product(entry, main)
             return
@@ -316,11 +315,19 @@ def main():
         step(stream)
     torch.cuda.synchronize()
     launches_per_step = lib.launch_count(reset=True)
-    use_graph = not args.no_graph and world == 1
+    use_graph = not args.no_graph
     if use_graph:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            step(torch.cuda.current_stream())
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step(torch.cuda.current_stream())
+        except Exception as error:  # a collective that cannot be captured: replay from the host instead
+            if world == 1:
+                raise
+            sys.stderr.write(f"rank {rank}: graph capture failed ({error}); launching from the host\n")
+            graph = None
+            use_graph = False
+            torch.cuda.synchronize()
 
     def run_step():
         if graph is not None:
