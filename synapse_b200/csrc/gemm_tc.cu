@@ -168,14 +168,37 @@ __device__ __forceinline__ void q4k_scale_min(uint32_t w0, uint32_t w1, uint32_t
     }
 }
 
+struct GemmArgs;
+
+// 16 bytes through 128-bit loads when the address is 16-byte aligned by construction, through eight 16-bit loads for
+// the file layouts whose blocks are only 2-byte aligned.
+template <bool ALIGNED>
+__device__ __forceinline__ uint4 load16(const uint8_t *p)
+{
+    if (ALIGNED) {
+        return __ldg(reinterpret_cast<const uint4 *>(p));
+    }
+    uint32_t h[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        h[i] = __ldg(reinterpret_cast<const unsigned short *>(p + 2 * i));
+    }
+    return make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+}
+__device__ __forceinline__ uint32_t load_u16(const uint8_t *p) { return __ldg(reinterpret_cast<const unsigned short *>(p)); }
+
 struct DequantQ4K {
     struct Raw {
         uint4 header, q0, q1;
     };
-    // `row` points at the row's first super-block; k tile `kt` is chunk kt%4 of super-block kt/4.
-    static __device__ __forceinline__ void load(const uint8_t *row, uint32_t kt, Raw &raw)
+    struct Row {
+        const uint8_t *base;  // the row's first super-block
+    };
+    static __device__ __forceinline__ Row row_of(const GemmArgs &a, uint64_t row);
+    // k tile `kt` is chunk kt%4 of super-block kt/4.
+    static __device__ __forceinline__ void load(const Row &r, uint32_t kt, Raw &raw)
     {
-        const uint8_t *block = row + (uint64_t)(kt >> 2) * 144;
+        const uint8_t *block = r.base + (uint64_t)(kt >> 2) * 144;
         raw.header = __ldg(reinterpret_cast<const uint4 *>(block));
         raw.q0 = __ldg(reinterpret_cast<const uint4 *>(block + 16 + (kt & 3) * 32));
         raw.q1 = __ldg(reinterpret_cast<const uint4 *>(block + 32 + (kt & 3) * 32));
@@ -207,13 +230,136 @@ struct DequantQ4K {
     }
 };
 
+// Q6_K: k tile kt is quarter kt%4 of super-block kt/4: half h = (kt%4)/2 of the block, nibble g = kt%2 of its 64 ql
+// bytes; tile values 0..31 pair ql[l] with bits (4g, 4g+1) of qh[l], values 32..63 pair ql[l+32] with bits (4g+2, 4g+3)
+// (GgufKQuantBlocks.cs:155-177). value = d * sc[8h + 4g + i/16] * (q - 32).
+template <bool PLANAR>
+struct DequantQ6K {
+    struct Raw {
+        uint4 ql[4], qh[2];
+        uint32_t scales;  // the four int8 scales of this k tile
+        uint32_t d;       // fp16 bits
+    };
+    struct Row {
+        const uint8_t *ql, *qh, *sc, *d;  // planar: per-plane row starts; file layout: all inside one block stream
+    };
+    static __device__ __forceinline__ Row row_of(const GemmArgs &a, uint64_t row);
+    static __device__ __forceinline__ void load(const Row &r, uint32_t kt, Raw &raw)
+    {
+        const uint32_t sb = kt >> 2, h = (kt >> 1) & 1, g = kt & 1;
+        const uint8_t *ql, *qh, *sc, *d;
+        if (PLANAR) {
+            ql = r.ql + (uint64_t)sb * 128 + h * 64;
+            qh = r.qh + (uint64_t)sb * 64 + h * 32;
+            sc = r.sc + (uint64_t)sb * 16 + h * 8 + g * 4;
+            d = r.d + (uint64_t)sb * 2;
+        } else {
+            const uint8_t *block = r.ql + (uint64_t)sb * 210;
+            ql = block + h * 64;
+            qh = block + 128 + h * 32;
+            sc = block + 192 + h * 8 + g * 4;
+            d = block + 208;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            raw.ql[i] = load16<PLANAR>(ql + 16 * i);
+        }
+        raw.qh[0] = load16<PLANAR>(qh);
+        raw.qh[1] = load16<PLANAR>(qh + 16);
+        raw.scales = PLANAR ? __ldg(reinterpret_cast<const uint32_t *>(sc)) : (load_u16(sc) | (load_u16(sc + 2) << 16));
+        raw.d = load_u16(d);
+    }
+    // part 0: tile values 0..31 (chunks 0..3), part 1: values 32..63 (chunks 4..7)
+    static __device__ __forceinline__ void expand(const Raw &raw, uint32_t kt, uint32_t part, uint4 (&out)[4])
+    {
+        const uint32_t g = kt & 1;
+        const float d = __half2float(__ushort_as_half((unsigned short)raw.d)) * kPrescale;
+        const __half2 k1056 = __float2half2_rn(1056.0f);  // 1024 from the exponent trick + the code offset 32
+        const uint32_t ql[8] = {part ? raw.ql[2].x : raw.ql[0].x, part ? raw.ql[2].y : raw.ql[0].y, part ? raw.ql[2].z : raw.ql[0].z,
+                                part ? raw.ql[2].w : raw.ql[0].w, part ? raw.ql[3].x : raw.ql[1].x, part ? raw.ql[3].y : raw.ql[1].y,
+                                part ? raw.ql[3].z : raw.ql[1].z, part ? raw.ql[3].w : raw.ql[1].w};
+        const uint32_t qh[8] = {raw.qh[0].x, raw.qh[0].y, raw.qh[0].z, raw.qh[0].w, raw.qh[1].x, raw.qh[1].y, raw.qh[1].z, raw.qh[1].w};
+        const uint32_t high_shift = 4 * g + 2 * part;
+        uint32_t v[16];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int scale = (int)(signed char)((raw.scales >> (8 * (2 * part + j / 4))) & 0xff);
+            const __half2 a = __float2half2_rn(d * (float)scale);
+            const uint32_t nibbles = (g ? (ql[j] >> 4) : ql[j]) & 0x0F0F0F0Fu;
+            const uint32_t codes = nibbles | (((qh[j] >> high_shift) & 0x03030303u) << 4);
+            v[2 * j] = h2_bits(__hmul2(__hsub2(bits_h2((codes & 0x00FF00FFu) | 0x64006400u), k1056), a));
+            v[2 * j + 1] = h2_bits(__hmul2(__hsub2(bits_h2(((codes >> 8) & 0x00FF00FFu) | 0x64006400u), k1056), a));
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            out[c] = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+        }
+    }
+};
+
+// Q8_0: k tile kt is blocks 2kt and 2kt+1 of the row; value = d * code (GgufLegacyBlocks.cs:85-92).
+template <bool PLANAR>
+struct DequantQ8 {
+    struct Raw {
+        uint4 codes[4];
+        uint32_t d0, d1;  // fp16 bits of the two block scales
+    };
+    struct Row {
+        const uint8_t *codes, *scales;
+    };
+    static __device__ __forceinline__ Row row_of(const GemmArgs &a, uint64_t row);
+    static __device__ __forceinline__ void load(const Row &r, uint32_t kt, Raw &raw)
+    {
+        if (PLANAR) {
+            const uint8_t *codes = r.codes + (uint64_t)kt * 64;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                raw.codes[i] = load16<true>(codes + 16 * i);
+            }
+            const uint32_t scales = __ldg(reinterpret_cast<const uint32_t *>(r.scales + (uint64_t)kt * 4));
+            raw.d0 = scales & 0xffff;
+            raw.d1 = scales >> 16;
+        } else {
+            const uint8_t *block = r.codes + (uint64_t)kt * 68;
+            raw.d0 = load_u16(block);
+            raw.codes[0] = load16<false>(block + 2);
+            raw.codes[1] = load16<false>(block + 18);
+            raw.d1 = load_u16(block + 34);
+            raw.codes[2] = load16<false>(block + 36);
+            raw.codes[3] = load16<false>(block + 52);
+        }
+    }
+    // part 0: the first block (chunks 0..3), part 1: the second (chunks 4..7)
+    static __device__ __forceinline__ void expand(const Raw &raw, uint32_t, uint32_t part, uint4 (&out)[4])
+    {
+        const float d = __half2float(__ushort_as_half((unsigned short)(part ? raw.d1 : raw.d0))) * kPrescale;
+        const __half2 a = __float2half2_rn(d);
+        const __half2 k1152 = __float2half2_rn(1152.0f);  // 1024 from the exponent trick + the 128 that makes the byte unsigned
+        const uint4 lo = part ? raw.codes[2] : raw.codes[0], hi = part ? raw.codes[3] : raw.codes[1];
+        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        uint32_t v[16];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t biased = words[j] ^ 0x80808080u;
+            v[2 * j] = h2_bits(__hmul2(__hsub2(bits_h2((biased & 0x00FF00FFu) | 0x64006400u), k1152), a));
+            v[2 * j + 1] = h2_bits(__hmul2(__hsub2(bits_h2(((biased >> 8) & 0x00FF00FFu) | 0x64006400u), k1152), a));
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            out[c] = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+        }
+    }
+};
+
 // ------------------------------------------------------------------------------------------------------
 // The GEMM kernel
 // ------------------------------------------------------------------------------------------------------
 
 struct GemmArgs {
-    const uint8_t *weights;  // file-layout rows
-    uint64_t row_bytes;
+    const uint8_t *weights;  // file-layout rows, or plane 0 of the planar layout
+    const uint8_t *plane1, *plane2, *plane3;
+    uint64_t row_bytes;      // of the file layout
+    uint64_t columns;
     uint64_t rows, tokens;
     uint32_t k_tiles, row_tiles, token_tiles;
     const uint8_t *x_tiles;  // converted activations
@@ -221,6 +367,25 @@ struct GemmArgs {
     uint64_t out_stride;
     uint32_t *fault;
 };
+
+__device__ __forceinline__ DequantQ4K::Row DequantQ4K::row_of(const GemmArgs &a, uint64_t row) { return Row{a.weights + row * a.row_bytes}; }
+template <bool PLANAR>
+__device__ __forceinline__ typename DequantQ6K<PLANAR>::Row DequantQ6K<PLANAR>::row_of(const GemmArgs &a, uint64_t row)
+{
+    if (PLANAR) {
+        return Row{a.weights + row * (a.columns / 2), a.plane1 + row * (a.columns / 4), a.plane2 + row * (a.columns / 16),
+                   a.plane3 + row * (a.columns / 128)};
+    }
+    return Row{a.weights + row * a.row_bytes, nullptr, nullptr, nullptr};
+}
+template <bool PLANAR>
+__device__ __forceinline__ typename DequantQ8<PLANAR>::Row DequantQ8<PLANAR>::row_of(const GemmArgs &a, uint64_t row)
+{
+    if (PLANAR) {
+        return Row{a.weights + row * a.columns, a.plane1 + row * (a.columns / 16)};
+    }
+    return Row{a.weights + row * a.row_bytes, nullptr};
+}
 
 template <class Dequant, int N>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
@@ -315,9 +480,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
         uint32_t s = 0, round = 0;
         typename Dequant::Raw next;
         uint64_t tile = blockIdx.x;
-        const uint8_t *row = nullptr;
+        typename Dequant::Row row{};
         if (tile < tiles) {
-            row = a.weights + min((tile % a.row_tiles) * kTileRows + r, a.rows - 1) * a.row_bytes;
+            row = Dequant::row_of(a, min((tile % a.row_tiles) * kTileRows + r, a.rows - 1));
             Dequant::load(row, 0, next);
         }
         for (; tile < tiles; tile += gridDim.x) {
@@ -326,7 +491,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                 if (kt + 1 < a.k_tiles) {
                     Dequant::load(row, kt + 1, next);
                 } else if (tile + gridDim.x < tiles) {
-                    row = a.weights + min(((tile + gridDim.x) % a.row_tiles) * kTileRows + r, a.rows - 1) * a.row_bytes;
+                    row = Dequant::row_of(a, min(((tile + gridDim.x) % a.row_tiles) * kTileRows + r, a.rows - 1));
                     Dequant::load(row, 0, next);
                 }
                 uint4 v[2][4];
@@ -410,6 +575,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
 
 constexpr uint32_t kGemmSharedBytes = kStages * kStageBytes + 1024;
 
+template <class Dequant>
+cudaError_t run_gemm(const GemmArgs &a, int n, uint64_t ctas, cudaStream_t stream)
+{
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t error = cudaFuncSetAttribute(gemm_tc_kernel<Dequant, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSharedBytes);
+        if (error == cudaSuccess) {
+            error = cudaFuncSetAttribute(gemm_tc_kernel<Dequant, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSharedBytes);
+        }
+        if (error != cudaSuccess) {
+            return error;
+        }
+        configured = true;
+    }
+    if (n == 256) {
+        gemm_tc_kernel<Dequant, 256><<<(unsigned)ctas, kGemmThreads, kGemmSharedBytes, stream>>>(a);
+    } else {
+        gemm_tc_kernel<Dequant, 128><<<(unsigned)ctas, kGemmThreads, kGemmSharedBytes, stream>>>(a);
+    }
+    return cudaGetLastError();
+}
+
 }  // namespace
 
 uint64_t gemm_scratch_bytes(uint64_t tokens, uint64_t columns)
@@ -425,19 +612,24 @@ int32_t launch_gemm(const syn_b200_matrix *m, const float *x, uint64_t tokens, u
     if (precision != SYN_B200_GEMM_F16) {
         return fail(SYN_B200_INVALID_ARGUMENT, "only the fp16-operand tensor-core product is built (precision " + std::to_string(precision) + ")");
     }
-    if (m->type != kQ4_K || m->layout != Layout::Natural) {
-        return fail(SYN_B200_UNAVAILABLE, "the tensor-core product is built for Q4_K matrices only (type " + std::to_string(m->type) + ")");
-    }
     if (in_stride < m->columns || in_stride % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15)) {
         return fail(SYN_B200_INVALID_ARGUMENT, "device activations must be 16-byte aligned with a stride that covers the row and is a multiple of 4 floats");
+    }
+    if (m->columns % kTileK != 0) {
+        return fail(SYN_B200_UNAVAILABLE, "the tensor-core product needs a row length that is a multiple of 64; this matrix has " + std::to_string(m->columns));
     }
     const uint64_t need = gemm_scratch_bytes(tokens, m->columns);
     if (!scratch || scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255)) {
         return fail(SYN_B200_INVALID_ARGUMENT, "tensor-core scratch must be 256-byte aligned and hold " + std::to_string(need) + " bytes");
     }
     GemmArgs a{};
-    a.weights = m->data;
+    const bool planar = m->layout == Layout::Planar;
+    a.weights = m->data + (planar ? m->planes.p0 : 0);
+    a.plane1 = m->data + m->planes.p1;
+    a.plane2 = m->data + m->planes.p2;
+    a.plane3 = m->data + m->planes.p3;
     a.row_bytes = m->row_bytes;
+    a.columns = m->columns;
     a.rows = m->rows;
     a.tokens = tokens;
     a.k_tiles = (uint32_t)(m->columns / kTileK);
@@ -463,31 +655,21 @@ int32_t launch_gemm(const syn_b200_matrix *m, const float *x, uint64_t tokens, u
     if (error != cudaSuccess) {
         return cuda_fail(error, "launching the activation conversion");
     }
-    static bool configured = false;
-    if (!configured) {
-        error = cudaFuncSetAttribute(gemm_tc_kernel<DequantQ4K, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSharedBytes);
-        if (error == cudaSuccess) {
-            error = cudaFuncSetAttribute(gemm_tc_kernel<DequantQ4K, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSharedBytes);
-        }
-        if (error != cudaSuccess) {
-            return cuda_fail(error, "configuring the tensor-core kernel");
-        }
-        configured = true;
-    }
     uint64_t ctas = (uint64_t)a.row_tiles * a.token_tiles;
     if (ctas > sms) {
         ctas = sms;
     }
-    if (n == 256) {
-        gemm_tc_kernel<DequantQ4K, 256><<<(unsigned)ctas, kGemmThreads, kGemmSharedBytes, stream>>>(a);
+    if (m->type == kQ4_K) {
+        error = run_gemm<DequantQ4K>(a, n, ctas, stream);
+    } else if (m->type == kQ6_K) {
+        error = planar ? run_gemm<DequantQ6K<true>>(a, n, ctas, stream) : run_gemm<DequantQ6K<false>>(a, n, ctas, stream);
     } else {
-        gemm_tc_kernel<DequantQ4K, 128><<<(unsigned)ctas, kGemmThreads, kGemmSharedBytes, stream>>>(a);
+        error = planar ? run_gemm<DequantQ8<true>>(a, n, ctas, stream) : run_gemm<DequantQ8<false>>(a, n, ctas, stream);
+    }
+    if (error != cudaSuccess) {
+        return cuda_fail(error, "configuring or launching the tensor-core kernel");
     }
     count_launch();
-    error = cudaGetLastError();
-    if (error != cudaSuccess) {
-        return cuda_fail(error, "launching the tensor-core kernel");
-    }
     return SYN_B200_OK;
 }
 

@@ -18,14 +18,19 @@ pytestmark = pytest.mark.gpu
 CASES = [  # type, rows, columns, tokens
     (sb.Q4_K, 512, 3584, 128), (sb.Q4_K, 256, 256, 1), (sb.Q4_K, 300, 1024, 7), (sb.Q4_K, 1024, 8192, 200),
     (sb.Q4_K, 128, 28672, 33), (sb.Q4_K, 3584, 3584, 300),
+    (sb.Q6_K, 512, 3584, 128), (sb.Q6_K, 300, 768, 5), (sb.Q6_K, 384, 18944, 140), (sb.Q6_K, 20000, 256, 130),
+    (sb.Q8_0, 4864, 896, 64), (sb.Q8_0, 100, 64, 3), (sb.Q8_0, 896, 4864, 260),
 ]
 
 
 @pytest.mark.parametrize("ggml_type,rows,columns,tokens", CASES)
-def test_tensor_core_product_tracks_the_reference_backend(oracle, ggml_type, rows, columns, tokens):
+@pytest.mark.parametrize("repack", [True, False])
+def test_tensor_core_product_tracks_the_reference_backend(oracle, ggml_type, rows, columns, tokens, repack):
+    if not repack and (ggml_type == sb.Q4_K or rows * columns > 4_000_000):
+        pytest.skip("Q4_K has one layout; the file-layout variants are covered on the smaller shapes")
     weights = synth.matrix(ggml_type, rows, columns, seed=51)
     x = synth.activations(tokens, columns, seed=52)
-    with sb.QuantizedMatrix(weights, ggml_type, rows, columns) as matrix:
+    with sb.QuantizedMatrix(weights, ggml_type, rows, columns, repack=repack) as matrix:
         y = matrix.gemm(x)
         assert sb.library().device_faults() == 0
     check = min(tokens, 16)  # the FP64 evaluation is the slow part; every token tile is still covered below
@@ -57,3 +62,7 @@ def test_tensor_core_product_respects_strides_and_leaves_gaps_alone():
         assert np.array_equal(strided[:, :rows], dense) and np.all(strided[:, rows:] == 12345.0)
         assert lib.raw.syn_b200_gemm(matrix.handle, x.ctypes.data, tokens, columns, strided.ctypes.data, rows - 1, sb.GEMM_F16) == 2
         assert lib.raw.syn_b200_gemm(matrix.handle, x.ctypes.data, tokens, columns, strided.ctypes.data, rows + 8, 7) == 2
+    ragged = synth.matrix(sb.Q8_0, 8, 96, seed=63)
+    with sb.QuantizedMatrix(ragged, sb.Q8_0, 8, 96) as matrix:
+        with pytest.raises(sb.BackendUnavailableError, match="multiple of 64"):
+            matrix.gemm(synth.activations(2, 96, seed=64))
