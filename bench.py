@@ -448,7 +448,18 @@ def main():
                 "gpu_launches": int(launches_per_step * args.steps)}
         print(json.dumps(line))
     if world > 1:
+        # Captured collectives keep the communicator busy at teardown on some NCCL builds: release the graphs first and
+        # do not let a stuck destroy hold the job (the result line is already printed).
+        sys.stdout.flush()
+        graph = None
+        roofline_graph = None
+        torch.cuda.synchronize()
+        watchdog = threading.Timer(20.0, lambda: os._exit(0))
+        watchdog.daemon = True
+        watchdog.start()
+        dist.barrier()
         dist.destroy_process_group()
+        watchdog.cancel()
 
 
 if __name__ == "__main__":
