@@ -9,8 +9,9 @@
 //   warp  12    loader    bulk-copies the A operand tile (activations, converted and pre-swizzled by a pre-pass)
 //   warp  13    MMA       one lane issues tcgen05.mma (M=128 tokens, N=256 or 128 weight rows, K=16) and commits
 // Tokens are the MMA's M so that the expensive operand to move, the 16-bit activations, is read once per 256 weight
-// rows. The accumulator (128 lanes x 256 columns FP32) is double-buffered in the 512 columns of tensor memory, so
-// the epilogue of one tile overlaps the MMAs of the next. Operands are fp16 (weights carry a 2^8 prescale so that
+// rows, and with two token tiles per CTA tile a weight tile is dequantised once per 256 tokens. The 512 columns of
+// tensor memory hold two 128 x 256 FP32 accumulators: the two token tiles of a tile, or (one token tile) two
+// buffers so that the epilogue of one tile overlaps the MMAs of the next. Operands are fp16 (weights carry a 2^8 prescale so that
 // small block scales stay out of the fp16 subnormal range; the epilogue removes it exactly).
 //
 // Every mbarrier wait is bounded: when one gives up the kernel bumps the host-mapped fault word and carries on to
@@ -26,10 +27,14 @@ namespace {
 constexpr int kTileTokens = 128;  // MMA M
 constexpr int kMaxTileRows = 256; // MMA N: 256, or 128 when that is needed to give every SM a tile
 constexpr int kTileK = 64;        // one 128-byte swizzle row of fp16
-constexpr int kStages = 4;
+constexpr int kMaxStages = 4;
 constexpr uint32_t kTileABytes = kTileTokens * kTileK * 2;     // 16 KB
 constexpr uint32_t kTileBBytes = kMaxTileRows * kTileK * 2;    // 32 KB
-constexpr uint32_t kStageBytes = kTileABytes + kTileBBytes;
+// A CTA tile covers TT token tiles (TT activation tiles per stage, TT accumulators) against one weight tile, so a
+// weight tile is dequantised once per TT * 128 tokens. TT = 1: four 48 KB stages, two accumulator buffers.
+// TT = 2: three 64 KB stages, both accumulators in use at once.
+constexpr uint32_t stage_bytes(int tt) { return tt * kTileABytes + kTileBBytes; }
+constexpr uint32_t stage_count(int tt) { return tt == 1 ? 4 : 3; }
 constexpr uint32_t kDequantWarps = 8;
 constexpr uint32_t kLoaderWarp = 4 + kDequantWarps, kMmaWarp = kLoaderWarp + 1;
 constexpr uint32_t kGemmThreads = (kMmaWarp + 1) * 32;
@@ -387,21 +392,24 @@ __device__ __forceinline__ typename DequantQ8<PLANAR>::Row DequantQ8<PLANAR>::ro
     return Row{a.weights + row * a.row_bytes, nullptr};
 }
 
-template <class Dequant, int N>
+template <class Dequant, int N, int TT>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
 {
     static_assert(N == 128 || N == 256, "the weight-row tile is 128 or 256");
+    static_assert(TT == 1 || TT == 2, "one or two token tiles per CTA tile");
     constexpr uint32_t kTileRows = N;
+    constexpr uint32_t kStages = stage_count(TT), kStageBytes = stage_bytes(TT);
+    constexpr uint32_t kBuffers = TT == 1 ? 2 : 1;  // accumulator sets that can be in flight
     extern __shared__ __align__(1024) uint8_t shared_raw[];
     // the dynamic window is only guaranteed 16-byte alignment; the swizzle needs 1024
     uint8_t *stages = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(shared_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) uint64_t barriers[2 * kStages + 4];  // full[s], empty[s], acc_full[2], acc_empty[2]
+    __shared__ __align__(8) uint64_t barriers[2 * kMaxStages + 4];  // full[s], empty[s], acc_full[2], acc_empty[2]
     __shared__ uint32_t tmem_slot;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t full0 = smem_u32(&barriers[0]), empty0 = smem_u32(&barriers[kStages]);
-    const uint32_t acc_full0 = smem_u32(&barriers[2 * kStages]), acc_empty0 = smem_u32(&barriers[2 * kStages + 2]);
+    const uint32_t full0 = smem_u32(&barriers[0]), empty0 = smem_u32(&barriers[kMaxStages]);
+    const uint32_t acc_full0 = smem_u32(&barriers[2 * kMaxStages]), acc_empty0 = smem_u32(&barriers[2 * kMaxStages + 2]);
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (uint32_t s = 0; s < kStages; ++s) {
             mbar_init(full0 + 8 * s, 1 + kDequantWarps);  // the loader's expect_tx arrival + one arrival per dequant warp
             mbar_init(empty0 + 8 * s, 1);     // tcgen05.commit
         }
@@ -419,20 +427,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
-    const uint64_t tiles = (uint64_t)a.row_tiles * a.token_tiles;
+    const uint32_t token_groups = (a.token_tiles + TT - 1) / TT;  // CTA tiles along the tokens
+    const uint64_t tiles = (uint64_t)a.row_tiles * token_groups;
 
     if (warp == kLoaderWarp) {
         // ---- loader: the activation tile of every (tile, k step) --------------------------------------
         if (lane == 0) {
             uint32_t s = 0, round = 0;
             for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-                const uint64_t tt = tile / a.row_tiles;
+                const uint64_t tt0 = (tile / a.row_tiles) * TT;
+                const uint32_t live = min((uint32_t)TT, a.token_tiles - (uint32_t)tt0);  // token tiles that exist
                 for (uint32_t kt = 0; kt < a.k_tiles; ++kt) {
                     if (round > 0) {
                         mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.fault);
                     }
-                    mbar_expect_tx(full0 + 8 * s, kTileABytes);
-                    bulk_copy(smem_u32(stages + s * kStageBytes), a.x_tiles + (tt * a.k_tiles + kt) * kTileABytes, kTileABytes, full0 + 8 * s);
+                    mbar_expect_tx(full0 + 8 * s, live * kTileABytes);
+                    for (uint32_t i = 0; i < live; ++i) {
+                        bulk_copy(smem_u32(stages + s * kStageBytes + i * kTileABytes), a.x_tiles + ((tt0 + i) * a.k_tiles + kt) * kTileABytes,
+                                  kTileABytes, full0 + 8 * s);
+                    }
                     if (++s == kStages) {
                         s = 0;
                         ++round;
@@ -445,21 +458,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
         if (lane == 0) {
             uint32_t s = 0, phase = 0, local = 0;
             for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
-                const uint32_t acc = local & 1;
-                if (local >= 2) {
-                    mbar_wait(acc_empty0 + 8 * acc, ((local >> 1) - 1) & 1, a.fault);
+                const uint32_t acc = local % kBuffers, use = local / kBuffers;
+                const uint32_t live = min((uint32_t)TT, a.token_tiles - (uint32_t)((tile / a.row_tiles) * TT));
+                if (use >= 1) {
+                    mbar_wait(acc_empty0 + 8 * acc, (use - 1) & 1, a.fault);
                 }
                 tc_fence_after();
-                const uint32_t tmem_d = tmem_base + acc * kMaxTileRows;
+                const uint32_t tmem_d = tmem_base + acc * kMaxTileRows;  // token tile i of a TT = 2 tile sits at + i * 256 columns
                 for (uint32_t kt = 0; kt < a.k_tiles; ++kt) {
                     mbar_wait(full0 + 8 * s, phase, a.fault);
                     tc_fence_after();
                     const uint32_t stage = smem_u32(stages + s * kStageBytes);
-                    const uint64_t desc_a = smem_desc(stage), desc_b = smem_desc(stage + kTileABytes);
+                    const uint64_t desc_b = smem_desc(stage + TT * kTileABytes);
 #pragma unroll
-                    for (uint32_t k = 0; k < kTileK / 16; ++k) {
-                        // 16 fp16 = 32 bytes further along the swizzled row: +2 in the descriptor's 16-byte units
-                        umma_f16(tmem_d, desc_a + 2 * k, desc_b + 2 * k, instr_desc(N), (kt | k) != 0 ? 1u : 0u);
+                    for (uint32_t i = 0; i < (uint32_t)TT; ++i) {
+                        if (i < live) {
+                            const uint64_t desc_a = smem_desc(stage + i * kTileABytes);
+#pragma unroll
+                            for (uint32_t k = 0; k < kTileK / 16; ++k) {
+                                // 16 fp16 = 32 bytes further along the swizzled row: +2 in the descriptor's 16-byte units
+                                umma_f16(tmem_d + i * kMaxTileRows, desc_a + 2 * k, desc_b + 2 * k, instr_desc(N), (kt | k) != 0 ? 1u : 0u);
+                            }
+                        }
                     }
                     umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
                     if (++s == kStages) {
@@ -504,7 +524,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                 if (round > 0) {
                     mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.fault);
                 }
-                uint8_t *tile_b = stages + s * kStageBytes + kTileABytes;
+                uint8_t *tile_b = stages + s * kStageBytes + TT * kTileABytes;
 #pragma unroll
                 for (uint32_t c = 0; c < 4; ++c) {
                     if (kParts == 1) {
@@ -530,29 +550,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
         // ---- epilogue warps: warp q owns accumulator lanes (tokens) 32q .. 32q+31 ----------------------
         uint32_t local = 0;
         for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
-            const uint32_t acc = local & 1;
+            const uint32_t acc = local % kBuffers, use = local / kBuffers;
             const uint64_t row0 = (tile % a.row_tiles) * kTileRows;
-            const uint64_t token = (tile / a.row_tiles) * kTileTokens + warp * 32 + lane;
-            mbar_wait(acc_full0 + 8 * acc, (local >> 1) & 1, a.fault);
+            const uint64_t tt0 = (tile / a.row_tiles) * TT;
+            const uint32_t live = min((uint32_t)TT, a.token_tiles - (uint32_t)tt0);
+            mbar_wait(acc_full0 + 8 * acc, use & 1, a.fault);
             tc_fence_after();
-            float *destination = a.y + token * a.out_stride + row0;
+            for (uint32_t i = 0; i < live; ++i) {
+                const uint64_t token = (tt0 + i) * kTileTokens + warp * 32 + lane;
+                float *destination = a.y + token * a.out_stride + row0;
 #pragma unroll 1
-            for (uint32_t c = 0; c < kTileRows / 32; ++c) {
-                uint32_t v[32];
-                tmem_load32(tmem_base + ((warp * 32) << 16) + acc * kMaxTileRows + c * 32, v);
-                if (token < a.tokens) {
-                    if (row0 + c * 32 + 32 <= a.rows && ((reinterpret_cast<uintptr_t>(destination) & 15) == 0)) {
+                for (uint32_t c = 0; c < kTileRows / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_load32(tmem_base + ((warp * 32) << 16) + (acc + i) * kMaxTileRows + c * 32, v);
+                    if (token < a.tokens) {
+                        if (row0 + c * 32 + 32 <= a.rows && ((reinterpret_cast<uintptr_t>(destination) & 15) == 0)) {
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            reinterpret_cast<float4 *>(destination + c * 32)[i] =
-                                make_float4(__uint_as_float(v[4 * i]) * (1.0f / kPrescale), __uint_as_float(v[4 * i + 1]) * (1.0f / kPrescale),
-                                            __uint_as_float(v[4 * i + 2]) * (1.0f / kPrescale), __uint_as_float(v[4 * i + 3]) * (1.0f / kPrescale));
-                        }
-                    } else {
+                            for (int j = 0; j < 8; ++j) {
+                                reinterpret_cast<float4 *>(destination + c * 32)[j] =
+                                    make_float4(__uint_as_float(v[4 * j]) * (1.0f / kPrescale), __uint_as_float(v[4 * j + 1]) * (1.0f / kPrescale),
+                                                __uint_as_float(v[4 * j + 2]) * (1.0f / kPrescale), __uint_as_float(v[4 * j + 3]) * (1.0f / kPrescale));
+                            }
+                        } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            if (row0 + c * 32 + i < a.rows) {
-                                destination[c * 32 + i] = __uint_as_float(v[i]) * (1.0f / kPrescale);
+                            for (int j = 0; j < 32; ++j) {
+                                if (row0 + c * 32 + j < a.rows) {
+                                    destination[c * 32 + j] = __uint_as_float(v[j]) * (1.0f / kPrescale);
+                                }
                             }
                         }
                     }
@@ -573,28 +597,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
     }
 }
 
-constexpr uint32_t kGemmSharedBytes = kStages * kStageBytes + 1024;
+constexpr uint32_t kGemmSharedBytes = 4 * stage_bytes(1) + 1024;  // = 3 * stage_bytes(2) + 1024
+static_assert(4 * stage_bytes(1) == 3 * stage_bytes(2), "both tile shapes use the same shared-memory budget");
 
-template <class Dequant>
-cudaError_t run_gemm(const GemmArgs &a, int n, uint64_t ctas, cudaStream_t stream)
+template <class Dequant, int N, int TT>
+cudaError_t run_gemm_shape(const GemmArgs &a, uint64_t ctas, cudaStream_t stream)
 {
     static bool configured = false;
     if (!configured) {
-        cudaError_t error = cudaFuncSetAttribute(gemm_tc_kernel<Dequant, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSharedBytes);
-        if (error == cudaSuccess) {
-            error = cudaFuncSetAttribute(gemm_tc_kernel<Dequant, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSharedBytes);
-        }
+        cudaError_t error = cudaFuncSetAttribute(gemm_tc_kernel<Dequant, N, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSharedBytes);
         if (error != cudaSuccess) {
             return error;
         }
         configured = true;
     }
-    if (n == 256) {
-        gemm_tc_kernel<Dequant, 256><<<(unsigned)ctas, kGemmThreads, kGemmSharedBytes, stream>>>(a);
-    } else {
-        gemm_tc_kernel<Dequant, 128><<<(unsigned)ctas, kGemmThreads, kGemmSharedBytes, stream>>>(a);
-    }
+    gemm_tc_kernel<Dequant, N, TT><<<(unsigned)ctas, kGemmThreads, kGemmSharedBytes, stream>>>(a);
     return cudaGetLastError();
+}
+
+template <class Dequant>
+cudaError_t run_gemm(const GemmArgs &a, int n, int tt, uint64_t ctas, cudaStream_t stream)
+{
+    if (tt == 2) {
+        return n == 256 ? run_gemm_shape<Dequant, 256, 2>(a, ctas, stream) : run_gemm_shape<Dequant, 128, 2>(a, ctas, stream);
+    }
+    return n == 256 ? run_gemm_shape<Dequant, 256, 1>(a, ctas, stream) : run_gemm_shape<Dequant, 128, 1>(a, ctas, stream);
 }
 
 }  // namespace
@@ -634,9 +661,12 @@ int32_t launch_gemm(const syn_b200_matrix *m, const float *x, uint64_t tokens, u
     a.tokens = tokens;
     a.k_tiles = (uint32_t)(m->columns / kTileK);
     a.token_tiles = (uint32_t)((tokens + kTileTokens - 1) / kTileTokens);
-    // 256-row tiles unless that leaves SMs without a tile and 128-row tiles would not
+    // Two token tiles per CTA tile when there are at least two (a weight tile is then dequantised once per 256
+    // tokens); 256-row tiles unless that leaves SMs without a tile and 128-row tiles would not.
     const uint64_t sms = (uint64_t)sm_count(m->device);
-    const uint64_t tiles256 = ((m->rows + 255) / 256) * a.token_tiles;
+    const int tt = a.token_tiles >= 2 ? 2 : 1;
+    const uint64_t token_groups = (a.token_tiles + tt - 1) / tt;
+    const uint64_t tiles256 = ((m->rows + 255) / 256) * token_groups;
     const int n = tiles256 >= sms ? 256 : 128;
     a.row_tiles = (uint32_t)((m->rows + n - 1) / n);
     a.x_tiles = static_cast<const uint8_t *>(scratch);
@@ -655,16 +685,16 @@ int32_t launch_gemm(const syn_b200_matrix *m, const float *x, uint64_t tokens, u
     if (error != cudaSuccess) {
         return cuda_fail(error, "launching the activation conversion");
     }
-    uint64_t ctas = (uint64_t)a.row_tiles * a.token_tiles;
+    uint64_t ctas = (uint64_t)a.row_tiles * token_groups;
     if (ctas > sms) {
         ctas = sms;
     }
     if (m->type == kQ4_K) {
-        error = run_gemm<DequantQ4K>(a, n, ctas, stream);
+        error = run_gemm<DequantQ4K>(a, n, tt, ctas, stream);
     } else if (m->type == kQ6_K) {
-        error = planar ? run_gemm<DequantQ6K<true>>(a, n, ctas, stream) : run_gemm<DequantQ6K<false>>(a, n, ctas, stream);
+        error = planar ? run_gemm<DequantQ6K<true>>(a, n, tt, ctas, stream) : run_gemm<DequantQ6K<false>>(a, n, tt, ctas, stream);
     } else {
-        error = planar ? run_gemm<DequantQ8<true>>(a, n, ctas, stream) : run_gemm<DequantQ8<false>>(a, n, ctas, stream);
+        error = planar ? run_gemm<DequantQ8<true>>(a, n, tt, ctas, stream) : run_gemm<DequantQ8<false>>(a, n, tt, ctas, stream);
     }
     if (error != cudaSuccess) {
         return cuda_fail(error, "configuring or launching the tensor-core kernel");
