@@ -77,6 +77,19 @@ typedef struct syn_b200_device_info {
 
 typedef struct syn_b200_matrix syn_b200_matrix;
 
+/* Fused epilogue of a device product: v = dot (+ bias[r]); v = silu(gate[t][r]) * v when gate is set;
+ * y = accumulate ? y + v : v. Mirrors the fused regions of the reference's CPU executor -- Q/K/V bias add, residual
+ * add, gate/up SwiGLU (src/Synapse.Runtime/Features/TextGeneration/Qwen2/Qwen2ProjectionWork.cs:7-131) -- and the
+ * bias / accumulate fields of MatmulArgs (native/synapse-gpu/.../cuda/kernels/common.cuh:52-69). Rows are counted from
+ * the first row of the call. All pointers are DEVICE memory; null switches the term off. */
+typedef struct syn_b200_epilogue {
+    const float *bias;    /* row_count floats */
+    const float *gate;    /* tokens rows of gate_stride floats: results of the gate projection for the same rows */
+    uint64_t gate_stride;
+    uint32_t accumulate;  /* 1: add to y (residual) */
+    uint32_t reserved;    /* must be 0 */
+} syn_b200_epilogue;
+
 /* Replaces synapse_kernels_abi_version / synapse_gpu_abi_version (ffi.rs:22 / ffi.rs:55-59). */
 SYN_B200_API uint32_t syn_b200_abi_version(void);
 
@@ -163,6 +176,11 @@ SYN_B200_API int32_t syn_b200_matmul_q8_dev(const syn_b200_matrix *matrix, uint6
                                const void *scratch, uint64_t tokens, float *y, uint64_t out_stride,
                                uint32_t epilogue, void *stream);
 
+/* syn_b200_matmul_q8_dev with a fused epilogue (null = plain store). */
+SYN_B200_API int32_t syn_b200_matmul_q8_ex_dev(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
+                                               const void *scratch, uint64_t tokens, float *y, uint64_t out_stride,
+                                               const syn_b200_epilogue *epilogue, void *stream);
+
 /* FP32 device activations x matrix rows. XQ8 mode quantises into `scratch` first (required, at least
  * syn_b200_activation_scratch_bytes); XF32 mode ignores scratch. */
 SYN_B200_API int32_t syn_b200_matvec_dev(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
@@ -185,6 +203,14 @@ SYN_B200_API int32_t syn_b200_matvec_static(const syn_b200_matrix *matrix, uint6
 
 /* Largest tokens * columns syn_b200_matvec_static accepts. */
 SYN_B200_API uint64_t syn_b200_matvec_static_capacity(void);
+
+/* syn_b200_matvec_dev with a fused epilogue (null = plain store). In XF32 mode prompt runs of more than 4 tokens go
+ * to the tensor-core product, as the reference's project() does (step/projection.rs:14,51-72); scratch must then hold
+ * syn_b200_gemm_scratch_bytes and the epilogue must be null. */
+SYN_B200_API int32_t syn_b200_matvec_ex_dev(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
+                                            const float *x, uint64_t tokens, uint64_t in_stride, float *y,
+                                            uint64_t out_stride, uint32_t mode, const syn_b200_epilogue *epilogue,
+                                            void *scratch, uint64_t scratch_bytes, void *stream);
 
 /* Bytes of device scratch syn_b200_gemm_dev needs for `tokens` x `columns` activations (16-bit operands). */
 SYN_B200_API uint64_t syn_b200_gemm_scratch_bytes(uint64_t tokens, uint64_t columns);

@@ -51,6 +51,12 @@ class KernelError(RuntimeError):
         self.status = status
 
 
+class Epilogue(ctypes.Structure):
+    """``syn_b200_epilogue``: v = dot (+ bias[r]); v = silu(gate[t][r]) * v; y = accumulate ? y + v : v (device pointers)."""
+
+    _fields_ = [("bias", c_void_p), ("gate", c_void_p), ("gate_stride", c_uint64), ("accumulate", c_uint32), ("reserved", c_uint32)]
+
+
 class DeviceInfo(ctypes.Structure):
     _fields_ = [("name", c_char * 128), ("total_memory_bytes", c_uint64), ("max_buffer_bytes", c_uint64),
                 ("compute_capability", c_uint32), ("multiprocessors", c_uint32)]
@@ -73,6 +79,8 @@ _EXPORTS = {
     "syn_b200_quantize_q8_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_uint64, c_void_p, c_uint64, c_void_p]),
     "syn_b200_matmul_q8_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, c_uint32, c_void_p]),
     "syn_b200_matvec_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32, c_uint32, c_void_p, c_uint64, c_void_p]),
+    "syn_b200_matmul_q8_ex_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, POINTER(Epilogue), c_void_p]),
+    "syn_b200_matvec_ex_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32, POINTER(Epilogue), c_void_p, c_uint64, c_void_p]),
     "syn_b200_matvec_static": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32, c_void_p]),
     "syn_b200_matvec_static_capacity": (c_uint64, []),
     "syn_b200_gemm_scratch_bytes": (c_uint64, [c_uint64, c_uint64]),
@@ -332,6 +340,23 @@ class QuantizedMatrix:
         row_count = self.rows - row_start if row_count is None else row_count
         self._lib.check(self._lib.raw.syn_b200_matvec_dev(self.handle, row_start, row_count, x_ptr, tokens, in_stride, y_ptr,
                                                          out_stride, mode, epilogue, scratch_ptr, scratch_bytes, stream))
+
+    def matvec_fused_device(self, x_ptr: int, tokens: int, in_stride: int, y_ptr: int, out_stride: int, mode: int = MODE_XQ8,
+                            bias_ptr: int = 0, gate_ptr: int = 0, gate_stride: int = 0, accumulate: bool = False, scratch_ptr: int = 0,
+                            scratch_bytes: int = 0, stream: int = 0, row_start: int = 0, row_count: int | None = None) -> None:
+        """Device product with the fused epilogue of the reference's projection regions (bias, SwiGLU gate, residual)."""
+        row_count = self.rows - row_start if row_count is None else row_count
+        epilogue = Epilogue(bias_ptr or None, gate_ptr or None, gate_stride, 1 if accumulate else 0, 0)
+        self._lib.check(self._lib.raw.syn_b200_matvec_ex_dev(self.handle, row_start, row_count, x_ptr, tokens, in_stride, y_ptr, out_stride,
+                                                            mode, byref(epilogue), scratch_ptr, scratch_bytes, stream))
+
+    def matmul_q8_fused_device(self, scratch_ptr: int, tokens: int, y_ptr: int, out_stride: int, bias_ptr: int = 0, gate_ptr: int = 0,
+                               gate_stride: int = 0, accumulate: bool = False, stream: int = 0, row_start: int = 0,
+                               row_count: int | None = None) -> None:
+        row_count = self.rows - row_start if row_count is None else row_count
+        epilogue = Epilogue(bias_ptr or None, gate_ptr or None, gate_stride, 1 if accumulate else 0, 0)
+        self._lib.check(self._lib.raw.syn_b200_matmul_q8_ex_dev(self.handle, row_start, row_count, scratch_ptr, tokens, y_ptr, out_stride,
+                                                               byref(epilogue), stream))
 
     def matvec_static(self, x_ptr: int, tokens: int, in_stride: int, y_ptr: int, out_stride: int, epilogue: int = EPILOGUE_STORE,
                       stream: int = 0, row_start: int = 0, row_count: int | None = None) -> None:

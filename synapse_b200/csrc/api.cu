@@ -282,9 +282,29 @@ int32_t create_matrix(const void *blocks, bool from_device, uint32_t type, uint6
 }
 
 // Queues quantise (or upload of ready codes) + product on `stream` with device x / y.
+// Prompt runs longer than this leave the matrix-vector kernels for the tensor cores (GEMM_MINIMUM_TOKENS,
+// native/synapse-gpu/src/Features/GpuKernels/step/projection.rs:14).
+constexpr uint64_t kGemmMinimumTokens = 4;
+
+int32_t convert_epilogue(const syn_b200_epilogue *in, Epilogue &out)
+{
+    out = Epilogue{};
+    if (!in) {
+        return SYN_B200_OK;
+    }
+    if (in->reserved != 0 || in->accumulate > 1) {
+        return fail(SYN_B200_INVALID_ARGUMENT, "epilogue flags must be 0 or 1 and the reserved field 0");
+    }
+    out.bias = in->bias;
+    out.gate = in->gate;
+    out.gate_stride = in->gate_stride;
+    out.accumulate = in->accumulate;
+    return SYN_B200_OK;
+}
+
 int32_t product_dev(const syn_b200_matrix *m, uint64_t row_start, uint64_t row_count, const float *x, uint64_t tokens,
                     uint64_t in_stride, float *y, uint64_t out_stride, uint32_t mode, uint32_t epilogue, void *scratch,
-                    uint64_t scratch_bytes, cudaStream_t stream)
+                    uint64_t scratch_bytes, cudaStream_t stream, const Epilogue &fused = Epilogue{})
 {
     if (mode != SYN_B200_MODE_XQ8 && mode != SYN_B200_MODE_XF32) {
         return fail(SYN_B200_INVALID_ARGUMENT, "unknown activation mode " + std::to_string(mode));
@@ -299,6 +319,12 @@ int32_t product_dev(const syn_b200_matrix *m, uint64_t row_start, uint64_t row_c
     if (in_stride % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) {
         return fail(SYN_B200_INVALID_ARGUMENT, "device activations must be 16-byte aligned with a stride that is a multiple of 4 floats");
     }
+    const bool plain = epilogue == SYN_B200_EPILOGUE_STORE && !fused.bias && !fused.gate && !fused.accumulate;
+    if (mode == SYN_B200_MODE_XF32 && tokens > kGemmMinimumTokens && plain && row_start == 0 && row_count == m->rows &&
+        m->columns % 64 == 0 && scratch && scratch_bytes >= gemm_scratch_bytes(tokens, m->columns) &&
+        (reinterpret_cast<uintptr_t>(scratch) & 255) == 0) {
+        return launch_gemm(m, x, tokens, in_stride, y, out_stride, SYN_B200_GEMM_F16, scratch, scratch_bytes, stream);
+    }
     MatvecArgs args{};
     args.matrix = m;
     args.row_start = row_start;
@@ -308,6 +334,7 @@ int32_t product_dev(const syn_b200_matrix *m, uint64_t row_start, uint64_t row_c
     args.out_stride = out_stride;
     args.mode = mode;
     args.epilogue = epilogue;
+    args.fused = fused;
     if (mode == SYN_B200_MODE_XQ8) {
         const ActLayout layout = act_layout(tokens, m->columns);
         if (!scratch || scratch_bytes < layout.total) {
@@ -560,6 +587,60 @@ int32_t syn_b200_matvec_dev(const syn_b200_matrix *matrix, uint64_t row_start, u
         }
         return product_dev(matrix, row_start, row_count, x, tokens, in_stride, y, out_stride, mode, epilogue, scratch,
                            scratch_bytes, static_cast<cudaStream_t>(stream));
+    });
+}
+
+int32_t syn_b200_matvec_ex_dev(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count, const float *x,
+                               uint64_t tokens, uint64_t in_stride, float *y, uint64_t out_stride, uint32_t mode,
+                               const syn_b200_epilogue *epilogue, void *scratch, uint64_t scratch_bytes, void *stream)
+{
+    if (!matrix || !x || !y) {
+        return fail(SYN_B200_NULL_POINTER, "matrix, activations or output");
+    }
+    return guarded([&]() -> int32_t {
+        int32_t status = check_product(matrix, row_start, row_count, tokens, out_stride, nullptr);
+        if (status == SYN_B200_OK) status = check_device(matrix);
+        Epilogue fused;
+        if (status == SYN_B200_OK) status = convert_epilogue(epilogue, fused);
+        if (status != SYN_B200_OK) {
+            return status;
+        }
+        return product_dev(matrix, row_start, row_count, x, tokens, in_stride, y, out_stride, mode, SYN_B200_EPILOGUE_STORE, scratch,
+                           scratch_bytes, static_cast<cudaStream_t>(stream), fused);
+    });
+}
+
+int32_t syn_b200_matmul_q8_ex_dev(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count, const void *scratch,
+                                  uint64_t tokens, float *y, uint64_t out_stride, const syn_b200_epilogue *epilogue, void *stream)
+{
+    if (!matrix || !scratch || !y) {
+        return fail(SYN_B200_NULL_POINTER, "matrix, scratch or output");
+    }
+    return guarded([&]() -> int32_t {
+        int32_t status = check_product(matrix, row_start, row_count, tokens, out_stride, nullptr);
+        if (status == SYN_B200_OK) status = check_device(matrix);
+        Epilogue fused;
+        if (status == SYN_B200_OK) status = convert_epilogue(epilogue, fused);
+        if (status != SYN_B200_OK) {
+            return status;
+        }
+        if (reinterpret_cast<uintptr_t>(scratch) & 255) {
+            return fail(SYN_B200_INVALID_ARGUMENT, "activation scratch must be 256-byte aligned");
+        }
+        MatvecArgs args{};
+        args.matrix = matrix;
+        args.row_start = row_start;
+        args.row_count = row_count;
+        args.tokens = tokens;
+        args.act = act_view(scratch, tokens, matrix->columns);
+        args.act_ready = true;
+        args.y = y;
+        args.out_stride = out_stride;
+        args.mode = SYN_B200_MODE_XQ8;
+        args.epilogue = SYN_B200_EPILOGUE_STORE;
+        args.fused = fused;
+        cudaError_t error = launch_matvec(args, static_cast<cudaStream_t>(stream));
+        return error == cudaSuccess ? SYN_B200_OK : cuda_fail(error, "launching the matrix-vector kernel");
     });
 }
 

@@ -126,6 +126,16 @@ uint64_t planar_bytes(uint32_t type, uint64_t rows, uint64_t columns, PlaneOffse
 cudaError_t launch_repack(uint32_t type, const uint8_t *natural, uint64_t rows, uint64_t columns, uint8_t *planar,
                           const PlaneOffsets &planes, cudaStream_t stream);
 
+// What happens to a finished dot product before it is stored (the fused regions of the reference's CPU executor,
+// Qwen2/Qwen2ProjectionWork.cs:7-131, and `accumulate` of cuda/kernels/common.cuh:52-69):
+//   v = dot (+ bias[row]);  v = silu(gate[token][row]) * v when gate is set;  y = accumulate ? y + v : v
+struct Epilogue {
+    const float *bias = nullptr;  // indexed by row relative to the first row of the call
+    const float *gate = nullptr;  // gate projection results, [token][row] with gate_stride, same row origin
+    uint64_t gate_stride = 0;
+    uint32_t accumulate = 0;
+};
+
 // matvec.cu
 struct MatvecArgs {
     const syn_b200_matrix *matrix;
@@ -140,7 +150,8 @@ struct MatvecArgs {
     float *y;
     uint64_t out_stride;
     uint32_t mode;
-    uint32_t epilogue;
+    uint32_t epilogue;  // SYN_B200_EPILOGUE_*; folded into `fused.accumulate` by launch_matvec
+    Epilogue fused;
     int32_t *dump;  // test hook: integer sub-block dots, or null
 };
 cudaError_t launch_matvec(const MatvecArgs &args, cudaStream_t stream);

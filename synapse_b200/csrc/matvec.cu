@@ -143,7 +143,7 @@ struct Q6KNaturalXf32 {
 template <class F, int T, int R>
 __global__ void __launch_bounds__(kWarps * 32)
 matvec_xf32_kernel(WeightView w, const float *__restrict__ x, uint64_t in_stride, uint64_t K, uint64_t rows, uint32_t tokens,
-                   float *__restrict__ y, uint64_t out_stride, uint32_t accumulate)
+                   float *__restrict__ y, uint64_t out_stride, Epilogue epilogue)
 {
     const uint32_t lane = threadIdx.x & 31;
     const uint64_t warp = (uint64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
@@ -181,8 +181,7 @@ matvec_xf32_kernel(WeightView w, const float *__restrict__ x, uint64_t in_stride
             for (int t = 0; t < T; ++t) {
                 const float total = warp_sum(acc[r][t]);
                 if (lane == 0 && row0 + r < rows && (uint32_t)t < live) {
-                    float *destination = y + (token0 + t) * out_stride + row0 + r;
-                    *destination = accumulate ? *destination + total : total;
+                    store_result(epilogue, y, token0 + t, out_stride, row0 + r, total);
                 }
             }
         }
@@ -220,8 +219,7 @@ cudaError_t run_xf32(const MatvecArgs &a, cudaStream_t stream)
     }
     const dim3 grid((unsigned)ctas, (unsigned)((a.tokens + T - 1) / T));
     matvec_xf32_kernel<F, T, R><<<grid, kWarps * 32, 0, stream>>>(view_of(a.matrix, a.row_start), a.x, a.in_stride, a.matrix->columns,
-                                                                 a.row_count, (uint32_t)a.tokens, a.y, a.out_stride,
-                                                                 a.epilogue == SYN_B200_EPILOGUE_ACCUMULATE);
+                                                                 a.row_count, (uint32_t)a.tokens, a.y, a.out_stride, a.fused);
     count_launch();
     return cudaGetLastError();
 }
@@ -241,9 +239,11 @@ cudaError_t dispatch_xf32(const MatvecArgs &a, cudaStream_t stream)
 }  // namespace
 }  // namespace mv
 
-cudaError_t launch_matvec(const MatvecArgs &a, cudaStream_t stream)
+cudaError_t launch_matvec(const MatvecArgs &args, cudaStream_t stream)
 {
     using namespace mv;
+    MatvecArgs a = args;
+    a.fused.accumulate = (a.epilogue == SYN_B200_EPILOGUE_ACCUMULATE || args.fused.accumulate) ? 1u : 0u;
     const syn_b200_matrix *m = a.matrix;
     const bool planar = m->layout == Layout::Planar;
     if (a.dump || a.mode == SYN_B200_MODE_XQ8) {

@@ -170,6 +170,20 @@ __device__ __forceinline__ void q6k_codes(uint32_t a, uint32_t b, uint32_t h, ui
     v4 = ((b >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u);
 }
 
+// Applies the epilogue to one finished dot product and stores it.
+__device__ __forceinline__ void store_result(const Epilogue &e, float *__restrict__ y, uint64_t token, uint64_t out_stride, uint64_t row, float v)
+{
+    if (e.bias) {
+        v += __ldg(e.bias + row);
+    }
+    if (e.gate) {
+        const float g = __ldg(e.gate + token * e.gate_stride + row);
+        v = g / (1.0f + expf(-g)) * v;
+    }
+    float *destination = y + token * out_stride + row;
+    *destination = e.accumulate ? *destination + v : v;
+}
+
 __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
 // ------------------------------------------------------------------------------------------------------

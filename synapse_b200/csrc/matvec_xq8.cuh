@@ -88,7 +88,7 @@ __host__ __device__ constexpr int team_warps(int W) { return (kWarps / W) * W; }
 template <class F, int T, int W, int UPL, int R, bool REGS, bool DUMP>
 __global__ void __launch_bounds__(team_warps(W) * 32)
 matvec_xq8_team_kernel(WeightView w, ActView act, uint64_t K, uint64_t rows, uint32_t tokens, float *__restrict__ y,
-                       uint64_t out_stride, uint32_t accumulate, int32_t *__restrict__ dump, uint64_t dump_groups)
+                       uint64_t out_stride, Epilogue epilogue, int32_t *__restrict__ dump, uint64_t dump_groups)
 {
     static_assert(!REGS || T == 1, "register-resident activations are for single-token launches");
     constexpr int kTeams = kWarps / W;
@@ -172,8 +172,7 @@ matvec_xq8_team_kernel(WeightView w, ActView act, uint64_t K, uint64_t rows, uin
 #pragma unroll
                     for (int t = 0; t < T; ++t) {
                         if (row0 + r < rows && (uint32_t)t < live) {
-                            float *destination = y + (token0 + t) * out_stride + row0 + r;
-                            *destination = accumulate ? *destination + acc[r][t] : acc[r][t];
+                            store_result(epilogue, y, token0 + t, out_stride, row0 + r, acc[r][t]);
                         }
                     }
                 }
@@ -198,8 +197,7 @@ matvec_xq8_team_kernel(WeightView w, ActView act, uint64_t K, uint64_t rows, uin
                     total += partial[buffer][team_in_cta * W + k][lane];
                 }
                 if (row0 + r < rows && t < live) {
-                    float *destination = y + (token0 + t) * out_stride + row0 + r;
-                    *destination = accumulate ? *destination + total : total;
+                    store_result(epilogue, y, token0 + t, out_stride, row0 + r, total);
                 }
             }
         }
@@ -230,8 +228,7 @@ cudaError_t launch_team(const MatvecArgs &a, const WeightView &view, uint64_t du
     }
     const dim3 grid((unsigned)ctas, (unsigned)((a.tokens + T - 1) / T));
     return launch_kernel(matvec_xq8_team_kernel<F, T, W, UPL, R, REGS, DUMP>, grid, dim3(team_warps(W) * 32), 0, stream, view, a.act,
-                         a.matrix->columns, a.row_count, (uint32_t)a.tokens, a.y, a.out_stride,
-                         (uint32_t)(a.epilogue == SYN_B200_EPILOGUE_ACCUMULATE), a.dump, dump_groups);
+                         a.matrix->columns, a.row_count, (uint32_t)a.tokens, a.y, a.out_stride, a.fused, a.dump, dump_groups);
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -300,7 +297,7 @@ __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %
 template <class F, int T, int W, int UPL, int R, bool REGS, bool FUSED>
 __global__ void __launch_bounds__(team_warps(W) * 32 + 32, F::min_ctas(W))
 matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uint64_t in_stride, uint64_t K, uint64_t rows, uint32_t tokens,
-                       float *__restrict__ y, uint64_t out_stride, uint32_t accumulate, uint32_t *fault)
+                       float *__restrict__ y, uint64_t out_stride, Epilogue epilogue, uint32_t *fault)
 {
     static_assert(!REGS || T == 1, "register-resident activations are for single-token launches");
     constexpr int kTeams = kWarps / W;
@@ -488,8 +485,7 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
 #pragma unroll
                     for (int t = 0; t < T; ++t) {
                         if (row0 + r < rows && (uint32_t)t < live) {
-                            float *destination = y + (token0 + t) * out_stride + row0 + r;
-                            *destination = accumulate ? *destination + acc[r][t] : acc[r][t];
+                            store_result(epilogue, y, token0 + t, out_stride, row0 + r, acc[r][t]);
                         }
                     }
                 }
@@ -514,8 +510,7 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
                     total += partial[buffer][team_in_cta * W + k][lane];
                 }
                 if (row0 + r < rows && t < live) {
-                    float *destination = y + (token0 + t) * out_stride + row0 + r;
-                    *destination = accumulate ? *destination + total : total;
+                    store_result(epilogue, y, token0 + t, out_stride, row0 + r, total);
                 }
             }
         }
@@ -573,7 +568,7 @@ cudaError_t launch_pipe(const MatvecArgs &a, const PipeArgs &p, cudaStream_t str
     }
     const dim3 grid((unsigned)ctas, (unsigned)((a.tokens + T - 1) / T));
     return launch_kernel(kernel, grid, dim3(team_warps(W) * 32 + 32), dynamic, stream, p, a.act, a.x, a.in_stride, a.matrix->columns, a.row_count,
-                         (uint32_t)a.tokens, a.y, a.out_stride, (uint32_t)(a.epilogue == SYN_B200_EPILOGUE_ACCUMULATE), fault_word_device());
+                         (uint32_t)a.tokens, a.y, a.out_stride, a.fused, fault_word_device());
 }
 
 template <class F, int W, int UPL>
