@@ -220,6 +220,63 @@ SYN_B200_API int32_t syn_b200_gemm_dev(const syn_b200_matrix *matrix, const floa
                           float *y, uint64_t out_stride, uint32_t precision, void *scratch,
                           uint64_t scratch_bytes, void *stream);
 
+/* ---- Whole decode step (the surround of the matrix products). Same structs as the reference's GPU ABI, so that
+ * GpuDecoderExecutor (src/Synapse.Runtime/Features/GpuKernels/GpuDecoderExecutor.cs:135-180) can fill them unchanged;
+ * numerics are those of the reference's optimized CPU executor (Q8_0-quantised activations in every projection,
+ * src/Synapse.Runtime/Features/TextGeneration/Qwen2/Qwen2CpuExecutor.cs:105-244). ---- */
+
+#define SYN_B200_NO_TENSOR 0xFFFFFFFFFFFFFFFFull
+
+/* DecoderLayerOffsets (native/synapse-gpu/src/Features/GpuKernels/decoder.rs:61-93), 120 bytes: byte offsets of one
+ * block's tensors inside `weights`; optional tensors use SYN_B200_NO_TENSOR. `encodings`: GGML type ids of Q, K, V, O,
+ * gate, up, down, four bits each from the lowest. Norm weights and biases are FP32. */
+typedef struct syn_b200_layer_offsets {
+    uint64_t attention_norm, query, key, value, query_bias, key_bias, value_bias, query_norm, key_norm;
+    uint64_t attention_output, feed_forward_norm, gate, up, down, encodings;
+} syn_b200_layer_offsets;
+
+/* DecoderDesc (decoder.rs:96-131), 136 bytes. `weights` is HOST memory (the mapped model file) and is not referenced
+ * after create; rope tables hold context * head_dim/2 floats each (computed by the host, RopeFrequencies.cs:55-78). */
+typedef struct syn_b200_decoder_desc {
+    const uint8_t *weights;
+    uint64_t weights_length;
+    const syn_b200_layer_offsets *layers;
+    const float *rope_cosines;
+    const float *rope_sines;
+    uint64_t token_embedding, output_norm, output;
+    uint32_t layer_count, hidden, feed_forward, heads, kv_heads, head_dim, vocabulary, context, session_slots;
+    uint32_t step_tokens, logits_rows;
+    float rms_epsilon;
+    uint32_t embedding_encoding, rope_layout, activation, kv_precision, kv_growth_positions, output_encoding;
+} syn_b200_decoder_desc;
+
+/* BatchToken (decoder.rs:134-141), 16 bytes: KV slot, token id, position, logits row or -1. */
+typedef struct syn_b200_batch_token {
+    int32_t slot, token, position, logits_row;
+} syn_b200_batch_token;
+
+typedef struct syn_b200_decoder syn_b200_decoder;
+
+/* Replaces synapse_gpu_decoder_create (ffi.rs:113-172). Up to 8 tokens per step; FP32 KV cache of `context` positions
+ * per slot; NeoX rotary layout; SwiGLU. */
+SYN_B200_API int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_decoder **out);
+
+/* Replaces synapse_gpu_decoder_forward (ffi.rs:181-203): one batched step; writes k * vocabulary logits for its k
+ * logits rows (numbered 0..k-1 in token order) to HOST memory. */
+SYN_B200_API int32_t syn_b200_decoder_forward(syn_b200_decoder *decoder, const syn_b200_batch_token *tokens, uint64_t count,
+                                              float *logits, uint64_t logits_capacity);
+
+/* Same step, but only the greedy choice of every logits row comes back (first maximum, as Q8Operators.ArgMax,
+ * src/Synapse.Runtime/Features/GraphExecution/Q8Operators.cs:152-173). No counterpart in the reference's ABI. */
+SYN_B200_API int32_t syn_b200_decoder_forward_argmax(syn_b200_decoder *decoder, const syn_b200_batch_token *tokens, uint64_t count,
+                                                     int32_t *argmax);
+
+/* Replaces synapse_gpu_decoder_destroy (ffi.rs:205-216); null is ignored. */
+SYN_B200_API void syn_b200_decoder_destroy(syn_b200_decoder *decoder);
+
+/* Replaces synapse_gpu_decoder_kv_bytes (ffi.rs:218-232). */
+SYN_B200_API uint64_t syn_b200_decoder_kv_bytes(const syn_b200_decoder *decoder);
+
 /* Number of bounded device-side waits that gave up since the last reset (0 in a healthy run). A kernel whose
  * wait on one of its own asynchronous copies runs out of patience records it here and still terminates; the
  * results of that launch are then undefined. No counterpart in the reference. */

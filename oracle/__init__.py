@@ -79,6 +79,14 @@ def lib():
         handle.orc_f32_matmul_threads.argtypes = [c_uint32, c_void_p, c_size_t, c_size_t, c_void_p, c_size_t, c_size_t, c_void_p, c_size_t, c_size_t]
         handle.orc_lcg_case.restype = None
         handle.orc_lcg_case.argtypes = [c_uint64, c_size_t, c_size_t, c_size_t, c_void_p, c_void_p, c_void_p]
+        handle.orc_decoder_create.restype = c_void_p
+        handle.orc_decoder_create.argtypes = [c_void_p, c_size_t]
+        handle.orc_decoder_destroy.restype = None
+        handle.orc_decoder_destroy.argtypes = [c_void_p]
+        handle.orc_decoder_forward.restype = c_int
+        handle.orc_decoder_forward.argtypes = [c_void_p, c_int32, c_int32, c_int32, c_void_p]
+        handle.orc_argmax.restype = c_int32
+        handle.orc_argmax.argtypes = [c_void_p, c_size_t]
         _lib = handle
     return _lib
 
@@ -258,3 +266,38 @@ def lcg_case(seed, rows, blocks, tokens):
     scales = np.empty(tokens * blocks, np.float32)
     lib().orc_lcg_case(seed, rows, blocks, tokens, _addr(weights), _addr(quants), _addr(scales))
     return weights, quants, scales
+
+
+class Decoder:
+    """The reference's optimized CPU executor, one token at a time (O8). ``desc`` is a ctypes structure with the layout of
+    the reference's DecoderDesc; it and the buffers it points to must outlive the decoder."""
+
+    def __init__(self, desc, vocabulary: int, threads: int | None = None):
+        self._desc = desc
+        self.vocabulary = vocabulary
+        self._handle = lib().orc_decoder_create(ctypes.addressof(desc), threads or (os.cpu_count() or 1))
+        if not self._handle:
+            raise MemoryError("oracle decoder allocation failed")
+
+    def decode(self, token: int, position: int, slot: int = 0) -> np.ndarray:
+        logits = np.empty(self.vocabulary, np.float32)
+        status = lib().orc_decoder_forward(self._handle, slot, token, position, _addr(logits))
+        if status != 0:
+            raise ValueError(f"oracle decoder rejected the token (status {status})")
+        return logits
+
+    @staticmethod
+    def argmax(logits: np.ndarray) -> int:
+        logits = _c(logits, np.float32)
+        return int(lib().orc_argmax(_addr(logits), logits.size))
+
+    def close(self):
+        if self._handle:
+            lib().orc_decoder_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -876,3 +876,252 @@ void orc_lcg_case(uint64_t seed, size_t rows, size_t blocks, size_t tokens, uint
     }
 #undef LCG_NEXT
 }
+
+/* ------------------------------------------------------------------------------------------------ */
+/* O8: the decode step of the optimized CPU executor (Q8_0-quantised activations everywhere)          */
+/* ------------------------------------------------------------------------------------------------ */
+
+#define ORC_NO_TENSOR 0xFFFFFFFFFFFFFFFFull
+
+/* Same field order and sizes as DecoderLayerOffsets (native/synapse-gpu/src/Features/GpuKernels/decoder.rs:61-93). */
+typedef struct {
+    uint64_t attention_norm, query, key, value, query_bias, key_bias, value_bias, query_norm, key_norm;
+    uint64_t attention_output, feed_forward_norm, gate, up, down, encodings;
+} orc_layer_offsets;
+
+/* Same field order and sizes as DecoderDesc (decoder.rs:96-131). */
+typedef struct {
+    const uint8_t *weights;
+    uint64_t weights_length;
+    const orc_layer_offsets *layers;
+    const float *rope_cosines, *rope_sines;
+    uint64_t token_embedding, output_norm, output;
+    uint32_t layer_count, hidden, feed_forward, heads, kv_heads, head_dim, vocabulary, context, session_slots;
+    uint32_t step_tokens, logits_rows;
+    float rms_epsilon;
+    uint32_t embedding_encoding, rope_layout, activation, kv_precision, kv_growth_positions, output_encoding;
+} orc_decoder_desc;
+
+typedef struct {
+    orc_decoder_desc desc;
+    float *keys, *values; /* [slot][layer][kv_head][position][head_dim] */
+    size_t threads;
+} orc_decoder;
+
+static uint32_t layer_encoding(const orc_layer_offsets *layer, int matrix)
+{
+    return (uint32_t)((layer->encodings >> (4 * matrix)) & 0xF);
+}
+
+/* RMSNorm with an FP64 sum of squares (GraphExecution/Q8Operators.cs:101-123). */
+static void rms_norm(const float *x, const float *w, float epsilon, size_t n, float *out)
+{
+    double sum = 0.0;
+    for (size_t i = 0; i < n; ++i) {
+        sum += (double)x[i] * x[i];
+    }
+    float scale = 1.0f / sqrtf((float)(sum / (double)n) + epsilon);
+    for (size_t i = 0; i < n; ++i) {
+        out[i] = x[i] * scale * w[i];
+    }
+}
+
+/* One quantised-activation product over all rows with the contract of the matching encoding (O2 / O6); large
+ * matrices are split into row ranges over threads, which does not change any row's arithmetic. */
+typedef struct {
+    uint32_t type;
+    const uint8_t *weights;
+    size_t rows, columns;
+    const int8_t *codes;
+    const float *scales;
+    float *out;
+} matmul_slice;
+
+static void *matmul_slice_run(void *arg)
+{
+    matmul_slice *m = (matmul_slice *)arg;
+    orc_kq_q8_matmul(m->type, m->weights, m->rows, m->columns, m->codes, m->scales, 1, m->out, m->rows);
+    return NULL;
+}
+
+static void decoder_matmul(const orc_decoder *d, uint32_t type, uint64_t offset, size_t rows, size_t columns, const int8_t *codes,
+                           const float *scales, float *out)
+{
+    size_t threads = d->threads;
+    if (rows * columns < (1u << 22) || threads < 2) {
+        orc_kq_q8_matmul(type, d->desc.weights + offset, rows, columns, codes, scales, 1, out, rows);
+        return;
+    }
+    if (threads > 64) {
+        threads = 64;
+    }
+    pthread_t ids[64];
+    matmul_slice slices[64];
+    size_t row_bytes = orc_row_bytes(type, columns), per = (rows + threads - 1) / threads, started = 0;
+    for (size_t t = 0; t < threads; ++t) {
+        size_t first = t * per;
+        if (first >= rows) {
+            break;
+        }
+        slices[t] = (matmul_slice){type, d->desc.weights + offset + first * row_bytes, rows - first < per ? rows - first : per, columns, codes,
+                                   scales, out + first};
+        if (pthread_create(&ids[t], NULL, matmul_slice_run, &slices[t]) != 0) {
+            matmul_slice_run(&slices[t]);
+            ids[t] = 0;
+        }
+        started = t + 1;
+    }
+    for (size_t t = 0; t < started; ++t) {
+        if (ids[t]) {
+            pthread_join(ids[t], NULL);
+        }
+    }
+}
+
+orc_decoder *orc_decoder_create(const orc_decoder_desc *desc, size_t threads)
+{
+    orc_decoder *d = (orc_decoder *)calloc(1, sizeof *d);
+    if (!d) {
+        return NULL;
+    }
+    d->desc = *desc;
+    d->threads = threads ? threads : 1;
+    size_t cache = (size_t)desc->session_slots * desc->layer_count * desc->kv_heads * desc->context * desc->head_dim;
+    d->keys = (float *)calloc(cache, sizeof(float));
+    d->values = (float *)calloc(cache, sizeof(float));
+    if (!d->keys || !d->values) {
+        free(d->keys);
+        free(d->values);
+        free(d);
+        return NULL;
+    }
+    return d;
+}
+
+void orc_decoder_destroy(orc_decoder *d)
+{
+    if (d) {
+        free(d->keys);
+        free(d->values);
+        free(d);
+    }
+}
+
+static size_t kv_index(const orc_decoder_desc *s, uint32_t slot, uint32_t layer, uint32_t kv_head, uint32_t position)
+{
+    return ((((size_t)slot * s->layer_count + layer) * s->kv_heads + kv_head) * s->context + position) * s->head_dim;
+}
+
+/* One token through the whole decoder: embedding row, per layer {RMSNorm -> quantise -> Q/K/V + bias -> NeoX RoPE ->
+ * KV store -> softmax attention over the slot's cache -> quantise -> output projection + residual -> RMSNorm ->
+ * quantise -> gate/up -> SwiGLU -> quantise -> down + residual}, output norm, quantise, vocabulary projection.
+ * Follows Qwen2/Qwen2CpuExecutor.cs:105-244, Qwen2ProjectionWork.cs:7-157, Qwen2CpuState.cs:85-105 (RoPE),
+ * Qwen2CpuAttention.cs:82-173. Returns 0, or 2 on an invalid token. logits holds `vocabulary` floats. */
+int orc_decoder_forward(orc_decoder *d, int32_t slot, int32_t token, int32_t position, float *logits)
+{
+    const orc_decoder_desc *s = &d->desc;
+    if (slot < 0 || (uint32_t)slot >= s->session_slots || token < 0 || (uint32_t)token >= s->vocabulary || position < 0 ||
+        (uint32_t)position >= s->context) {
+        return 2;
+    }
+    const size_t hidden = s->hidden, ffn = s->feed_forward, kvw = (size_t)s->kv_heads * s->head_dim, half = s->head_dim / 2;
+    float *h = (float *)malloc(sizeof(float) * (hidden * 4 + kvw * 2 + ffn * 3 + s->context));
+    if (!h) {
+        return 3;
+    }
+    float *normed = h + hidden, *q = normed + hidden, *attn = q + hidden, *k = attn + hidden, *v = k + kvw, *gate = v + kvw,
+          *up = gate + ffn, *ff = up + ffn, *scores = ff + ffn;
+    size_t widest = hidden > ffn ? hidden : ffn;
+    int8_t *codes = (int8_t *)malloc(widest);
+    float *scales = (float *)malloc(sizeof(float) * (widest / 32));
+    orc_decode_row(s->embedding_encoding, s->weights + s->token_embedding + (size_t)token * orc_row_bytes(s->embedding_encoding, hidden),
+                   hidden, h);
+    const float *cosines = s->rope_cosines + (size_t)position * half, *sines = s->rope_sines + (size_t)position * half;
+    const float attention_scale = 1.0f / sqrtf((float)s->head_dim);
+    for (uint32_t l = 0; l < s->layer_count; ++l) {
+        const orc_layer_offsets *L = &s->layers[l];
+        rms_norm(h, (const float *)(s->weights + L->attention_norm), s->rms_epsilon, hidden, normed);
+        orc_q8_quantize_row(normed, hidden, codes, scales);
+        decoder_matmul(d, layer_encoding(L, 0), L->query, hidden, hidden, codes, scales, q);
+        decoder_matmul(d, layer_encoding(L, 1), L->key, kvw, hidden, codes, scales, k);
+        decoder_matmul(d, layer_encoding(L, 2), L->value, kvw, hidden, codes, scales, v);
+        if (L->query_bias != ORC_NO_TENSOR) {
+            const float *bq = (const float *)(s->weights + L->query_bias), *bk = (const float *)(s->weights + L->key_bias),
+                        *bv = (const float *)(s->weights + L->value_bias);
+            for (size_t i = 0; i < hidden; ++i) q[i] += bq[i];
+            for (size_t i = 0; i < kvw; ++i) k[i] += bk[i];
+            for (size_t i = 0; i < kvw; ++i) v[i] += bv[i];
+        }
+        for (uint32_t head = 0; head < s->heads + s->kv_heads; ++head) {
+            float *x = head < s->heads ? q + (size_t)head * s->head_dim : k + (size_t)(head - s->heads) * s->head_dim;
+            for (size_t i = 0; i < half; ++i) {
+                float a = x[i], b = x[i + half];
+                x[i] = a * cosines[i] - b * sines[i];
+                x[i + half] = a * sines[i] + b * cosines[i];
+            }
+        }
+        for (uint32_t kh = 0; kh < s->kv_heads; ++kh) {
+            memcpy(d->keys + kv_index(s, (uint32_t)slot, l, kh, (uint32_t)position), k + (size_t)kh * s->head_dim, sizeof(float) * s->head_dim);
+            memcpy(d->values + kv_index(s, (uint32_t)slot, l, kh, (uint32_t)position), v + (size_t)kh * s->head_dim, sizeof(float) * s->head_dim);
+        }
+        const uint32_t group = s->heads / s->kv_heads;
+        for (uint32_t head = 0; head < s->heads; ++head) {
+            const float *qh = q + (size_t)head * s->head_dim;
+            const uint32_t kh = head / group;
+            float maximum = -INFINITY;
+            for (int32_t p = 0; p <= position; ++p) {
+                const float *kp = d->keys + kv_index(s, (uint32_t)slot, l, kh, (uint32_t)p);
+                float dot = 0.0f;
+                for (uint32_t i = 0; i < s->head_dim; ++i) dot += qh[i] * kp[i];
+                scores[p] = dot * attention_scale;
+                maximum = fmaxf(maximum, scores[p]);
+            }
+            float sum = 0.0f;
+            for (int32_t p = 0; p <= position; ++p) {
+                scores[p] = expf(scores[p] - maximum);
+                sum += scores[p];
+            }
+            const float inverse = 1.0f / sum;
+            float *out = attn + (size_t)head * s->head_dim;
+            for (uint32_t i = 0; i < s->head_dim; ++i) out[i] = 0.0f;
+            for (int32_t p = 0; p <= position; ++p) {
+                const float *vp = d->values + kv_index(s, (uint32_t)slot, l, kh, (uint32_t)p);
+                const float weight = scores[p] * inverse;
+                for (uint32_t i = 0; i < s->head_dim; ++i) out[i] += weight * vp[i];
+            }
+        }
+        orc_q8_quantize_row(attn, hidden, codes, scales);
+        decoder_matmul(d, layer_encoding(L, 3), L->attention_output, hidden, hidden, codes, scales, normed);
+        for (size_t i = 0; i < hidden; ++i) h[i] += normed[i];
+        rms_norm(h, (const float *)(s->weights + L->feed_forward_norm), s->rms_epsilon, hidden, normed);
+        orc_q8_quantize_row(normed, hidden, codes, scales);
+        decoder_matmul(d, layer_encoding(L, 4), L->gate, ffn, hidden, codes, scales, gate);
+        decoder_matmul(d, layer_encoding(L, 5), L->up, ffn, hidden, codes, scales, up);
+        for (size_t i = 0; i < ffn; ++i) {
+            float value = gate[i];
+            ff[i] = value / (1.0f + expf(-value)) * up[i];
+        }
+        orc_q8_quantize_row(ff, ffn, codes, scales);
+        decoder_matmul(d, layer_encoding(L, 6), L->down, hidden, ffn, codes, scales, normed);
+        for (size_t i = 0; i < hidden; ++i) h[i] += normed[i];
+    }
+    rms_norm(h, (const float *)(s->weights + s->output_norm), s->rms_epsilon, hidden, normed);
+    orc_q8_quantize_row(normed, hidden, codes, scales);
+    decoder_matmul(d, s->output_encoding, s->output, s->vocabulary, hidden, codes, scales, logits);
+    free(codes);
+    free(scales);
+    free(h);
+    return 0;
+}
+
+/* First maximum (GraphExecution/Q8Operators.cs:152-173). */
+int32_t orc_argmax(const float *values, size_t count)
+{
+    size_t best = 0;
+    for (size_t i = 1; i < count; ++i) {
+        if (values[i] > values[best]) {
+            best = i;
+        }
+    }
+    return (int32_t)best;
+}

@@ -85,6 +85,11 @@ _EXPORTS = {
     "syn_b200_matvec_static_capacity": (c_uint64, []),
     "syn_b200_gemm_scratch_bytes": (c_uint64, [c_uint64, c_uint64]),
     "syn_b200_gemm_dev": (c_int32, [c_void_p, c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32, c_void_p, c_uint64, c_void_p]),
+    "syn_b200_decoder_create": (c_int32, [c_void_p, POINTER(c_void_p)]),
+    "syn_b200_decoder_forward": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p, c_uint64]),
+    "syn_b200_decoder_forward_argmax": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p]),
+    "syn_b200_decoder_destroy": (None, [c_void_p]),
+    "syn_b200_decoder_kv_bytes": (c_uint64, [c_void_p]),
     "syn_b200_launch_count": (c_uint64, [c_uint32]),
     "syn_b200_device_faults": (c_uint32, [c_uint32]),
 }

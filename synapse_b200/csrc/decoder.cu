@@ -1,0 +1,768 @@
+// The decode step around the matrix products: a whole-decoder create / forward / destroy behind the same structs as
+// the reference's GPU ABI (DecoderDesc, DecoderLayerOffsets, BatchToken: native/synapse-gpu/src/Features/GpuKernels/
+// decoder.rs:61-141, ffi.rs:113-271), with the numeric contract of the reference's optimized CPU executor
+// (Qwen2/Qwen2CpuExecutor.cs:105-244): every projection multiplies Q8_0-quantised activations.
+//
+// One step = embedding rows, then per layer {RMSNorm + quantise, Q/K/V with bias, NeoX RoPE + KV append, softmax
+// attention over the slot's cache, quantise, output projection + residual, RMSNorm + quantise, gate, up with the
+// SwiGLU epilogue, quantise, down + residual}, output norm + quantise, vocabulary projection. Token, position and
+// slot are read by the kernels from a small device array, so the launch sequence of a step does not depend on
+// them: it is captured once per token count into a CUDA graph and replayed.
+#include <vector>
+
+#include "common.cuh"
+
+namespace syn {
+
+namespace {
+
+constexpr uint64_t kNoTensor = 0xFFFFFFFFFFFFFFFFull;
+constexpr uint32_t kMaxStepTokens = 8;
+
+struct BatchToken {
+    int32_t slot, token, position, logits_row;
+};
+
+// ---- small kernels ------------------------------------------------------------------------------------
+
+// Exact ggml-order decode of element i of a row (GgufLegacyBlocks.cs:85-92, GgufKQuantBlocks.cs:99-177).
+__device__ float decode_element(uint32_t type, const uint8_t *row, uint32_t i)
+{
+    if (type == kQ8_0) {
+        const uint8_t *block = row + (uint64_t)(i / 32) * 34;
+        const float d = __half2float(__ushort_as_half((unsigned short)(block[0] | (block[1] << 8))));
+        return d * (float)(signed char)block[2 + (i & 31)];
+    }
+    if (type == kQ4_K) {
+        const uint8_t *block = row + (uint64_t)(i / 256) * 144;
+        const uint32_t within = i & 255, chunk = within / 64, l = within & 31, high = (within >> 5) & 1;
+        const float d = __half2float(__ushort_as_half((unsigned short)(block[0] | (block[1] << 8))));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(block[2] | (block[3] << 8))));
+        const uint8_t *s = block + 4;
+        const uint32_t j = chunk * 2 + high;
+        uint32_t sc, mn;
+        if (j < 4) {
+            sc = s[j] & 63;
+            mn = s[j + 4] & 63;
+        } else {
+            sc = (s[j + 4] & 0x0F) | ((s[j - 4] >> 6) << 4);
+            mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
+        }
+        const uint32_t q = high ? (block[16 + chunk * 32 + l] >> 4) : (block[16 + chunk * 32 + l] & 0x0F);
+        return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)mn));
+    }
+    const uint8_t *block = row + (uint64_t)(i / 256) * 210;
+    const uint32_t within = i & 255, half = within / 128, rest = within & 127, quarter = rest / 32, l = rest & 31;
+    const uint8_t *ql = block + half * 64, *qh = block + 128 + half * 32;
+    const float d = __half2float(__ushort_as_half((unsigned short)(block[208] | (block[209] << 8))));
+    const int scale = (int)(signed char)block[192 + half * 8 + l / 16 + 2 * quarter];
+    const uint32_t low = (quarter & 1) ? ql[l + 32] : ql[l];
+    const uint32_t nibble = quarter < 2 ? (low & 0x0F) : (low >> 4);
+    const int q = (int)(nibble | (((qh[l] >> (2 * quarter)) & 3) << 4)) - 32;
+    return __fmul_rn(__fmul_rn(d, (float)scale), (float)q);
+}
+
+// hidden[t] = embedding row of tokens[t].token (Qwen2CpuExecutor.cs:110-117).
+__global__ void embed_kernel(const BatchToken *__restrict__ tokens, const uint8_t *__restrict__ table, uint32_t type, uint64_t row_bytes,
+                             uint32_t hidden, float *__restrict__ out)
+{
+    const uint8_t *row = table + (uint64_t)tokens[blockIdx.y].token * row_bytes;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) {
+        out[(uint64_t)blockIdx.y * hidden + i] = decode_element(type, row, i);
+    }
+}
+
+// RMSNorm with an FP64 sum of squares (Q8Operators.cs:101-123) fused with the Q8_0 activation quantiser
+// (Q8ActivationQuantizer.cs:34-57), one CTA per token. With `by_logits_row` the token's activations go to row
+// tokens[t].logits_row and tokens without a logits row are skipped (Qwen2CpuExecutor.cs:202-222).
+__global__ void __launch_bounds__(256)
+rmsnorm_quantize_kernel(const BatchToken *__restrict__ tokens, const float *__restrict__ x, const float *__restrict__ weight, float epsilon,
+                        uint32_t n, uint32_t rows, uint32_t by_logits_row, int8_t *__restrict__ codes, float *__restrict__ scales,
+                        int16_t *__restrict__ sums)
+{
+    __shared__ double partial[8];
+    __shared__ float shared_scale;
+    const uint32_t t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int target = (int)t;
+    if (by_logits_row) {
+        target = tokens[t].logits_row;
+        if (target < 0 || (uint32_t)target >= rows) {
+            return;
+        }
+    }
+    const float *row = x + (uint64_t)t * n;
+    double sum = 0.0;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const double v = (double)row[i];
+        sum += v * v;
+    }
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+    }
+    if (lane == 0) {
+        partial[warp] = sum;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double total = 0.0;
+        for (int w = 0; w < 8; ++w) {
+            total += partial[w];
+        }
+        shared_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float)(total / (double)n), epsilon)));
+    }
+    __syncthreads();
+    const float scale = shared_scale;
+    const uint32_t blocks = n / 32;
+    for (uint32_t b = warp; b < blocks; b += 8) {
+        const uint32_t i = b * 32 + lane;
+        const float value = __fmul_rn(__fmul_rn(row[i], scale), weight[i]);
+        float amax = fabsf(value);
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+        }
+        const float d = __fdiv_rn(amax, 127.0f);
+        const float inverse = d == 0.0f ? 0.0f : __fdiv_rn(1.0f, d);
+        const int code = __float2int_rn(__fmul_rn(value, inverse));
+        codes[(uint64_t)target * n + i] = (int8_t)code;
+        int group = code;
+        for (int offset = 8; offset > 0; offset >>= 1) {
+            group += __shfl_xor_sync(0xffffffffu, group, offset);
+        }
+        if ((lane & 15) == 0) {
+            sums[(uint64_t)target * (n / 16) + b * 2 + (lane >> 4)] = (int16_t)group;
+        }
+        if (lane == 0) {
+            scales[(uint64_t)target * blocks + b] = __half2float(__float2half_rn(d));
+        }
+    }
+}
+
+// NeoX rotation of every query and key head (first half against second half, Qwen2CpuState.cs:85-105) and the
+// append of the rotated key and the value to the slot's cache. Grid (heads + kv_heads, tokens), head_dim/2 threads.
+__global__ void rope_store_kernel(const BatchToken *__restrict__ tokens, float *__restrict__ q, float *__restrict__ k,
+                                  const float *__restrict__ v, const float *__restrict__ cosines, const float *__restrict__ sines,
+                                  float *__restrict__ keys, float *__restrict__ values, uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
+                                  uint32_t layer, uint32_t layers, uint32_t context)
+{
+    const uint32_t t = blockIdx.y, head = blockIdx.x, half = head_dim / 2, i = threadIdx.x;
+    const BatchToken token = tokens[t];
+    const float c = cosines[(uint64_t)token.position * half + i], s = sines[(uint64_t)token.position * half + i];
+    float *x = head < heads ? q + ((uint64_t)t * heads + head) * head_dim : k + ((uint64_t)t * kv_heads + (head - heads)) * head_dim;
+    const float a = x[i], b = x[i + half];
+    const float first = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)), second = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
+    x[i] = first;
+    x[i + half] = second;
+    if (head >= heads) {
+        const uint32_t kh = head - heads;
+        const uint64_t at = ((((uint64_t)token.slot * layers + layer) * kv_heads + kh) * context + token.position) * head_dim;
+        keys[at + i] = first;
+        keys[at + i + half] = second;
+        const float *vs = v + ((uint64_t)t * kv_heads + kh) * head_dim;
+        values[at + i] = vs[i];
+        values[at + i + half] = vs[i + half];
+    }
+}
+
+// Softmax attention of one token's query head over positions 0..position of its slot (Qwen2CpuAttention.cs:82-173).
+// Grid (heads, tokens), four warps; each warp walks every fourth position with an online softmax, the four partial
+// results are merged in shared memory. Head dimensions up to 256.
+__global__ void __launch_bounds__(128)
+attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict__ q, const float *__restrict__ keys,
+                 const float *__restrict__ values, float *__restrict__ out, uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t layer,
+                 uint32_t layers, uint32_t context, float scale)
+{
+    constexpr int kPerLane = 8;  // head_dim / 32, at most
+    __shared__ float merged[4][256 + 2];
+    const uint32_t t = blockIdx.y, head = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const BatchToken token = tokens[t];
+    const uint32_t kh = head / (heads / kv_heads), per_lane = head_dim / 32;
+    const float *query = q + ((uint64_t)t * heads + head) * head_dim;
+    const uint64_t base = (((uint64_t)token.slot * layers + layer) * kv_heads + kh) * context * head_dim;
+    float qv[kPerLane], acc[kPerLane];
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+        qv[j] = (uint32_t)j < per_lane ? query[lane + 32 * j] : 0.0f;
+        acc[j] = 0.0f;
+    }
+    float running_max = -INFINITY, running_sum = 0.0f;
+    for (int p = (int)warp; p <= token.position; p += 4) {
+        const float *key = keys + base + (uint64_t)p * head_dim;
+        float dot = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j) {
+            if ((uint32_t)j < per_lane) {
+                dot = fmaf(qv[j], key[lane + 32 * j], dot);
+            }
+        }
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            dot += __shfl_xor_sync(0xffffffffu, dot, offset);
+        }
+        const float score = dot * scale;
+        const float next_max = fmaxf(running_max, score);
+        const float rescale = expf(running_max - next_max), weight = expf(score - next_max);
+        const float *value = values + base + (uint64_t)p * head_dim;
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j) {
+            if ((uint32_t)j < per_lane) {
+                acc[j] = fmaf(weight, value[lane + 32 * j], acc[j] * rescale);
+            }
+        }
+        running_sum = running_sum * rescale + weight;
+        running_max = next_max;
+    }
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+        if ((uint32_t)j < per_lane) {
+            merged[warp][lane + 32 * j] = acc[j];
+        }
+    }
+    if (lane == 0) {
+        merged[warp][256] = running_max;
+        merged[warp][257] = running_sum;
+    }
+    __syncthreads();
+    float total_max = -INFINITY;
+    for (int w = 0; w < 4; ++w) {
+        total_max = fmaxf(total_max, merged[w][256]);
+    }
+    float total_sum = 0.0f;
+    for (int w = 0; w < 4; ++w) {
+        total_sum += merged[w][257] * expf(merged[w][256] - total_max);  // an idle warp has sum 0 and max -inf: exp(-inf) = 0
+    }
+    for (uint32_t i = threadIdx.x; i < head_dim; i += blockDim.x) {
+        float value = 0.0f;
+        for (int w = 0; w < 4; ++w) {
+            value += merged[w][i] * expf(merged[w][256] - total_max);
+        }
+        out[((uint64_t)t * heads + head) * head_dim + i] = value / total_sum;
+    }
+}
+
+// First maximum of each logits row (Q8Operators.cs:152-173): larger value wins, equal values keep the lower index.
+__global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ logits, uint32_t vocabulary, int32_t *__restrict__ out)
+{
+    __shared__ float best_value[32];
+    __shared__ int best_index[32];
+    const float *row = logits + (uint64_t)blockIdx.x * vocabulary;
+    float value = -INFINITY;
+    int index = 0x7fffffff;
+    for (uint32_t i = threadIdx.x; i < vocabulary; i += blockDim.x) {
+        const float v = row[i];
+        if (v > value || (v == value && (int)i < index)) {
+            value = v;
+            index = (int)i;
+        }
+    }
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        const float other_value = __shfl_xor_sync(0xffffffffu, value, offset);
+        const int other_index = __shfl_xor_sync(0xffffffffu, index, offset);
+        if (other_value > value || (other_value == value && other_index < index)) {
+            value = other_value;
+            index = other_index;
+        }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        best_value[threadIdx.x >> 5] = value;
+        best_index[threadIdx.x >> 5] = index;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
+            if (best_value[w] > value || (best_value[w] == value && best_index[w] < index)) {
+                value = best_value[w];
+                index = best_index[w];
+            }
+        }
+        out[blockIdx.x] = index;
+    }
+}
+
+struct Layer {
+    syn_b200_matrix *query = nullptr, *key = nullptr, *value = nullptr, *output = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
+    float *attention_norm = nullptr, *feed_forward_norm = nullptr, *query_bias = nullptr, *key_bias = nullptr, *value_bias = nullptr;
+};
+
+}  // namespace
+
+}  // namespace syn
+
+using namespace syn;
+
+struct syn_b200_decoder {
+    syn_b200_decoder_desc shape{};  // scalars only; the pointers inside are not kept
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    std::vector<Layer> layers;
+    syn_b200_matrix *embedding = nullptr, *output = nullptr;
+    float *output_norm = nullptr, *cosines = nullptr, *sines = nullptr;
+    std::vector<void *> owned;  // every cudaMalloc'd block, for destroy
+    float *hidden = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attention = nullptr, *gate = nullptr, *ff = nullptr, *logits = nullptr;
+    void *act_hidden = nullptr, *act_ffn = nullptr;
+    float *keys = nullptr, *values = nullptr;
+    syn::BatchToken *device_tokens = nullptr, *host_tokens = nullptr;
+    int32_t *device_argmax = nullptr, *host_argmax = nullptr;
+    cudaGraphExec_t graphs[kMaxStepTokens + 1] = {};
+    uint64_t launches_per_step[kMaxStepTokens + 1] = {};
+    uint32_t steps_seen[kMaxStepTokens + 1] = {};  // the first step of a token count runs uncaptured (one-time kernel set-up)
+};
+
+namespace syn {
+namespace {
+
+template <class T>
+int32_t device_alloc(syn_b200_decoder *d, T **out, uint64_t count)
+{
+    void *p = nullptr;
+    cudaError_t error = cudaMalloc(&p, count * sizeof(T) + 256);
+    if (error != cudaSuccess) {
+        cudaGetLastError();
+        return cuda_fail(error, "allocating decoder buffers");
+    }
+    d->owned.push_back(p);
+    *out = static_cast<T *>(p);
+    return SYN_B200_OK;
+}
+
+int32_t upload_floats(syn_b200_decoder *d, const syn_b200_decoder_desc &desc, uint64_t offset, uint64_t count, const char *name, float **out)
+{
+    if (offset == kNoTensor) {
+        *out = nullptr;
+        return SYN_B200_OK;
+    }
+    if (offset % 4 != 0 || offset > desc.weights_length || count * 4 > desc.weights_length - offset) {
+        return fail(SYN_B200_INVALID_ARGUMENT, std::string("tensor ") + name + " lies outside the weights or is misaligned");
+    }
+    int32_t status = device_alloc(d, out, count);
+    if (status != SYN_B200_OK) {
+        return status;
+    }
+    cudaError_t error = cudaMemcpy(*out, desc.weights + offset, count * 4, cudaMemcpyHostToDevice);
+    return error == cudaSuccess ? SYN_B200_OK : cuda_fail(error, "uploading a decoder tensor");
+}
+
+int32_t upload_matrix(const syn_b200_decoder_desc &desc, uint64_t offset, uint32_t type, uint64_t rows, uint64_t columns, uint32_t flags,
+                      const char *name, syn_b200_matrix **out)
+{
+    const uint64_t values = block_values(type);
+    if (values == 0) {
+        return fail(SYN_B200_UNAVAILABLE, std::string("tensor ") + name + " uses GGML type " + std::to_string(type) + ", which is not implemented");
+    }
+    if (columns % values != 0) {
+        return fail(SYN_B200_UNAVAILABLE, std::string("tensor ") + name + " has " + std::to_string(columns) + " columns, not a multiple of its " +
+                                              std::to_string(values) + "-value blocks");
+    }
+    const uint64_t bytes = rows * (columns / values) * block_bytes(type);
+    if (offset % 2 != 0 || offset > desc.weights_length || bytes > desc.weights_length - offset) {
+        return fail(SYN_B200_INVALID_ARGUMENT, std::string("tensor ") + name + " lies outside the weights");
+    }
+    return syn_b200_matrix_create(desc.weights + offset, type, rows, columns, flags, out);
+}
+
+cudaError_t product(syn_b200_decoder *d, const syn_b200_matrix *m, const void *act, uint32_t tokens, float *y, uint64_t out_stride,
+                    const Epilogue &epilogue)
+{
+    MatvecArgs args{};
+    args.matrix = m;
+    args.row_start = 0;
+    args.row_count = m->rows;
+    args.tokens = tokens;
+    args.act = act_view(act, tokens, m->columns);
+    args.act_ready = true;
+    args.y = y;
+    args.out_stride = out_stride;
+    args.mode = SYN_B200_MODE_XQ8;
+    args.epilogue = SYN_B200_EPILOGUE_STORE;
+    args.fused = epilogue;
+    return launch_matvec(args, d->stream);
+}
+
+cudaError_t quantize(syn_b200_decoder *d, const float *x, uint32_t tokens, uint64_t columns, void *act)
+{
+    const ActLayout layout = act_layout(tokens, columns);
+    uint8_t *base = static_cast<uint8_t *>(act);
+    return launch_quantize(x, tokens, columns, columns, reinterpret_cast<int8_t *>(base + layout.codes),
+                           reinterpret_cast<float *>(base + layout.scales), reinterpret_cast<int16_t *>(base + layout.sums), d->stream);
+}
+
+cudaError_t norm_quantize(syn_b200_decoder *d, const float *x, const float *weight, uint32_t tokens, uint32_t rows, bool by_logits_row, void *act)
+{
+    const uint32_t n = d->shape.hidden;
+    const ActLayout layout = act_layout(rows, n);
+    uint8_t *base = static_cast<uint8_t *>(act);
+    rmsnorm_quantize_kernel<<<tokens, 256, 0, d->stream>>>(d->device_tokens, x, weight, d->shape.rms_epsilon, n, rows, by_logits_row ? 1u : 0u,
+                                                           reinterpret_cast<int8_t *>(base + layout.codes),
+                                                           reinterpret_cast<float *>(base + layout.scales),
+                                                           reinterpret_cast<int16_t *>(base + layout.sums));
+    count_launch();
+    return cudaGetLastError();
+}
+
+#define SYN_TRY(expression)                \
+    do {                                   \
+        cudaError_t syn_error = (expression); \
+        if (syn_error != cudaSuccess) {    \
+            return syn_error;              \
+        }                                  \
+    } while (0)
+
+// Queues one step for `count` tokens (already in device_tokens) on the decoder's stream.
+cudaError_t enqueue_step(syn_b200_decoder *d, uint32_t count, uint32_t logits_rows)
+{
+    const syn_b200_decoder_desc &s = d->shape;
+    const uint32_t hidden = s.hidden, kvw = s.kv_heads * s.head_dim, ffn = s.feed_forward;
+    embed_kernel<<<dim3((hidden + 255) / 256, count), 256, 0, d->stream>>>(d->device_tokens, d->embedding->data, d->embedding->type,
+                                                                          d->embedding->row_bytes, hidden, d->hidden);
+    count_launch();
+    SYN_TRY(cudaGetLastError());
+    for (uint32_t l = 0; l < s.layer_count; ++l) {
+        const Layer &L = d->layers[l];
+        SYN_TRY(norm_quantize(d, d->hidden, L.attention_norm, count, count, false, d->act_hidden));
+        Epilogue bias;
+        bias.bias = L.query_bias;
+        SYN_TRY(product(d, L.query, d->act_hidden, count, d->q, hidden, bias));
+        bias.bias = L.key_bias;
+        SYN_TRY(product(d, L.key, d->act_hidden, count, d->k, kvw, bias));
+        bias.bias = L.value_bias;
+        SYN_TRY(product(d, L.value, d->act_hidden, count, d->v, kvw, bias));
+        rope_store_kernel<<<dim3(s.heads + s.kv_heads, count), s.head_dim / 2, 0, d->stream>>>(
+            d->device_tokens, d->q, d->k, d->v, d->cosines, d->sines, d->keys, d->values, s.heads, s.kv_heads, s.head_dim, l, s.layer_count, s.context);
+        count_launch();
+        attention_kernel<<<dim3(s.heads, count), 128, 0, d->stream>>>(d->device_tokens, d->q, d->keys, d->values, d->attention, s.heads, s.kv_heads,
+                                                                      s.head_dim, l, s.layer_count, s.context, 1.0f / sqrtf((float)s.head_dim));
+        count_launch();
+        SYN_TRY(cudaGetLastError());
+        SYN_TRY(quantize(d, d->attention, count, hidden, d->act_hidden));
+        Epilogue residual;
+        residual.accumulate = 1;
+        SYN_TRY(product(d, L.output, d->act_hidden, count, d->hidden, hidden, residual));
+        SYN_TRY(norm_quantize(d, d->hidden, L.feed_forward_norm, count, count, false, d->act_hidden));
+        SYN_TRY(product(d, L.gate, d->act_hidden, count, d->gate, ffn, Epilogue{}));
+        Epilogue swiglu;
+        swiglu.gate = d->gate;
+        swiglu.gate_stride = ffn;
+        SYN_TRY(product(d, L.up, d->act_hidden, count, d->ff, ffn, swiglu));
+        SYN_TRY(quantize(d, d->ff, count, ffn, d->act_ffn));
+        SYN_TRY(product(d, L.down, d->act_ffn, count, d->hidden, hidden, residual));
+    }
+    if (logits_rows > 0) {
+        SYN_TRY(norm_quantize(d, d->hidden, d->output_norm, count, logits_rows, true, d->act_hidden));
+        SYN_TRY(product(d, d->output, d->act_hidden, logits_rows, d->logits, s.vocabulary, Epilogue{}));
+        argmax_kernel<<<logits_rows, 1024, 0, d->stream>>>(d->logits, s.vocabulary, d->device_argmax);
+        count_launch();
+        SYN_TRY(cudaGetLastError());
+    }
+    return cudaSuccess;
+}
+
+// Validates a step like Qwen2CpuExecutor.Validate (Qwen2CpuExecutor.cs:141-163) and returns its logits rows.
+int32_t validate_step(const syn_b200_decoder *d, const syn_b200_batch_token *tokens, uint64_t count, uint32_t *logits_rows)
+{
+    const syn_b200_decoder_desc &s = d->shape;
+    if (count == 0 || count > s.step_tokens) {
+        return fail(SYN_B200_INVALID_ARGUMENT, "a step holds 1.." + std::to_string(s.step_tokens) + " tokens, not " + std::to_string(count));
+    }
+    uint32_t rows = 0;
+    for (uint64_t i = 0; i < count; ++i) {
+        const syn_b200_batch_token &t = tokens[i];
+        if (t.slot < 0 || (uint32_t)t.slot >= s.session_slots || t.token < 0 || (uint32_t)t.token >= s.vocabulary || t.position < 0 ||
+            (uint32_t)t.position >= s.context || t.logits_row >= (int32_t)s.logits_rows) {
+            return fail(SYN_B200_INVALID_ARGUMENT, "invalid batch token " + std::to_string(i));
+        }
+        if (t.logits_row >= 0) {
+            if ((uint32_t)t.logits_row != rows) {
+                return fail(SYN_B200_INVALID_ARGUMENT, "logits rows must be numbered 0, 1, ... in token order");
+            }
+            ++rows;
+        }
+    }
+    *logits_rows = rows;
+    return SYN_B200_OK;
+}
+
+int32_t run_step(syn_b200_decoder *d, const syn_b200_batch_token *tokens, uint64_t count, uint32_t *rows_out)
+{
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device != d->device) {
+        cudaGetLastError();
+        return fail(SYN_B200_INVALID_ARGUMENT, "the decoder lives on device " + std::to_string(d->device) + ", which is not the calling thread's current device");
+    }
+    uint32_t rows = 0;
+    int32_t status = validate_step(d, tokens, count, &rows);
+    if (status != SYN_B200_OK) {
+        return status;
+    }
+    *rows_out = rows;
+    for (uint64_t i = 0; i < count; ++i) {
+        d->host_tokens[i] = syn::BatchToken{tokens[i].slot, tokens[i].token, tokens[i].position, tokens[i].logits_row};
+    }
+    // Steps in which every token asks for logits (plain decoding) replay a graph captured on their second occurrence;
+    // anything else is enqueued kernel by kernel.
+    const bool graphable = true;
+    cudaError_t error = cudaSuccess;
+    if (graphable && rows == count && d->steps_seen[count]++ > 0) {
+        if (!d->graphs[count]) {
+            fault_word_device();
+            const uint64_t before = syn_b200_launch_count(0);
+            cudaGraph_t graph = nullptr;
+            error = cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeThreadLocal);
+            if (error == cudaSuccess) {
+                error = cudaMemcpyAsync(d->device_tokens, d->host_tokens, count * sizeof(syn::BatchToken), cudaMemcpyHostToDevice, d->stream);
+                if (error == cudaSuccess) {
+                    error = enqueue_step(d, (uint32_t)count, rows);
+                }
+                cudaError_t end = cudaStreamEndCapture(d->stream, &graph);
+                if (error == cudaSuccess) {
+                    error = end;
+                }
+            }
+            if (error == cudaSuccess) {
+                error = cudaGraphInstantiate(&d->graphs[count], graph, 0);
+            }
+            if (graph) {
+                cudaGraphDestroy(graph);
+            }
+            if (error != cudaSuccess) {
+                cudaGetLastError();
+                return cuda_fail(error, "capturing the decode step");
+            }
+            d->launches_per_step[count] = syn_b200_launch_count(0) - before;
+        } else {
+            for (uint64_t i = 0; i < d->launches_per_step[count]; ++i) {
+                count_launch();
+            }
+        }
+        error = cudaGraphLaunch(d->graphs[count], d->stream);
+    } else {
+        error = cudaMemcpyAsync(d->device_tokens, d->host_tokens, count * sizeof(syn::BatchToken), cudaMemcpyHostToDevice, d->stream);
+        if (error == cudaSuccess) {
+            error = enqueue_step(d, (uint32_t)count, rows);
+        }
+    }
+    if (error != cudaSuccess) {
+        cudaGetLastError();
+        return cuda_fail(error, "running the decode step");
+    }
+    return SYN_B200_OK;
+}
+
+}  // namespace
+}  // namespace syn
+
+extern "C" {
+
+int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_decoder **out)
+{
+    if (!desc || !out) {
+        return fail(SYN_B200_NULL_POINTER, "model description or output");
+    }
+    *out = nullptr;
+    if (!desc->weights || !desc->layers || !desc->rope_cosines || !desc->rope_sines) {
+        return fail(SYN_B200_NULL_POINTER, "model description");
+    }
+    try {
+        const syn_b200_decoder_desc &s = *desc;
+        if (s.layer_count == 0 || s.hidden == 0 || s.feed_forward == 0 || s.heads == 0 || s.kv_heads == 0 || s.head_dim == 0 ||
+            s.vocabulary == 0 || s.context == 0 || s.session_slots == 0 || s.step_tokens == 0 || s.logits_rows == 0) {
+            return fail(SYN_B200_INVALID_ARGUMENT, "every decoder dimension must be positive");
+        }
+        if (s.heads % s.kv_heads != 0 || s.heads * s.head_dim != s.hidden || s.head_dim % 32 != 0 || s.head_dim > 256 || s.hidden % 32 != 0 ||
+            s.feed_forward % 32 != 0) {
+            return fail(SYN_B200_UNAVAILABLE, "unsupported head geometry: heads * head_dim must equal hidden, head_dim a multiple of 32 up to 256");
+        }
+        if (s.step_tokens > kMaxStepTokens || s.logits_rows > s.step_tokens) {
+            return fail(SYN_B200_UNAVAILABLE, "a step holds at most " + std::to_string(kMaxStepTokens) + " tokens on this backend");
+        }
+        if (s.kv_precision != 0 || s.rope_layout != 0 || s.activation != 0) {
+            return fail(SYN_B200_UNAVAILABLE, "only FP32 KV, the NeoX rotary layout and SwiGLU are implemented");
+        }
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(SYN_B200_UNAVAILABLE, "no usable CUDA device");
+        }
+        syn_b200_decoder *d = new syn_b200_decoder();
+        d->shape = s;
+        d->shape.weights = nullptr;
+        d->shape.layers = nullptr;
+        d->shape.rope_cosines = d->shape.rope_sines = nullptr;
+        d->device = device;
+        int32_t status = SYN_B200_OK;
+        auto fail_out = [&](int32_t code) {
+            syn_b200_decoder_destroy(d);
+            return code;
+        };
+        const uint32_t kvw = s.kv_heads * s.head_dim, half = s.head_dim / 2;
+        // the embedding is read row by row in its file layout; the projections take the load-time repack
+        status = upload_matrix(s, s.token_embedding, s.embedding_encoding, s.vocabulary, s.hidden, 0, "token_embd", &d->embedding);
+        if (status == SYN_B200_OK) status = upload_matrix(s, s.output, s.output_encoding, s.vocabulary, s.hidden, SYN_B200_REPACK, "output", &d->output);
+        if (status == SYN_B200_OK) status = upload_floats(d, s, s.output_norm, s.hidden, "output_norm", &d->output_norm);
+        if (status != SYN_B200_OK) return fail_out(status);
+        d->layers.resize(s.layer_count);
+        for (uint32_t l = 0; l < s.layer_count; ++l) {
+            const syn_b200_layer_offsets &o = s.layers[l];
+            Layer &L = d->layers[l];
+            auto type = [&](int index) { return (uint32_t)((o.encodings >> (4 * index)) & 0xF); };
+            if (o.query_norm != kNoTensor || o.key_norm != kNoTensor) {
+                return fail_out(fail(SYN_B200_UNAVAILABLE, "per-head query/key norms are not implemented"));
+            }
+            status = upload_floats(d, s, o.attention_norm, s.hidden, "attn_norm", &L.attention_norm);
+            if (status == SYN_B200_OK) status = upload_floats(d, s, o.feed_forward_norm, s.hidden, "ffn_norm", &L.feed_forward_norm);
+            if (status == SYN_B200_OK) status = upload_floats(d, s, o.query_bias, s.hidden, "attn_q.bias", &L.query_bias);
+            if (status == SYN_B200_OK) status = upload_floats(d, s, o.key_bias, kvw, "attn_k.bias", &L.key_bias);
+            if (status == SYN_B200_OK) status = upload_floats(d, s, o.value_bias, kvw, "attn_v.bias", &L.value_bias);
+            if (status == SYN_B200_OK) status = upload_matrix(s, o.query, type(0), s.hidden, s.hidden, SYN_B200_REPACK, "attn_q", &L.query);
+            if (status == SYN_B200_OK) status = upload_matrix(s, o.key, type(1), kvw, s.hidden, SYN_B200_REPACK, "attn_k", &L.key);
+            if (status == SYN_B200_OK) status = upload_matrix(s, o.value, type(2), kvw, s.hidden, SYN_B200_REPACK, "attn_v", &L.value);
+            if (status == SYN_B200_OK) status = upload_matrix(s, o.attention_output, type(3), s.hidden, s.hidden, SYN_B200_REPACK, "attn_output", &L.output);
+            if (status == SYN_B200_OK) status = upload_matrix(s, o.gate, type(4), s.feed_forward, s.hidden, SYN_B200_REPACK, "ffn_gate", &L.gate);
+            if (status == SYN_B200_OK) status = upload_matrix(s, o.up, type(5), s.feed_forward, s.hidden, SYN_B200_REPACK, "ffn_up", &L.up);
+            if (status == SYN_B200_OK) status = upload_matrix(s, o.down, type(6), s.hidden, s.feed_forward, SYN_B200_REPACK, "ffn_down", &L.down);
+            if (status != SYN_B200_OK) return fail_out(status);
+        }
+        const uint64_t T = s.step_tokens;
+        const uint64_t cache = (uint64_t)s.session_slots * s.layer_count * s.kv_heads * s.context * s.head_dim;
+        uint8_t *act_hidden = nullptr, *act_ffn = nullptr;
+        status = device_alloc(d, &d->cosines, (uint64_t)s.context * half);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->sines, (uint64_t)s.context * half);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->hidden, T * s.hidden);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->q, T * s.hidden);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->k, T * kvw);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->v, T * kvw);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->attention, T * s.hidden);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->gate, T * s.feed_forward);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->ff, T * s.feed_forward);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->logits, (uint64_t)s.logits_rows * s.vocabulary);
+        if (status == SYN_B200_OK) status = device_alloc(d, &act_hidden, act_layout(T, s.hidden).total);
+        if (status == SYN_B200_OK) status = device_alloc(d, &act_ffn, act_layout(T, s.feed_forward).total);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->keys, cache);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->values, cache);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->device_tokens, T);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->device_argmax, T);
+        if (status != SYN_B200_OK) return fail_out(status);
+        d->act_hidden = act_hidden;
+        d->act_ffn = act_ffn;
+        cudaError_t error = cudaMemcpy(d->cosines, s.rope_cosines, (uint64_t)s.context * half * 4, cudaMemcpyHostToDevice);
+        if (error == cudaSuccess) error = cudaMemcpy(d->sines, s.rope_sines, (uint64_t)s.context * half * 4, cudaMemcpyHostToDevice);
+        if (error == cudaSuccess) error = cudaMemset(d->keys, 0, cache * 4);
+        if (error == cudaSuccess) error = cudaMemset(d->values, 0, cache * 4);
+        if (error == cudaSuccess) error = cudaHostAlloc(reinterpret_cast<void **>(&d->host_tokens), T * sizeof(syn::BatchToken), cudaHostAllocDefault);
+        if (error == cudaSuccess) error = cudaHostAlloc(reinterpret_cast<void **>(&d->host_argmax), T * sizeof(int32_t), cudaHostAllocDefault);
+        if (error == cudaSuccess) error = cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking);
+        if (error != cudaSuccess) {
+            cudaGetLastError();
+            return fail_out(cuda_fail(error, "setting up the decoder"));
+        }
+        *out = d;
+        return SYN_B200_OK;
+    } catch (...) {
+        return fail(SYN_B200_INTERNAL, "exception at the ABI");
+    }
+}
+
+void syn_b200_decoder_destroy(syn_b200_decoder *d)
+{
+    if (!d) {
+        return;
+    }
+    if (d->stream) {
+        cudaStreamSynchronize(d->stream);
+    }
+    for (cudaGraphExec_t graph : d->graphs) {
+        if (graph) {
+            cudaGraphExecDestroy(graph);
+        }
+    }
+    for (Layer &L : d->layers) {
+        syn_b200_matrix_destroy(L.query);
+        syn_b200_matrix_destroy(L.key);
+        syn_b200_matrix_destroy(L.value);
+        syn_b200_matrix_destroy(L.output);
+        syn_b200_matrix_destroy(L.gate);
+        syn_b200_matrix_destroy(L.up);
+        syn_b200_matrix_destroy(L.down);
+    }
+    syn_b200_matrix_destroy(d->embedding);
+    syn_b200_matrix_destroy(d->output);
+    for (void *p : d->owned) {
+        cudaFree(p);
+    }
+    if (d->host_tokens) cudaFreeHost(d->host_tokens);
+    if (d->host_argmax) cudaFreeHost(d->host_argmax);
+    if (d->stream) cudaStreamDestroy(d->stream);
+    delete d;
+}
+
+int32_t syn_b200_decoder_forward(syn_b200_decoder *d, const syn_b200_batch_token *tokens, uint64_t count, float *logits, uint64_t logits_capacity)
+{
+    if (!d || !tokens || !logits) {
+        return fail(SYN_B200_NULL_POINTER, "model, tokens, or logits");
+    }
+    try {
+        uint32_t rows = 0;
+        int32_t status = run_step(d, tokens, count, &rows);
+        if (status != SYN_B200_OK) {
+            return status;
+        }
+        if ((uint64_t)rows * d->shape.vocabulary > logits_capacity) {
+            cudaStreamSynchronize(d->stream);
+            return fail(SYN_B200_INVALID_ARGUMENT, "the logits buffer holds " + std::to_string(logits_capacity) + " floats, the step needs " +
+                                                       std::to_string((uint64_t)rows * d->shape.vocabulary));
+        }
+        cudaError_t error = cudaSuccess;
+        if (rows > 0) {
+            error = cudaMemcpyAsync(logits, d->logits, (uint64_t)rows * d->shape.vocabulary * 4, cudaMemcpyDeviceToHost, d->stream);
+        }
+        if (error == cudaSuccess) {
+            error = cudaStreamSynchronize(d->stream);
+        }
+        if (error != cudaSuccess) {
+            cudaGetLastError();
+            return cuda_fail(error, "reading the logits");
+        }
+        return SYN_B200_OK;
+    } catch (...) {
+        return fail(SYN_B200_INTERNAL, "exception at the ABI");
+    }
+}
+
+int32_t syn_b200_decoder_forward_argmax(syn_b200_decoder *d, const syn_b200_batch_token *tokens, uint64_t count, int32_t *argmax)
+{
+    if (!d || !tokens || !argmax) {
+        return fail(SYN_B200_NULL_POINTER, "model, tokens, or argmax");
+    }
+    try {
+        uint32_t rows = 0;
+        int32_t status = run_step(d, tokens, count, &rows);
+        if (status != SYN_B200_OK) {
+            return status;
+        }
+        cudaError_t error = cudaSuccess;
+        if (rows > 0) {
+            error = cudaMemcpyAsync(d->host_argmax, d->device_argmax, rows * sizeof(int32_t), cudaMemcpyDeviceToHost, d->stream);
+        }
+        if (error == cudaSuccess) {
+            error = cudaStreamSynchronize(d->stream);
+        }
+        if (error != cudaSuccess) {
+            cudaGetLastError();
+            return cuda_fail(error, "reading the argmax");
+        }
+        for (uint32_t r = 0; r < rows; ++r) {
+            argmax[r] = d->host_argmax[r];
+        }
+        return SYN_B200_OK;
+    } catch (...) {
+        return fail(SYN_B200_INTERNAL, "exception at the ABI");
+    }
+}
+
+uint64_t syn_b200_decoder_kv_bytes(const syn_b200_decoder *d)
+{
+    if (!d) {
+        return 0;
+    }
+    const syn_b200_decoder_desc &s = d->shape;
+    return 2ull * s.session_slots * s.layer_count * s.kv_heads * s.context * s.head_dim * 4;
+}
+
+}  // extern "C"
