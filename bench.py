@@ -229,19 +229,25 @@ def main():
     lib = sb.library()
     lib.probe()
 
-    # ---- weights: every rank holds rows [rank*R/world, (rank+1)*R/world) of every matrix -------------------
-    specs = model_matrices(args.layers)
+    # ---- weights: one random-init model image (the stand-in for the mapped GGUF file); every rank holds rows
+    # [rank*R/world, (rank+1)*R/world) of every projection matrix ------------------------------------------------
+    from synapse_b200 import decoder as dec
+
+    shape = dict(dec.QWEN25_7B, layers=args.layers)
+    image = dec.ModelImage(**shape, context=64, matrix_types=dec.Q4KM_TYPES, embedding_type=synth.Q4_K, output_type=synth.Q4_K, seed=100,
+                           bias=True)
+    leaf_fields = {"attn_q": "query", "attn_k": "key", "attn_v": "value", "attn_o": "attention_output", "ffn_gate": "gate", "ffn_up": "up",
+                   "ffn_down": "down"}
     matrices = []
     total_bytes = 0
-    for index, (name, ggml_type, rows, columns) in enumerate(specs):
+    for name, ggml_type, rows, columns in model_matrices(args.layers):
+        leaf = name.split(".")[-1]
+        base = image.output if leaf == "lm_head" else getattr(image.layers[int(name.split(".")[1])], leaf_fields[leaf])
         _, shard_rows = sharding.shard_rows(rows, world, rank)
         offset, count = sharding.shard_bytes(ggml_type, rows, columns, world, rank)
-        row_bytes = synth.row_bytes(ggml_type, columns)
-        blocks = synth.matrix(ggml_type, rows, columns, seed=100 + index, name=name)
-        shard = blocks[offset:offset + count]
+        shard = image.weights[base + offset:base + offset + count]
         matrices.append((name, ggml_type, rows, columns, shard_rows, sb.QuantizedMatrix(shard, ggml_type, shard_rows, columns)))
-        total_bytes += rows * row_bytes
-        del blocks, shard
+        total_bytes += rows * synth.row_bytes(ggml_type, columns)
 
     # ---- activations (resident) and outputs -----------------------------------------------------------------
     x_host = {3584: synth.activations(1, 3584, seed=5), 18944: synth.activations(1, 18944, seed=6)}
@@ -401,7 +407,9 @@ def main():
 
     # ---- end to end through the host-pointer C ABI: pinned host x in, host y out, per matrix ----------------
     e2e = None
+    per_matrix = None
     if not args.no_e2e:
+        # (a) the per-projection boundary: one host call per matrix, pinned host x in, host y out
         host_x = {k: torch.from_numpy(v).pin_memory() for k, v in x_host.items()}
         host_y = {m[4]: torch.zeros(m[4], dtype=torch.float32).pin_memory() for m in matrices}
         torch.cuda.synchronize()
@@ -426,9 +434,68 @@ def main():
             slowest = torch.tensor([e2e_seconds], dtype=torch.float64, device=device)
             dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
             e2e_seconds = float(slowest.item())
-        e2e = {"value": total_bytes * e2e_steps / e2e_seconds / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": e2e_seconds / e2e_steps * 1e3, "steps": e2e_steps,
-               "api": "syn_b200_matvec (host FP32 activations in, host FP32 outputs out, one call per matrix)"}
+        per_matrix = {"value": total_bytes * e2e_steps / e2e_seconds / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                      "ms_per_step": e2e_seconds / e2e_steps * 1e3, "steps": e2e_steps,
+                      "api": "syn_b200_matvec (host FP32 activations in, host FP32 outputs out, one call per matrix)"}
+        e2e = per_matrix
+        if world == 1:
+            # (b) the per-step boundary a generation loop uses: syn_b200_decoder_forward, host tokens in, host logits out.
+            # The step runs the same 197 projections plus the kernels between them (norms, rotary, attention, SwiGLU).
+            for entry in matrices:
+                entry[5].close()
+            with dec.Decoder(image) as model:
+                token = 11
+                for position in range(3):
+                    token = int(np.argmax(model.decode(token, position)))
+                torch.cuda.synchronize()
+                decode_steps = max(3, min(args.steps, 20))
+                start = time.perf_counter()
+                for position in range(3, 3 + decode_steps):
+                    token = int(np.argmax(model.decode(token, position)))
+                decode_seconds = time.perf_counter() - start
+            e2e = {"value": total_bytes * decode_steps / decode_seconds / 1e9, "unit": UNIT, "h2d_bytes_per_step": 16,
+                   "d2h_bytes_per_step": 4 * shape["vocabulary"], "ms_per_step": decode_seconds / decode_steps * 1e3, "steps": decode_steps,
+                   "tokens_per_s": decode_steps / decode_seconds,
+                   "api": "syn_b200_decoder_forward (one call per decoded token: host BatchToken in, host logits out, greedy pick on the host)"}
+
+    extras = None
+    if world == 1 and not args.no_e2e:
+        extras = {}
+        # prefill: the tensor-core product on one gate matrix (18944 x 3584 Q4_K) at 2048 tokens
+        gate_offset = image.layers[0].gate
+        gate_bytes = 18944 * synth.row_bytes(synth.Q4_K, 3584)
+        tokens = 2048
+        with sb.QuantizedMatrix(image.weights[gate_offset:gate_offset + gate_bytes], synth.Q4_K, 18944, 3584) as gate:
+            xs = torch.randn(tokens, 3584, device=device)
+            ys = torch.empty(tokens, 18944, device=device)
+            need = lib.gemm_scratch_bytes(tokens, 3584)
+            work = torch.empty(need + 256, dtype=torch.uint8, device=device)
+            work_ptr = (work.data_ptr() + 255) // 256 * 256
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    gate.gemm_device(xs.data_ptr(), tokens, 3584, ys.data_ptr(), 18944, work_ptr, need, stream=stream.cuda_stream)
+                g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                g0.record(stream)
+                for _ in range(10):
+                    gate.gemm_device(xs.data_ptr(), tokens, 3584, ys.data_ptr(), 18944, work_ptr, need, stream=stream.cuda_stream)
+                g1.record(stream)
+                stream.synchronize()
+            gemm_ms = g0.elapsed_time(g1) / 10
+            extras["prefill"] = {"workload": "Q4_K 18944x3584 x 2048 tokens, fp16 operands, FP32 accumulate (activation conversion included)",
+                                 "tflops": 2.0 * tokens * 18944 * 3584 / (gemm_ms * 1e-3) / 1e12, "ms": gemm_ms}
+            del xs, ys, work
+        # config 1: the Qwen2.5-0.5B-shaped all-Q8_0 decode step through the decoder, greedy pick on the device
+        small = dec.ModelImage(**dec.QWEN25_05B, context=64, matrix_types=dec.Q8_TYPES, seed=101)
+        with dec.Decoder(small) as model:
+            token = 11
+            for position in range(3):
+                token = model.forward_argmax([(0, token, position, 0)])[0]
+            start = time.perf_counter()
+            for position in range(3, 35):
+                token = model.forward_argmax([(0, token, position, 0)])[0]
+            seconds = time.perf_counter() - start
+        extras["qwen2.5-0.5b_q8_0_decode"] = {"tokens_per_s": 32 / seconds, "weight_gbs": small.matrix_bytes * 32 / seconds / 1e9,
+                                               "api": "syn_b200_decoder_forward_argmax, one call per token"}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -444,7 +511,7 @@ def main():
                            "quantize": args.quantize, "branches": "serial" if args.serial else "q|k|v and gate|up on parallel graph branches",
                            "l2": "weights per step exceed L2 35x, no flush", "parallelism": f"row-shard x{world}" if world > 1 else "single gpu",
                            "tokens_per_s": 1e3 / ms_per_step},
-                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_per_matrix_calls": per_matrix, "extras": extras, "clocks": clocks,
                 "gpu_launches": int(launches_per_step * args.steps)}
         print(json.dumps(line))
     if world > 1:
