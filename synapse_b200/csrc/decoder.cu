@@ -66,6 +66,8 @@ __device__ float decode_element(uint32_t type, const uint8_t *row, uint32_t i)
 __global__ void embed_kernel(const BatchToken *__restrict__ tokens, const uint8_t *__restrict__ table, uint32_t type, uint64_t row_bytes,
                              uint32_t hidden, float *__restrict__ out)
 {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint8_t *row = table + (uint64_t)tokens[blockIdx.y].token * row_bytes;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) {
         out[(uint64_t)blockIdx.y * hidden + i] = decode_element(type, row, i);
@@ -82,6 +84,8 @@ rmsnorm_quantize_kernel(const BatchToken *__restrict__ tokens, const float *__re
 {
     __shared__ double partial[8];
     __shared__ float shared_scale;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int target = (int)t;
     if (by_logits_row) {
@@ -144,6 +148,8 @@ __global__ void rope_store_kernel(const BatchToken *__restrict__ tokens, float *
                                   float *__restrict__ keys, float *__restrict__ values, uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
                                   uint32_t layer, uint32_t layers, uint32_t context)
 {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t t = blockIdx.y, head = blockIdx.x, half = head_dim / 2, i = threadIdx.x;
     const BatchToken token = tokens[t];
     const float c = cosines[(uint64_t)token.position * half + i], s = sines[(uint64_t)token.position * half + i];
@@ -168,11 +174,13 @@ __global__ void rope_store_kernel(const BatchToken *__restrict__ tokens, float *
 // results are merged in shared memory. Head dimensions up to 256.
 __global__ void __launch_bounds__(128)
 attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict__ q, const float *__restrict__ keys,
-                 const float *__restrict__ values, float *__restrict__ out, uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t layer,
-                 uint32_t layers, uint32_t context, float scale)
+                 const float *__restrict__ values, uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t layer, uint32_t layers,
+                 uint32_t context, float scale, int8_t *__restrict__ codes, float *__restrict__ scales, int16_t *__restrict__ sums)
 {
     constexpr int kPerLane = 8;  // head_dim / 32, at most
     __shared__ float merged[4][256 + 2];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t t = blockIdx.y, head = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const BatchToken token = tokens[t];
     const uint32_t kh = head / (heads / kv_heads), per_lane = head_dim / 32;
@@ -229,12 +237,35 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
     for (int w = 0; w < 4; ++w) {
         total_sum += merged[w][257] * expf(merged[w][256] - total_max);  // an idle warp has sum 0 and max -inf: exp(-inf) = 0
     }
-    for (uint32_t i = threadIdx.x; i < head_dim; i += blockDim.x) {
+    // The head's output is head_dim/32 whole Q8_0 blocks of the attention row: quantise them here (one warp per
+    // block, same arithmetic as the activation quantiser) instead of storing FP32 and launching the quantiser.
+    const uint32_t hidden = heads * head_dim;
+    for (uint32_t block = warp; block < head_dim / 32; block += 4) {
+        const uint32_t i = block * 32 + lane;
         float value = 0.0f;
         for (int w = 0; w < 4; ++w) {
             value += merged[w][i] * expf(merged[w][256] - total_max);
         }
-        out[((uint64_t)t * heads + head) * head_dim + i] = value / total_sum;
+        value = value / total_sum;
+        float amax = fabsf(value);
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+        }
+        const float d = __fdiv_rn(amax, 127.0f);
+        const float inverse = d == 0.0f ? 0.0f : __fdiv_rn(1.0f, d);
+        const int code = __float2int_rn(__fmul_rn(value, inverse));
+        const uint64_t column = (uint64_t)head * head_dim + i;
+        codes[(uint64_t)t * hidden + column] = (int8_t)code;
+        int group = code;
+        for (int offset = 8; offset > 0; offset >>= 1) {
+            group += __shfl_xor_sync(0xffffffffu, group, offset);
+        }
+        if ((lane & 15) == 0) {
+            sums[(uint64_t)t * (hidden / 16) + column / 16] = (int16_t)group;
+        }
+        if (lane == 0) {
+            scales[(uint64_t)t * (hidden / 32) + column / 32] = __half2float(__float2half_rn(d));
+        }
     }
 }
 
@@ -243,6 +274,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
 {
     __shared__ float best_value[32];
     __shared__ int best_index[32];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const float *row = logits + (uint64_t)blockIdx.x * vocabulary;
     float value = -INFINITY;
     int index = 0x7fffffff;
@@ -292,6 +325,8 @@ struct syn_b200_decoder {
     syn_b200_decoder_desc shape{};  // scalars only; the pointers inside are not kept
     int device = 0;
     cudaStream_t stream = nullptr;
+    cudaStream_t side[2] = {};      // the key and value projections run beside the query projection
+    cudaEvent_t fork = nullptr, join[2] = {};
     std::vector<Layer> layers;
     syn_b200_matrix *embedding = nullptr, *output = nullptr;
     float *output_norm = nullptr, *cosines = nullptr, *sines = nullptr;
@@ -359,7 +394,7 @@ int32_t upload_matrix(const syn_b200_decoder_desc &desc, uint64_t offset, uint32
 }
 
 cudaError_t product(syn_b200_decoder *d, const syn_b200_matrix *m, const void *act, uint32_t tokens, float *y, uint64_t out_stride,
-                    const Epilogue &epilogue)
+                    const Epilogue &epilogue, cudaStream_t stream = nullptr)
 {
     MatvecArgs args{};
     args.matrix = m;
@@ -373,7 +408,7 @@ cudaError_t product(syn_b200_decoder *d, const syn_b200_matrix *m, const void *a
     args.mode = SYN_B200_MODE_XQ8;
     args.epilogue = SYN_B200_EPILOGUE_STORE;
     args.fused = epilogue;
-    return launch_matvec(args, d->stream);
+    return launch_matvec(args, stream ? stream : d->stream);
 }
 
 cudaError_t quantize(syn_b200_decoder *d, const float *x, uint32_t tokens, uint64_t columns, void *act)
@@ -389,12 +424,9 @@ cudaError_t norm_quantize(syn_b200_decoder *d, const float *x, const float *weig
     const uint32_t n = d->shape.hidden;
     const ActLayout layout = act_layout(rows, n);
     uint8_t *base = static_cast<uint8_t *>(act);
-    rmsnorm_quantize_kernel<<<tokens, 256, 0, d->stream>>>(d->device_tokens, x, weight, d->shape.rms_epsilon, n, rows, by_logits_row ? 1u : 0u,
-                                                           reinterpret_cast<int8_t *>(base + layout.codes),
-                                                           reinterpret_cast<float *>(base + layout.scales),
-                                                           reinterpret_cast<int16_t *>(base + layout.sums));
-    count_launch();
-    return cudaGetLastError();
+    return launch_kernel(rmsnorm_quantize_kernel, dim3(tokens), dim3(256), 0, d->stream, (const BatchToken *)d->device_tokens, x, weight,
+                         d->shape.rms_epsilon, n, rows, by_logits_row ? 1u : 0u, reinterpret_cast<int8_t *>(base + layout.codes),
+                         reinterpret_cast<float *>(base + layout.scales), reinterpret_cast<int16_t *>(base + layout.sums));
 }
 
 #define SYN_TRY(expression)                \
@@ -410,28 +442,39 @@ cudaError_t enqueue_step(syn_b200_decoder *d, uint32_t count, uint32_t logits_ro
 {
     const syn_b200_decoder_desc &s = d->shape;
     const uint32_t hidden = s.hidden, kvw = s.kv_heads * s.head_dim, ffn = s.feed_forward;
-    embed_kernel<<<dim3((hidden + 255) / 256, count), 256, 0, d->stream>>>(d->device_tokens, d->embedding->data, d->embedding->type,
-                                                                          d->embedding->row_bytes, hidden, d->hidden);
-    count_launch();
-    SYN_TRY(cudaGetLastError());
+    SYN_TRY(launch_kernel(embed_kernel, dim3((hidden + 255) / 256, count), dim3(256), 0, d->stream, d->device_tokens,
+                          (const uint8_t *)d->embedding->data, d->embedding->type, d->embedding->row_bytes, hidden, d->hidden));
     for (uint32_t l = 0; l < s.layer_count; ++l) {
         const Layer &L = d->layers[l];
         SYN_TRY(norm_quantize(d, d->hidden, L.attention_norm, count, count, false, d->act_hidden));
+        // q | k | v read the same activations and write disjoint outputs: k and v fork onto side streams (parallel
+        // branches of the captured graph) and join before the rotation.
+        SYN_TRY(cudaEventRecord(d->fork, d->stream));
         Epilogue bias;
+        bias.bias = L.key_bias;
+        SYN_TRY(cudaStreamWaitEvent(d->side[0], d->fork, 0));
+        SYN_TRY(product(d, L.key, d->act_hidden, count, d->k, kvw, bias, d->side[0]));
+        SYN_TRY(cudaEventRecord(d->join[0], d->side[0]));
+        bias.bias = L.value_bias;
+        SYN_TRY(cudaStreamWaitEvent(d->side[1], d->fork, 0));
+        SYN_TRY(product(d, L.value, d->act_hidden, count, d->v, kvw, bias, d->side[1]));
+        SYN_TRY(cudaEventRecord(d->join[1], d->side[1]));
         bias.bias = L.query_bias;
         SYN_TRY(product(d, L.query, d->act_hidden, count, d->q, hidden, bias));
-        bias.bias = L.key_bias;
-        SYN_TRY(product(d, L.key, d->act_hidden, count, d->k, kvw, bias));
-        bias.bias = L.value_bias;
-        SYN_TRY(product(d, L.value, d->act_hidden, count, d->v, kvw, bias));
-        rope_store_kernel<<<dim3(s.heads + s.kv_heads, count), s.head_dim / 2, 0, d->stream>>>(
-            d->device_tokens, d->q, d->k, d->v, d->cosines, d->sines, d->keys, d->values, s.heads, s.kv_heads, s.head_dim, l, s.layer_count, s.context);
-        count_launch();
-        attention_kernel<<<dim3(s.heads, count), 128, 0, d->stream>>>(d->device_tokens, d->q, d->keys, d->values, d->attention, s.heads, s.kv_heads,
-                                                                      s.head_dim, l, s.layer_count, s.context, 1.0f / sqrtf((float)s.head_dim));
-        count_launch();
-        SYN_TRY(cudaGetLastError());
-        SYN_TRY(quantize(d, d->attention, count, hidden, d->act_hidden));
+        SYN_TRY(cudaStreamWaitEvent(d->stream, d->join[0], 0));
+        SYN_TRY(cudaStreamWaitEvent(d->stream, d->join[1], 0));
+        SYN_TRY(launch_kernel(rope_store_kernel, dim3(s.heads + s.kv_heads, count), dim3(s.head_dim / 2), 0, d->stream,
+                              (const BatchToken *)d->device_tokens, d->q, d->k, (const float *)d->v, (const float *)d->cosines,
+                              (const float *)d->sines, d->keys, d->values, s.heads, s.kv_heads, s.head_dim, l, s.layer_count, s.context));
+        {
+            // the attention output replaces the normalised activations of this layer in the same scratch
+            const ActLayout layout = act_layout(count, hidden);
+            uint8_t *base = static_cast<uint8_t *>(d->act_hidden);
+            SYN_TRY(launch_kernel(attention_kernel, dim3(s.heads, count), dim3(128), 0, d->stream, (const BatchToken *)d->device_tokens,
+                                  (const float *)d->q, (const float *)d->keys, (const float *)d->values, s.heads, s.kv_heads, s.head_dim, l,
+                                  s.layer_count, s.context, 1.0f / sqrtf((float)s.head_dim), reinterpret_cast<int8_t *>(base + layout.codes),
+                                  reinterpret_cast<float *>(base + layout.scales), reinterpret_cast<int16_t *>(base + layout.sums)));
+        }
         Epilogue residual;
         residual.accumulate = 1;
         SYN_TRY(product(d, L.output, d->act_hidden, count, d->hidden, hidden, residual));
@@ -447,9 +490,7 @@ cudaError_t enqueue_step(syn_b200_decoder *d, uint32_t count, uint32_t logits_ro
     if (logits_rows > 0) {
         SYN_TRY(norm_quantize(d, d->hidden, d->output_norm, count, logits_rows, true, d->act_hidden));
         SYN_TRY(product(d, d->output, d->act_hidden, logits_rows, d->logits, s.vocabulary, Epilogue{}));
-        argmax_kernel<<<logits_rows, 1024, 0, d->stream>>>(d->logits, s.vocabulary, d->device_argmax);
-        count_launch();
-        SYN_TRY(cudaGetLastError());
+        SYN_TRY(launch_kernel(argmax_kernel, dim3(logits_rows), dim3(1024), 0, d->stream, (const float *)d->logits, s.vocabulary, d->device_argmax));
     }
     return cudaSuccess;
 }
@@ -648,6 +689,11 @@ int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_deco
         if (error == cudaSuccess) error = cudaHostAlloc(reinterpret_cast<void **>(&d->host_tokens), T * sizeof(syn::BatchToken), cudaHostAllocDefault);
         if (error == cudaSuccess) error = cudaHostAlloc(reinterpret_cast<void **>(&d->host_argmax), T * sizeof(int32_t), cudaHostAllocDefault);
         if (error == cudaSuccess) error = cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking);
+        for (int i = 0; i < 2; ++i) {
+            if (error == cudaSuccess) error = cudaStreamCreateWithFlags(&d->side[i], cudaStreamNonBlocking);
+            if (error == cudaSuccess) error = cudaEventCreateWithFlags(&d->join[i], cudaEventDisableTiming);
+        }
+        if (error == cudaSuccess) error = cudaEventCreateWithFlags(&d->fork, cudaEventDisableTiming);
         if (error != cudaSuccess) {
             cudaGetLastError();
             return fail_out(cuda_fail(error, "setting up the decoder"));
@@ -688,6 +734,11 @@ void syn_b200_decoder_destroy(syn_b200_decoder *d)
     }
     if (d->host_tokens) cudaFreeHost(d->host_tokens);
     if (d->host_argmax) cudaFreeHost(d->host_argmax);
+    for (int i = 0; i < 2; ++i) {
+        if (d->side[i]) cudaStreamDestroy(d->side[i]);
+        if (d->join[i]) cudaEventDestroy(d->join[i]);
+    }
+    if (d->fork) cudaEventDestroy(d->fork);
     if (d->stream) cudaStreamDestroy(d->stream);
     delete d;
 }

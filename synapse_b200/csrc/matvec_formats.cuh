@@ -20,7 +20,10 @@
 namespace syn {
 namespace mv {
 
-constexpr int kWarps = 8;  // most consumer warps a CTA runs
+#ifndef SYN_MV_WARPS
+#define SYN_MV_WARPS 8
+#endif
+constexpr int kWarps = SYN_MV_WARPS;  // most consumer warps a CTA runs
 #ifndef SYN_DEFAULT_CTAS
 #define SYN_DEFAULT_CTAS 2
 #endif
@@ -335,8 +338,11 @@ struct Q4KXq8 {
 #ifndef SYN_Q4K_CTAS
 #define SYN_Q4K_CTAS 1
 #endif
+#ifndef SYN_Q4K_MINCTAS
+#define SYN_Q4K_MINCTAS 2
+#endif
     static constexpr int kMaxUpl = 1, kRows = SYN_Q4K_ROWS, kCtasPerSm = SYN_Q4K_CTAS;
-    static constexpr int min_ctas(int) { return 2; }
+    static constexpr int min_ctas(int) { return SYN_Q4K_MINCTAS; }
     static constexpr int ctas_per_sm(int) { return kCtasPerSm; }
     static void plane_row_bytes(uint64_t, uint64_t row_bytes, uint32_t *out) { out[0] = (uint32_t)row_bytes; }
     static __device__ __forceinline__ uint64_t units(uint64_t K) { return K / 128; }

@@ -242,7 +242,10 @@ cudaError_t launch_team(const MatvecArgs &a, const WeightView &view, uint64_t du
 
 constexpr int kMaxStages = 8;
 constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr uint32_t kStageBudget = 100 * 1024;  // dynamic shared memory per CTA, so that two CTAs fit one SM
+#ifndef SYN_MV_STAGE_KB
+#define SYN_MV_STAGE_KB 100
+#endif
+constexpr uint32_t kStageBudget = SYN_MV_STAGE_KB * 1024;  // dynamic shared memory per CTA, so that two CTAs fit one SM
 
 struct PipeArgs {
     WeightView global;            // plane bases at the first row of the call

@@ -4,8 +4,8 @@
 
 ``--copies`` distinct matrices are rotated so that consecutive launches never find their weights in L2
 (8 x 38 MB > 126 MB). Prints one JSON line: microseconds per launch (CUDA events on the launch stream) and
-GB/s of source GGUF block bytes. Small enough to run under a profiler: ``--reps 1 --warmup 0`` gives exactly
-``copies`` launches of the kernel.
+GB/s of source GGUF block bytes. Small enough to run under a profiler: ``--reps 1 --warmup 0`` with ``--cycles 1`` gives
+exactly ``copies`` launches of the kernel.
 """
 from __future__ import annotations
 
@@ -22,6 +22,7 @@ def main():
     parser.add_argument("--cols", type=int, default=3584)
     parser.add_argument("--tokens", type=int, default=1)
     parser.add_argument("--copies", type=int, default=8)
+    parser.add_argument("--cycles", type=int, default=4, help="times every copy is launched inside one graph (amortises the graph launch)")
     parser.add_argument("--reps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--mode", default="xq8", choices=["xq8", "xf32", "gemm"])
@@ -63,8 +64,9 @@ def main():
             matrix.matmul_q8_device(scratch_ptr, args.tokens, y.data_ptr(), args.rows, stream=stream_ptr)
 
     def one_round(stream_ptr):
-        for matrix in matrices:
-            launch(matrix, stream_ptr)
+        for _ in range(args.cycles):
+            for matrix in matrices:
+                launch(matrix, stream_ptr)
 
     graph = None
     with torch.cuda.stream(stream):
@@ -85,11 +87,11 @@ def main():
             graph.replay() if graph is not None else one_round(stream.cuda_stream)
         end.record(stream)
         stream.synchronize()
-    launches = args.reps * args.copies
+    launches = args.reps * args.copies * args.cycles
     microseconds = begin.elapsed_time(end) * 1e3 / launches
     source_bytes = matrices[0].source_bytes
     print(json.dumps({"type": args.type, "rows": args.rows, "cols": args.cols, "tokens": args.tokens, "mode": args.mode,
-                      "repack": not args.no_repack, "copies": args.copies, "graph": graph is not None, "us_per_launch": microseconds,
+                      "repack": not args.no_repack, "copies": args.copies, "cycles": args.cycles, "graph": graph is not None, "us_per_launch": microseconds,
                       "weight_gbs": source_bytes / microseconds / 1e3,
                       "tflops": 2.0 * args.rows * args.cols * args.tokens / microseconds / 1e6,
                       "checksum": float(y.double().sum().item())}))
