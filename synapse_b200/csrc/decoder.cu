@@ -8,9 +8,12 @@
 // SwiGLU epilogue, quantise, down + residual}, output norm + quantise, vocabulary projection. Token, position and
 // slot are read by the kernels from a small device array, so the launch sequence of a step does not depend on
 // them: it is captured once per token count into a CUDA graph and replayed.
+#include <cstdio>
+#include <cstdlib>
 #include <vector>
 
 #include "common.cuh"
+#include "decode_program.cuh"
 
 namespace syn {
 
@@ -19,48 +22,10 @@ namespace {
 constexpr uint64_t kNoTensor = 0xFFFFFFFFFFFFFFFFull;
 constexpr uint32_t kMaxStepTokens = 8;
 
-struct BatchToken {
-    int32_t slot, token, position, logits_row;
-};
+using prog::BatchToken;
+using prog::decode_element;
 
 // ---- small kernels ------------------------------------------------------------------------------------
-
-// Exact ggml-order decode of element i of a row (GgufLegacyBlocks.cs:85-92, GgufKQuantBlocks.cs:99-177).
-__device__ float decode_element(uint32_t type, const uint8_t *row, uint32_t i)
-{
-    if (type == kQ8_0) {
-        const uint8_t *block = row + (uint64_t)(i / 32) * 34;
-        const float d = __half2float(__ushort_as_half((unsigned short)(block[0] | (block[1] << 8))));
-        return d * (float)(signed char)block[2 + (i & 31)];
-    }
-    if (type == kQ4_K) {
-        const uint8_t *block = row + (uint64_t)(i / 256) * 144;
-        const uint32_t within = i & 255, chunk = within / 64, l = within & 31, high = (within >> 5) & 1;
-        const float d = __half2float(__ushort_as_half((unsigned short)(block[0] | (block[1] << 8))));
-        const float dmin = __half2float(__ushort_as_half((unsigned short)(block[2] | (block[3] << 8))));
-        const uint8_t *s = block + 4;
-        const uint32_t j = chunk * 2 + high;
-        uint32_t sc, mn;
-        if (j < 4) {
-            sc = s[j] & 63;
-            mn = s[j + 4] & 63;
-        } else {
-            sc = (s[j + 4] & 0x0F) | ((s[j - 4] >> 6) << 4);
-            mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
-        }
-        const uint32_t q = high ? (block[16 + chunk * 32 + l] >> 4) : (block[16 + chunk * 32 + l] & 0x0F);
-        return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)mn));
-    }
-    const uint8_t *block = row + (uint64_t)(i / 256) * 210;
-    const uint32_t within = i & 255, half = within / 128, rest = within & 127, quarter = rest / 32, l = rest & 31;
-    const uint8_t *ql = block + half * 64, *qh = block + 128 + half * 32;
-    const float d = __half2float(__ushort_as_half((unsigned short)(block[208] | (block[209] << 8))));
-    const int scale = (int)(signed char)block[192 + half * 8 + l / 16 + 2 * quarter];
-    const uint32_t low = (quarter & 1) ? ql[l + 32] : ql[l];
-    const uint32_t nibble = quarter < 2 ? (low & 0x0F) : (low >> 4);
-    const int q = (int)(nibble | (((qh[l] >> (2 * quarter)) & 3) << 4)) - 32;
-    return __fmul_rn(__fmul_rn(d, (float)scale), (float)q);
-}
 
 // hidden[t] = embedding row of tokens[t].token (Qwen2CpuExecutor.cs:110-117).
 __global__ void embed_kernel(const BatchToken *__restrict__ tokens, const uint8_t *__restrict__ table, uint32_t type, uint64_t row_bytes,
@@ -82,7 +47,7 @@ rmsnorm_quantize_kernel(const BatchToken *__restrict__ tokens, const float *__re
                         uint32_t n, uint32_t rows, uint32_t by_logits_row, int8_t *__restrict__ codes, float *__restrict__ scales,
                         int16_t *__restrict__ sums)
 {
-    __shared__ double partial[8];
+    __shared__ double quad_sums[256];  // rows of up to 32768 values
     __shared__ float shared_scale;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -95,24 +60,19 @@ rmsnorm_quantize_kernel(const BatchToken *__restrict__ tokens, const float *__re
         }
     }
     const float *row = x + (uint64_t)t * n;
-    double sum = 0.0;
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-        const double v = (double)row[i];
-        sum += v * v;
-    }
-    for (int offset = 16; offset > 0; offset >>= 1) {
-        sum += __shfl_xor_sync(0xffffffffu, sum, offset);
-    }
-    if (lane == 0) {
-        partial[warp] = sum;
+    // sums of squares per 128-value piece, pieces added in index order: the order every normalising kernel uses
+    const uint32_t quads = (n + 127) / 128;
+    for (uint32_t quad = warp; quad < quads; quad += 8) {
+        const uint32_t first = quad * 128 + lane * 4;
+        const float4 v = first < n ? *reinterpret_cast<const float4 *>(row + first) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const double s = prog::quad_square_sum(v);
+        if (lane == 0) {
+            quad_sums[quad] = s;
+        }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        double total = 0.0;
-        for (int w = 0; w < 8; ++w) {
-            total += partial[w];
-        }
-        shared_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float)(total / (double)n), epsilon)));
+        shared_scale = prog::norm_scale_from(quad_sums, quads, n, epsilon);
     }
     __syncthreads();
     const float scale = shared_scale;
@@ -339,6 +299,14 @@ struct syn_b200_decoder {
     cudaGraphExec_t graphs[kMaxStepTokens + 1] = {};
     uint64_t launches_per_step[kMaxStepTokens + 1] = {};
     uint32_t steps_seen[kMaxStepTokens + 1] = {};  // the first step of a token count runs uncaptured (one-time kernel set-up)
+    // Single-token steps run as one persistent kernel when the model fits it (decode_program.cuh).
+    bool program_ready = false;
+    syn::prog::Op *program_ops = nullptr;
+    uint32_t *program_sync = nullptr;
+    syn::prog::Params program{};
+    uint32_t program_grid = 0, program_shared = 0;
+    uint64_t *program_timeline = nullptr;  // only with SYN_B200_PROGRAM_TIMELINE set: per-operation timestamps of CTA 0
+    std::vector<uint32_t> program_kinds;
 };
 
 namespace syn {
@@ -495,6 +463,373 @@ cudaError_t enqueue_step(syn_b200_decoder *d, uint32_t count, uint32_t logits_ro
     return cudaSuccess;
 }
 
+// ---- the single-token step as one persistent kernel ------------------------------------------------------
+
+// Describes `m` as a projection of the program; false when its encoding or layout has no in-kernel consumer.
+bool program_matvec(const syn_b200_matrix *m, float *y, const float *bias, const float *gate, bool accumulate, prog::Op &op)
+{
+    using namespace prog;
+    const uint64_t K = m->columns;
+    uint32_t units = 0, U = 1;
+    op = Op{};
+    op.kind = kOpMatvec;
+    if (m->type == kQ8_0 && m->layout == Layout::Planar) {
+        op.format = kFormatQ8Planar;
+        units = (uint32_t)(K / 16);
+        U = mv::Q8PlanarXq8::kMaxUpl;
+        op.planes = mv::Q8PlanarXq8::kPlanes;
+        mv::Q8PlanarXq8::plane_row_bytes(K, m->row_bytes, op.plane_row_bytes);
+        op.plane[0] = m->data + m->planes.p0;
+        op.plane[1] = m->data + m->planes.p1;
+    } else if (m->type == kQ4_K && m->layout == Layout::Natural) {
+        op.format = kFormatQ4K;
+        units = (uint32_t)(K / 128);
+        U = mv::Q4KXq8::kMaxUpl;
+        op.planes = mv::Q4KXq8::kPlanes;
+        mv::Q4KXq8::plane_row_bytes(K, m->row_bytes, op.plane_row_bytes);
+        op.plane[0] = m->data;
+    } else if (m->type == kQ6_K && m->layout == Layout::Planar) {
+        op.format = kFormatQ6KPlanar;
+        units = (uint32_t)(K / 64);
+        U = mv::Q6KPlanarXq8::kMaxUpl;
+        op.planes = mv::Q6KPlanarXq8::kPlanes;
+        mv::Q6KPlanarXq8::plane_row_bytes(K, m->row_bytes, op.plane_row_bytes);
+        op.plane[0] = m->data + m->planes.p0;
+        op.plane[1] = m->data + m->planes.p1;
+        op.plane[2] = m->data + m->planes.p2;
+        op.plane[3] = m->data + m->planes.p3;
+    } else {
+        return false;
+    }
+    // The team shape of launch_format: it depends on the row length only.
+    if (units <= 32) {
+        op.team = 1;
+        op.upl = 1;
+        op.one_pass = 1;
+    } else {
+        const uint32_t teams = (units + 32 * U - 1) / (32 * U);
+        if (teams > 8) {
+            return false;  // rows that need several passes of an eight-warp team stay with the per-operation kernels
+        }
+        op.team = teams;
+        op.upl = U;
+        op.one_pass = 1;
+    }
+    op.rows = (uint32_t)m->rows;
+    op.columns = (uint32_t)K;
+    op.group_rows = prog::kConsumerWarps / op.team;
+    uint64_t offset = 0;
+    for (uint32_t k = 0; k < op.planes; ++k) {
+        op.plane_offset[k] = (uint32_t)offset;
+        offset += align_up((uint64_t)op.group_rows * op.plane_row_bytes[k] + 16, 128);
+    }
+    op.stage_bytes = (uint32_t)offset;
+    op.teams = op.group_rows;
+    op.groups = (op.rows + op.teams - 1) / op.teams;
+    op.units = units;
+    op.scales_offset = mv::shared_act_codes_bytes(1, (uint32_t)K);
+    op.sums_offset = op.scales_offset + mv::shared_act_side_bytes(1, (uint32_t)K);
+    for (uint32_t warp = 0; warp < (uint32_t)prog::kConsumerWarps; ++warp) {
+        const bool active = warp < op.teams * op.team;
+        op.team_of_warp |= (uint64_t)(active ? warp / op.team : 0) << (4 * warp);
+        op.index_in_team |= (uint64_t)(warp % op.team) << (4 * warp);
+    }
+    op.y = y;
+    op.bias = bias;
+    op.gate = gate;
+    op.accumulate = accumulate ? 1u : 0u;
+    return true;
+}
+
+// Builds the program of a one-token step. Leaves d->program_ready false (the per-operation kernels are used)
+// when the model does not fit: an encoding without an in-kernel consumer, more heads than CTAs, no room for the ring.
+cudaError_t build_program(syn_b200_decoder *d)
+{
+    using namespace prog;
+    const syn_b200_decoder_desc &s = d->shape;
+    // SYN_B200_DECODE_PROGRAM=0 keeps the per-operation kernels, =1 asks for the program wherever it can be built.
+    // By default it is used for rows of 2048 values and more: with shorter rows a projection is a few microseconds of
+    // work and the replayed graph of per-operation kernels is faster (1300 against 1000 tokens/s on the 0.5B shapes).
+    const char *choice = getenv("SYN_B200_DECODE_PROGRAM");
+    if (choice ? choice[0] == '0' : s.hidden < 2048) {
+        return cudaSuccess;
+    }
+    int cooperative = 0;
+    cudaDeviceGetAttribute(&cooperative, cudaDevAttrCooperativeLaunch, d->device);
+    const uint32_t grid = (uint32_t)sm_count(d->device);
+    if (!cooperative || s.heads > grid || s.head_dim > 256) {
+        return cudaSuccess;
+    }
+    // the in-kernel quantiser holds a whole vector in the registers of one CTA
+    if (s.hidden > (uint32_t)kNormDepth * kConsumerWarps * 128 || s.feed_forward > (uint32_t)kPlainDepth * kConsumerWarps * 128) {
+        return cudaSuccess;
+    }
+    std::vector<Op> ops;
+    uint32_t cursor = 0;
+    bool supported = true;
+    auto matvec = [&](const syn_b200_matrix *m, float *y, const float *bias, const float *gate, bool accumulate) -> Op * {
+        Op op;
+        if (!program_matvec(m, y, bias, gate, accumulate, op)) {
+            supported = false;
+            return nullptr;
+        }
+        op.first_cta = cursor % grid;
+        cursor = (cursor + op.groups) % grid;
+        ops.push_back(op);
+        return &ops.back();
+    };
+    auto quantize = [&](const float *x, const float *norm, uint32_t n) {
+        Op op;
+        op.kind = kOpQuantize;
+        op.barrier = 1;  // x was written by other CTAs, and every warp must be done with the previous activations
+        op.x = x;
+        op.norm_weight = norm;
+        op.epsilon = s.rms_epsilon;
+        op.columns = n;
+        ops.push_back(op);
+    };
+    {
+        Op op;
+        op.kind = kOpEmbed;
+        op.format = d->embedding->type;
+        op.plane[0] = d->embedding->data;
+        op.row_bytes = d->embedding->row_bytes;
+        op.columns = s.hidden;
+        op.y = d->hidden;
+        ops.push_back(op);
+    }
+    if (d->embedding->layout != Layout::Natural) {
+        supported = false;
+    }
+    for (uint32_t l = 0; l < s.layer_count && supported; ++l) {
+        const Layer &L = d->layers[l];
+        quantize(d->hidden, L.attention_norm, s.hidden);
+        matvec(L.query, d->q, L.query_bias, nullptr, false);
+        matvec(L.key, d->k, L.key_bias, nullptr, false);
+        matvec(L.value, d->v, L.value_bias, nullptr, false);
+        {
+            Op op;
+            op.kind = kOpAttention;
+            op.barrier = 1;
+            op.layer = l;
+            ops.push_back(op);
+        }
+        quantize(d->attention, nullptr, s.hidden);
+        matvec(L.output, d->hidden, nullptr, nullptr, true);
+        quantize(d->hidden, L.feed_forward_norm, s.hidden);
+        const uint32_t gate_cta = cursor;
+        Op *gate = matvec(L.gate, d->gate, nullptr, nullptr, false);
+        const Op gate_copy = gate ? *gate : Op{};
+        const uint32_t after_gate = cursor;
+        cursor = gate_cta;  // the up projection reads each gate value in the thread that wrote it: same row-to-CTA map
+        Op *up = matvec(L.up, d->ff, nullptr, d->gate, false);
+        if (gate && up) {
+            if (up->format != gate_copy.format || up->team != gate_copy.team || up->upl != gate_copy.upl || up->rows != gate_copy.rows) {
+                up->barrier = 1;  // different team shapes: the gate values come from other threads, through global memory
+            } else if ((up->groups + grid - 1) / grid <= kStashIterations) {
+                up->gate_stash = 2;
+                (up - 1)->gate_stash = 1;  // the gate projection is the operation before
+            }
+        }
+        cursor = (after_gate + (cursor + grid - gate_cta) % grid) % grid;
+        quantize(d->ff, nullptr, s.feed_forward);
+        matvec(L.down, d->hidden, nullptr, nullptr, true);
+    }
+    if (supported) {
+        quantize(d->hidden, d->output_norm, s.hidden);
+        if (Op *head = matvec(d->output, d->logits, nullptr, nullptr, false)) {
+            head->track_argmax = 1;
+        }
+        Op op;
+        op.kind = kOpArgmax;
+        op.barrier = 1;
+        ops.push_back(op);
+    }
+    if (!supported) {
+        return cudaSuccess;
+    }
+    uint32_t largest = 0, longest = s.hidden > s.feed_forward ? s.hidden : s.feed_forward;
+    for (const Op &op : ops) {
+        if (op.kind == kOpMatvec && op.stage_bytes > largest) {
+            largest = op.stage_bytes;
+        }
+    }
+    const uint32_t act_bytes = (uint32_t)align_up(mv::shared_act_bytes(1, longest), 128);
+    // the ring must hold at least two of the largest stages, or the producer could never run ahead
+    if (largest == 0 || act_bytes + 2 * (uint64_t)largest > kDynamicSharedBudget) {
+        return cudaSuccess;
+    }
+    uint32_t ring_bytes = (kDynamicSharedBudget - act_bytes) / 128 * 128;
+    if (const char *limit = getenv("SYN_B200_PROGRAM_RING_KB")) {  // tuning aid: a smaller ring
+        const uint32_t wanted = (uint32_t)atoi(limit) * 1024;
+        if (wanted >= 2 * largest && wanted < ring_bytes) {
+            ring_bytes = wanted;
+        }
+    }
+    const uint32_t dynamic = act_bytes + ring_bytes;
+    cudaError_t error = cudaFuncSetAttribute(decode_program_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dynamic);
+    int resident = 0;
+    if (error == cudaSuccess) {
+        error = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, decode_program_kernel, kThreads, dynamic);
+    }
+    if (error != cudaSuccess) {
+        return error;
+    }
+    if (resident < 1) {
+        return cudaSuccess;
+    }
+    void *p = nullptr;
+    error = cudaMalloc(&p, ops.size() * sizeof(Op));
+    if (error != cudaSuccess) {
+        return error;
+    }
+    d->owned.push_back(p);
+    d->program_ops = static_cast<Op *>(p);
+    error = cudaMemcpy(d->program_ops, ops.data(), ops.size() * sizeof(Op), cudaMemcpyHostToDevice);
+    if (error != cudaSuccess) {
+        return error;
+    }
+    std::vector<ProducerOp> streams;
+    for (const Op &op : ops) {
+        if (op.kind == kOpMatvec) {
+            ProducerOp stream;
+            for (int k = 0; k < 4; ++k) {
+                stream.plane[k] = op.plane[k];
+                stream.plane_row_bytes[k] = op.plane_row_bytes[k];
+                stream.plane_offset[k] = op.plane_offset[k];
+            }
+            stream.rows = op.rows;
+            stream.group_rows = op.group_rows;
+            stream.first_cta = op.first_cta;
+            stream.planes = op.planes;
+            stream.stage_bytes = op.stage_bytes;
+            stream.groups = op.groups;
+            streams.push_back(stream);
+        }
+    }
+    error = cudaMalloc(&p, streams.size() * sizeof(ProducerOp));
+    if (error != cudaSuccess) {
+        return error;
+    }
+    d->owned.push_back(p);
+    error = cudaMemcpy(p, streams.data(), streams.size() * sizeof(ProducerOp), cudaMemcpyHostToDevice);
+    if (error != cudaSuccess) {
+        return error;
+    }
+    const ProducerOp *producer_ops = static_cast<const ProducerOp *>(p);
+    error = cudaMalloc(&p, 256);
+    if (error != cudaSuccess) {
+        return error;
+    }
+    d->owned.push_back(p);
+    d->program_sync = static_cast<uint32_t *>(p);
+    Params &P = d->program;
+    P.ops = d->program_ops;
+    P.op_count = (uint32_t)ops.size();
+    P.producer_ops = producer_ops;
+    P.producer_count = (uint32_t)streams.size();
+    P.token = d->device_tokens;
+    P.sync = d->program_sync;
+    P.fault = fault_word_device();
+    P.ring_bytes = ring_bytes;
+    P.act_bytes = act_bytes;
+    P.q = d->q;
+    P.k = d->k;
+    P.v = d->v;
+    P.attention = d->attention;
+    P.keys = d->keys;
+    P.values = d->values;
+    P.cosines = d->cosines;
+    P.sines = d->sines;
+    P.heads = s.heads;
+    P.kv_heads = s.kv_heads;
+    P.head_dim = s.head_dim;
+    P.layers = s.layer_count;
+    P.context = s.context;
+    P.attention_scale = 1.0f / sqrtf((float)s.head_dim);
+    error = cudaMalloc(&p, 2 * grid * sizeof(float));
+    if (error != cudaSuccess) {
+        return error;
+    }
+    d->owned.push_back(p);
+    P.best_value = static_cast<float *>(p);
+    P.best_index = reinterpret_cast<int32_t *>(P.best_value + grid);
+    P.argmax = d->device_argmax;
+    P.timeline = nullptr;
+    if (getenv("SYN_B200_PROGRAM_TIMELINE")) {
+        error = cudaMalloc(&p, (2 * ops.size() + 1) * sizeof(uint64_t));
+        if (error == cudaSuccess) {
+            error = cudaMemset(p, 0, (2 * ops.size() + 1) * sizeof(uint64_t));
+        }
+        if (error != cudaSuccess) {
+            return error;
+        }
+        d->owned.push_back(p);
+        d->program_timeline = P.timeline = static_cast<uint64_t *>(p);
+        for (const Op &op : ops) {
+            d->program_kinds.push_back(op.kind);
+        }
+    }
+    d->program_grid = grid;
+    d->program_shared = dynamic;
+    d->program_ready = true;
+    return cudaSuccess;
+}
+
+// Queues a one-token step (token already in host_tokens) as the persistent kernel.
+cudaError_t enqueue_program(syn_b200_decoder *d)
+{
+    cudaError_t error = cudaMemcpyAsync(d->device_tokens, d->host_tokens, sizeof(BatchToken), cudaMemcpyHostToDevice, d->stream);
+    if (error == cudaSuccess) {
+        error = cudaMemsetAsync(d->program_sync, 0, 8, d->stream);
+    }
+    if (error != cudaSuccess) {
+        return error;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(d->program_grid);
+    config.blockDim = dim3(prog::kThreads);
+    config.dynamicSmemBytes = d->program_shared;
+    config.stream = d->stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident at once, or the launch fails
+    attribute[0].val.cooperative = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    count_launch();
+    error = cudaLaunchKernelEx(&config, prog::decode_program_kernel, d->program);
+    if (error == cudaSuccess && d->program_timeline) {
+        // Profiling aid: nanoseconds CTA 0 spent per kind of operation, and waiting in the grid barriers.
+        std::vector<uint64_t> t(2 * d->program_kinds.size() + 1);
+        error = cudaStreamSynchronize(d->stream);
+        if (error == cudaSuccess) {
+            error = cudaMemcpy(t.data(), d->program_timeline, t.size() * sizeof(uint64_t), cudaMemcpyDeviceToHost);
+        }
+        if (error == cudaSuccess) {
+            uint64_t by_kind[5] = {0, 0, 0, 0, 0}, barriers = 0;
+            for (size_t i = 0; i < d->program_kinds.size(); ++i) {
+                barriers += t[2 * i + 1] - t[2 * i];
+                by_kind[d->program_kinds[i]] += t[2 * i + 2] - t[2 * i + 1];
+            }
+            const char *detail = getenv("SYN_B200_PROGRAM_TIMELINE");
+            if (detail && detail[0] == '2') {
+                for (size_t i = 0; i < d->program_kinds.size(); ++i) {
+                    if (i >= 32 && i + 4 < d->program_kinds.size()) {
+                        continue;
+                    }
+                    fprintf(stderr, "  op %zu kind %u at %llu: barrier %llu ns, body %llu ns\n", i, d->program_kinds[i],
+                            (unsigned long long)(t[2 * i] - t[0]), (unsigned long long)(t[2 * i + 1] - t[2 * i]),
+                            (unsigned long long)(t[2 * i + 2] - t[2 * i + 1]));
+                }
+            }
+            fprintf(stderr, "decode program: total %llu ns; barriers %llu, embed %llu, quantize %llu, matvec %llu, attention %llu, argmax %llu\n",
+                    (unsigned long long)(t[2 * d->program_kinds.size()] - t[0]), (unsigned long long)barriers, (unsigned long long)by_kind[0],
+                    (unsigned long long)by_kind[1], (unsigned long long)by_kind[2], (unsigned long long)by_kind[3], (unsigned long long)by_kind[4]);
+        }
+    }
+    return error;
+}
+
 // Validates a step like Qwen2CpuExecutor.Validate (Qwen2CpuExecutor.cs:141-163) and returns its logits rows.
 int32_t validate_step(const syn_b200_decoder *d, const syn_b200_batch_token *tokens, uint64_t count, uint32_t *logits_rows)
 {
@@ -540,7 +875,9 @@ int32_t run_step(syn_b200_decoder *d, const syn_b200_batch_token *tokens, uint64
     // anything else is enqueued kernel by kernel.
     const bool graphable = true;
     cudaError_t error = cudaSuccess;
-    if (graphable && rows == count && d->steps_seen[count]++ > 0) {
+    if (d->program_ready && count == 1 && rows == 1) {
+        error = enqueue_program(d);
+    } else if (graphable && rows == count && d->steps_seen[count]++ > 0) {
         if (!d->graphs[count]) {
             fault_word_device();
             const uint64_t before = syn_b200_launch_count(0);
@@ -606,7 +943,7 @@ int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_deco
             s.vocabulary == 0 || s.context == 0 || s.session_slots == 0 || s.step_tokens == 0 || s.logits_rows == 0) {
             return fail(SYN_B200_INVALID_ARGUMENT, "every decoder dimension must be positive");
         }
-        if (s.heads % s.kv_heads != 0 || s.heads * s.head_dim != s.hidden || s.head_dim % 32 != 0 || s.head_dim > 256 || s.hidden % 32 != 0 ||
+        if (s.heads % s.kv_heads != 0 || s.heads * s.head_dim != s.hidden || s.head_dim % 32 != 0 || s.head_dim > 256 || s.hidden % 32 != 0 || s.hidden > 32768 ||
             s.feed_forward % 32 != 0) {
             return fail(SYN_B200_UNAVAILABLE, "unsupported head geometry: heads * head_dim must equal hidden, head_dim a multiple of 32 up to 256");
         }
@@ -694,6 +1031,7 @@ int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_deco
             if (error == cudaSuccess) error = cudaEventCreateWithFlags(&d->join[i], cudaEventDisableTiming);
         }
         if (error == cudaSuccess) error = cudaEventCreateWithFlags(&d->fork, cudaEventDisableTiming);
+        if (error == cudaSuccess) error = build_program(d);
         if (error != cudaSuccess) {
             cudaGetLastError();
             return fail_out(cuda_fail(error, "setting up the decoder"));

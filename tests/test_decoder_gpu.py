@@ -86,3 +86,33 @@ def test_qwen25_05b_shaped_decode_step_has_identical_greedy_tokens(oracle):
         print(r)
     assert all(r["error"] <= 5e-2 for r in records), records
     assert [r["gpu"] for r in records] == [r["cpu"] for r in records], records
+
+
+@pytest.mark.parametrize("shape,types,embedding,output,steps", [
+    (TINY, dec.Q8_TYPES, synth.Q8_0, synth.Q8_0, 10),
+    (TINY, dec.Q4KM_TYPES, synth.Q4_K, synth.Q6_K, 10),
+    (dict(layers=2, hidden=1024, feed_forward=5632, heads=8, kv_heads=2, vocabulary=2048, context=32), dec.Q4KM_TYPES, synth.Q4_K, synth.Q4_K, 6),
+    (dict(dec.QWEN25_05B, layers=4, context=32), dec.Q8_TYPES, synth.Q8_0, synth.Q8_0, 5),
+])
+def test_single_kernel_step_equals_the_per_operation_kernels(monkeypatch, shape, types, embedding, output, steps):
+    """Single-token steps run as one persistent kernel; with SYN_B200_DECODE_PROGRAM=0 the same decoder launches one
+    kernel per operation. Both keep the summation order of every dot product, so logits are identical bit for bit,
+    the caches stay interchangeable and no bounded wait gives up."""
+    image = dec.ModelImage(**shape, matrix_types=types, embedding_type=embedding, output_type=output, seed=8)
+    lib = sb.library()
+    monkeypatch.setenv("SYN_B200_DECODE_PROGRAM", "1")
+    with dec.Decoder(image) as program:
+        before = lib.launch_count()
+        first = program.decode(3, 0)
+        assert lib.launch_count() - before == 1, "a single-token step is one kernel launch"
+        monkeypatch.setenv("SYN_B200_DECODE_PROGRAM", "0")
+        with dec.Decoder(image) as kernels:
+            monkeypatch.delenv("SYN_B200_DECODE_PROGRAM")
+            assert kernels.decode(3, 0).tobytes() == first.tobytes()
+            token = int(np.argmax(first))
+            for position in range(1, steps):
+                a, b = program.decode(token, position), kernels.decode(token, position)
+                assert a.tobytes() == b.tobytes(), position
+                assert program.forward_argmax([(0, token, position, 0)]) == [int(np.argmax(a))]
+                token = int(np.argmax(a))
+    assert lib.device_faults() == 0
