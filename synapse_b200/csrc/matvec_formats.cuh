@@ -189,6 +189,17 @@ __device__ __forceinline__ void store_result(const Epilogue &e, float *__restric
 
 __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
+// Exact integer-to-float conversions on the FMA pipe (a PRMT or IADD plus one FADD) instead of I2F, which runs on the
+// quarter-rate XU pipe: 2^23 + n is exactly representable for 0 <= n < 2^23, and 1.5 * 2^23 + n for |n| < 2^22.
+__device__ __forceinline__ float byte_to_float(uint32_t word, int index)
+{
+    return __int_as_float((int)__byte_perm(word, 0x4B000000u, 0x7650 + index)) - 8388608.0f;
+}
+__device__ __forceinline__ float small_int_to_float(int n)  // |n| < 2^22
+{
+    return __int_as_float(0x4B400000 + n) - 12582912.0f;
+}
+
 // ------------------------------------------------------------------------------------------------------
 // Weight views
 // ------------------------------------------------------------------------------------------------------
@@ -244,7 +255,7 @@ struct Q8PlanarXq8 {
             }
         }
         if (valid) {
-            acc = fmaf((float)d, w.d * a.d, acc);
+            acc = fmaf(small_int_to_float(d), w.d * a.d, acc);  // |d| <= 32 * 127 * 127
         }
     }
 };
@@ -286,7 +297,7 @@ struct Q8NaturalXq8 {
             if (DUMP) {
                 dump[u] = d;
             }
-            acc = fmaf((float)d, w.d * a.d, acc);
+            acc = fmaf(small_int_to_float(d), w.d * a.d, acc);  // |d| <= 32 * 127 * 127
         }
     }
 };
@@ -318,8 +329,6 @@ __device__ __forceinline__ int dp4a_us(uint32_t a_unsigned, uint32_t b_signed, i
     asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_unsigned), "r"(b_signed), "r"(c));
     return d;
 }
-__device__ __forceinline__ float byte_to_float(uint32_t word, int index) { return (float)((word >> (8 * index)) & 0xffu); }
-
 // Q4_K in its file layout (144-byte blocks are 16-byte aligned). Unit = half a super-block: 64 nibble bytes = the
 // four sub-blocks 4h..4h+3 (h = u%2) of super-block u/2. Taking four sub-blocks at once lets the 6-bit scales and
 // mins be unpacked four at a time with a handful of word operations, and the high nibbles are used in place
@@ -417,10 +426,11 @@ struct Q4KXq8 {
             sc = (w.hdr.w & 0x0f0f0f0fu) | ((w.hdr.y >> 2) & 0x30303030u);
             mn = ((w.hdr.w >> 4) & 0x0f0f0f0fu) | ((w.hdr.z >> 2) & 0x30303030u);
         }
-        float f_lo = (byte_to_float(sc, 0) * (float)lo[0]) * a.d[0];
-        f_lo = fmaf(byte_to_float(sc, 2) * (float)lo[1], a.d[2], f_lo);
-        float f_hi = (byte_to_float(sc, 1) * (float)hi16[0]) * a.d[1];
-        f_hi = fmaf(byte_to_float(sc, 3) * (float)hi16[1], a.d[3], f_hi);
+        // |lo| <= 32 * 15 * 127 and |hi16| <= 16 times that: both below 2^22
+        float f_lo = (byte_to_float(sc, 0) * small_int_to_float(lo[0])) * a.d[0];
+        f_lo = fmaf(byte_to_float(sc, 2) * small_int_to_float(lo[1]), a.d[2], f_lo);
+        float f_hi = (byte_to_float(sc, 1) * small_int_to_float(hi16[0])) * a.d[1];
+        f_hi = fmaf(byte_to_float(sc, 3) * small_int_to_float(hi16[1]), a.d[3], f_hi);
         float g = byte_to_float(mn, 0) * a.ds[0];
         g = fmaf(byte_to_float(mn, 1), a.ds[1], g);
         g = fmaf(byte_to_float(mn, 2), a.ds[2], g);
@@ -496,7 +506,7 @@ __device__ __forceinline__ void q6k_dot(const Q6KW &w, const Q6KAct &a, bool val
         if (DUMP) {
             dump[(u >> 2) * 16 + h * 8 + 2 * q + i] = dot;
         }
-        acc = fmaf((w.d * (float)sc) * a.d[q], (float)dot, acc);
+        acc = fmaf((w.d * small_int_to_float(sc)) * a.d[q], small_int_to_float(dot), acc);  // |dot| <= 16 * (63 + 32) * 127
     }
 }
 
