@@ -402,7 +402,10 @@ def main():
     peak, peak_kind = measured_peak_hbm()
     achieved = per_launch_bytes / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": "matvec_xq8_kernel<Q4_K, T=1> on ffn_gate/ffn_up (18944x3584)", "achieved": achieved,
-                "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this matrix shape, from the ncu
+                # capture summarised in profiles/matvec_q4k_18944x3584.md (38,212,352 read, 0 written: outputs stay in L2)
+                "traffic": 38212352 if per_launch_bytes == 38191104 else None,
                 "bytes_per_launch": per_launch_bytes, "us_per_launch": kernel_ms * 1e3, "launches_timed": len(durations)}
 
     # ---- end to end through the host-pointer C ABI: pinned host x in, host y out, per matrix ----------------
@@ -453,10 +456,17 @@ def main():
                 for position in range(3, 3 + decode_steps):
                     token = int(np.argmax(model.decode(token, position)))
                 decode_seconds = time.perf_counter() - start
+                # the same step with the greedy pick on the device (4 bytes back instead of the logits)
+                start = time.perf_counter()
+                for position in range(3 + decode_steps, 3 + 2 * decode_steps):
+                    token = model.forward_argmax([(0, token, position, 0)])[0]
+                argmax_seconds = time.perf_counter() - start
             e2e = {"value": total_bytes * decode_steps / decode_seconds / 1e9, "unit": UNIT, "h2d_bytes_per_step": 16,
                    "d2h_bytes_per_step": 4 * shape["vocabulary"], "ms_per_step": decode_seconds / decode_steps * 1e3, "steps": decode_steps,
                    "tokens_per_s": decode_steps / decode_seconds,
-                   "api": "syn_b200_decoder_forward (one call per decoded token: host BatchToken in, host logits out, greedy pick on the host)"}
+                   "api": "syn_b200_decoder_forward (one call per decoded token: host BatchToken in, host logits out, greedy pick on the "
+                          "host); the step runs as one persistent kernel"}
+            e2e["argmax_api_tokens_per_s"] = decode_steps / argmax_seconds
 
     extras = None
     if world == 1 and not args.no_e2e:

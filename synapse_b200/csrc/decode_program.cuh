@@ -574,7 +574,7 @@ __device__ __noinline__ void quantize_local(const Op *op, Shared &sh, uint32_t a
         sum += __shfl_xor_sync(kFull, sum, 2);
         if (first < n) {
             const uint32_t packed = (uint32_t)(c0 & 0xff) | ((uint32_t)(c1 & 0xff) << 8) | ((uint32_t)(c2 & 0xff) << 16) | ((uint32_t)c3 << 24);
-            asm volatile("st.shared.u32 [%0], %1;" ::"r"(codes + first), "r"(packed) : "memory");
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(codes + swizzled_code_offset(first)), "r"(packed) : "memory");
             if ((lane & 3) == 0) {
                 asm volatile("st.shared.u16 [%0], %1;" ::"r"(sums + (first / 16) * 2), "h"((short)sum) : "memory");
             }

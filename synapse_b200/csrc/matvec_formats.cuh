@@ -41,6 +41,18 @@ __device__ __forceinline__ uint32_t ld_u16(const void *p) { return __ldg(reinter
 __device__ __forceinline__ float half_bits_to_float(uint32_t bits) { return __half2float(__ushort_as_half((unsigned short)bits)); }
 
 // Where a kernel reads its weights from: global memory directly, or a shared-memory stage filled by bulk copies.
+// Where byte `offset` of the quantised activation codes lives in shared memory. Piece p (16 bytes) of line l (128
+// bytes) is stored at piece p ^ g(l), g(l) = 2 * (l % 4) + (l / 4) % 2: a permutation of the eight pieces for any eight
+// consecutive lines (Q4_K: lane u reads piece i of line u) that also separates the piece pairs {2q, 2q+1} of four
+// consecutive lines (Q6_K: lanes 2m, 2m+1 read pieces 2q, 2q+1 of line m). The code array must start on a 128-byte
+// boundary.
+__host__ __device__ __forceinline__ uint32_t swizzled_code_offset(uint32_t offset)
+{
+    const uint32_t line = offset >> 7;
+    const uint32_t g = ((line & 3u) << 1) | ((line >> 2) & 1u);
+    return offset ^ (g << 4);
+}
+
 template <class P>
 struct WeightViewT;
 struct GlobalMem {
@@ -49,6 +61,8 @@ struct GlobalMem {
     using index = uint64_t;
     static __device__ __forceinline__ uint4 v4(const void *p) { return ld_stream(p); }
     static __device__ __forceinline__ uint4 v4c(const void *p) { return ld_cached(p); }
+    // 16 activation codes at byte `offset` of the code array (a multiple of 16)
+    static __device__ __forceinline__ uint4 code16(const uint8_t *codes, uint64_t offset) { return ld_cached(codes + offset); }
     static __device__ __forceinline__ uint2 v2(const void *p) { return __ldg(reinterpret_cast<const uint2 *>(p)); }
     static __device__ __forceinline__ uint32_t u16(const void *p) { return ld_u16(p); }
     static __device__ __forceinline__ float f1(const void *p) { return __ldg(reinterpret_cast<const float *>(p)); }
@@ -66,6 +80,10 @@ struct SharedMem {
         return v;
     }
     static __device__ __forceinline__ uint4 v4c(uint32_t p) { return v4(p); }
+    // Activation codes in shared memory are stored with the 16-byte pieces of every 128-byte line permuted (see
+    // swizzled_code_offset): a lane reads pieces 128 bytes (Q4_K) or 32 bytes (Q6_K) apart from its neighbours, which
+    // would otherwise all fall into the same banks (an eight-way conflict on every load).
+    static __device__ __forceinline__ uint4 code16(uint32_t codes, uint32_t offset) { return v4(codes + swizzled_code_offset(offset)); }
     static __device__ __forceinline__ uint2 v2(uint32_t p)
     {
         uint2 v;
@@ -231,7 +249,7 @@ struct Q8PlanarXq8 {
     {
         using I = typename M::index;
         const I K = (I)K_, t = (I)t_, u = (I)u_;
-        out.c = M::v4c(a.codes + t * K + u * 16);
+        out.c = M::code16(a.codes, t * K + u * 16);
         out.d = M::f1(a.scales + (t * (K / 32) + (u >> 1)) * 4);
     }
     template <class M>
@@ -274,8 +292,8 @@ struct Q8NaturalXq8 {
     {
         using I = typename M::index;
         const I K = (I)K_, t = (I)t_, u = (I)u_;
-        out.c0 = M::v4c(a.codes + t * K + u * 32);
-        out.c1 = M::v4c(a.codes + t * K + u * 32 + 16);
+        out.c0 = M::code16(a.codes, t * K + u * 32);
+        out.c1 = M::code16(a.codes, t * K + u * 32 + 16);
         out.d = M::f1(a.scales + (t * (K / 32) + u) * 4);
     }
     template <class M>
@@ -360,10 +378,10 @@ struct Q4KXq8 {
     {
         using I = typename M::index;
         const I K = (I)K_, t = (I)t_, u = (I)u_;
-        const typename M::pointer codes = a.codes + t * K + u * 128;
+        const I codes = t * K + u * 128;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            out.c[i] = M::v4c(codes + 16 * i);
+            out.c[i] = M::code16(a.codes, codes + 16 * i);
         }
         const float4 d = M::f4(a.scales + (t * (K / 32) + u * 4) * 4);
         const uint4 s = M::v4c(a.sums + (t * (K / 16) + u * 8) * 2);
@@ -456,10 +474,10 @@ __device__ __forceinline__ void q6k_load_act(const ActPtrT<typename M::pointer> 
     const I K = (I)K_, t = (I)t_, u = (I)u_;
     const I sb = u >> 2;
     const I h = (u >> 1) & 1, i = u & 1;
-    const typename M::pointer codes = a.codes + t * K + sb * 256 + h * 128 + i * 16;
+    const I codes = t * K + sb * 256 + h * 128 + i * 16;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-        out.c[q] = M::v4c(codes + 32 * q);
+        out.c[q] = M::code16(a.codes, codes + 32 * q);
     }
     const float4 d = M::f4(a.scales + (t * (K / 32) + sb * 8 + h * 4) * 4);
     out.d[0] = d.x;

@@ -68,7 +68,7 @@ __device__ __forceinline__ void quantize_to_shared(const float *__restrict__ x, 
                 sum += __shfl_xor_sync(kFull, sum, 2);
                 if (first < K) {
                     const uint32_t packed = (uint32_t)(c0 & 0xff) | ((uint32_t)(c1 & 0xff) << 8) | ((uint32_t)(c2 & 0xff) << 16) | ((uint32_t)c3 << 24);
-                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst.codes + t * K + first), "r"(packed) : "memory");
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst.codes + swizzled_code_offset(t * K + first)), "r"(packed) : "memory");
                     if ((lane & 3) == 0) {
                         asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst.sums + (t * (K / 16) + first / 16) * 2), "h"((short)sum) : "memory");
                     }

@@ -25,7 +25,8 @@ def main():
     parser.add_argument("--cycles", type=int, default=4, help="times every copy is launched inside one graph (amortises the graph launch)")
     parser.add_argument("--reps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
-    parser.add_argument("--mode", default="xq8", choices=["xq8", "xf32", "gemm"])
+    parser.add_argument("--mode", default="xq8", choices=["xq8", "xf32", "gemm", "decode"])
+    parser.add_argument("--layers", type=int, default=4, help="decode mode: layers of the Qwen2.5-7B-shaped Q4_K_M model")
     parser.add_argument("--no-repack", action="store_true")
     parser.add_argument("--fused-quantize", action="store_true", help="time quantise + product together (xq8)")
     parser.add_argument("--no-graph", action="store_true", help="launch from the host each time instead of replaying one CUDA graph")
@@ -35,6 +36,9 @@ def main():
 
     import synapse_b200 as sb
     from synapse_b200 import synth
+
+    if args.mode == "decode":
+        return decode(args)
 
     ggml_type = {"q8_0": sb.Q8_0, "q4_k": sb.Q4_K, "q6_k": sb.Q6_K}[args.type]
     lib = sb.library()
@@ -95,6 +99,32 @@ def main():
                       "weight_gbs": source_bytes / microseconds / 1e3,
                       "tflops": 2.0 * args.rows * args.cols * args.tokens / microseconds / 1e6,
                       "checksum": float(y.double().sum().item())}))
+
+
+def decode(args):
+    """Whole single-token decode steps of a Qwen2.5-7B-shaped Q4_K_M model with ``--layers`` layers (a few layers keep
+    the device footprint small enough for a profiler): ``--warmup`` + ``--reps`` steps, one kernel launch each."""
+    import time
+
+    import synapse_b200 as sb
+    from synapse_b200 import decoder as dec
+    from synapse_b200 import synth
+
+    image = dec.ModelImage(**dict(dec.QWEN25_7B, layers=args.layers), context=64, matrix_types=dec.Q4KM_TYPES, embedding_type=synth.Q4_K,
+                           output_type=synth.Q4_K, seed=100)
+    with dec.Decoder(image) as model:
+        token, position = 5, 0
+        for _ in range(args.warmup):
+            token = model.forward_argmax([(0, token, position, 0)])[0]
+            position += 1
+        start = time.perf_counter()
+        for _ in range(args.reps):
+            token = model.forward_argmax([(0, token, position, 0)])[0]
+            position += 1
+        seconds = time.perf_counter() - start
+    print(json.dumps({"mode": "decode", "layers": args.layers, "steps": args.reps, "ms_per_step": seconds / args.reps * 1e3,
+                      "weight_gbs": image.matrix_bytes * args.reps / seconds / 1e9, "last_token": token,
+                      "device_faults": sb.library().device_faults()}))
 
 
 if __name__ == "__main__":
