@@ -85,6 +85,12 @@ def lib():
         handle.orc_decoder_destroy.argtypes = [c_void_p]
         handle.orc_decoder_forward.restype = c_int
         handle.orc_decoder_forward.argtypes = [c_void_p, c_int32, c_int32, c_int32, c_void_p]
+        for name, argtypes in (("orc_rms_norm", [c_void_p, c_void_p, ctypes.c_float, c_size_t, c_void_p]),
+                               ("orc_rotate_neox", [c_void_p, c_size_t, c_void_p, c_void_p]),
+                               ("orc_swiglu", [c_void_p, c_void_p, c_size_t, c_void_p]),
+                               ("orc_softmax", [c_void_p, c_size_t])):
+            getattr(handle, name).restype = None
+            getattr(handle, name).argtypes = argtypes
         handle.orc_argmax.restype = c_int32
         handle.orc_argmax.argtypes = [c_void_p, c_size_t]
         _lib = handle
@@ -97,6 +103,35 @@ def _c(array, dtype):
 
 def _addr(array: np.ndarray) -> int:
     return array.ctypes.data
+
+
+def rms_norm(x, weight, epsilon):
+    """RMSNorm with the FP64 sum of squares of the optimized CPU executor."""
+    x, weight = _c(x, np.float32), _c(weight, np.float32)
+    out = np.empty_like(x)
+    lib().orc_rms_norm(_addr(x), _addr(weight), np.float32(epsilon), x.size, _addr(out))
+    return out
+
+
+def rotate_neox(x, cosines, sines):
+    """NeoX rotation of one head (first half against second half)."""
+    out = _c(x, np.float32).copy()
+    cosines, sines = _c(cosines, np.float32), _c(sines, np.float32)
+    lib().orc_rotate_neox(_addr(out), out.size, _addr(cosines), _addr(sines))
+    return out
+
+
+def swiglu(gate, up):
+    gate, up = _c(gate, np.float32), _c(up, np.float32)
+    out = np.empty_like(gate)
+    lib().orc_swiglu(_addr(gate), _addr(up), gate.size, _addr(out))
+    return out
+
+
+def softmax(scores):
+    out = _c(scores, np.float32).copy()
+    lib().orc_softmax(_addr(out), out.size)
+    return out
 
 
 def fp16_to_f32(bits: int) -> float:

@@ -926,6 +926,48 @@ static void rms_norm(const float *x, const float *w, float epsilon, size_t n, fl
     }
 }
 
+/* The pieces of the step, exported so that the reference's own operator vectors can be replayed against them
+ * (ReferenceOperatorsTests.cs:105-164, RopeFrequenciesTests.cs:13-34). */
+void orc_rms_norm(const float *x, const float *w, float epsilon, size_t n, float *out) { rms_norm(x, w, epsilon, n, out); }
+
+/* NeoX rotation of one head: element i against element i + head_dim/2 (Qwen2CpuState.cs:85-105). */
+void orc_rotate_neox(float *x, size_t head_dim, const float *cosines, const float *sines)
+{
+    const size_t half = head_dim / 2;
+    for (size_t i = 0; i < half; ++i) {
+        float a = x[i], b = x[i + half];
+        x[i] = a * cosines[i] - b * sines[i];
+        x[i + half] = a * sines[i] + b * cosines[i];
+    }
+}
+
+/* SwiGLU: silu(gate) * up (Qwen2CpuExecutor.cs:189-196). */
+void orc_swiglu(const float *gate, const float *up, size_t n, float *out)
+{
+    for (size_t i = 0; i < n; ++i) {
+        float value = gate[i];
+        out[i] = value / (1.0f + expf(-value)) * up[i];
+    }
+}
+
+/* Max-subtracted softmax in place; returns nothing, scores[p] become the weights (Qwen2CpuAttention.cs:120-150). */
+void orc_softmax(float *scores, size_t n)
+{
+    float maximum = -INFINITY;
+    for (size_t p = 0; p < n; ++p) {
+        maximum = fmaxf(maximum, scores[p]);
+    }
+    float sum = 0.0f;
+    for (size_t p = 0; p < n; ++p) {
+        scores[p] = expf(scores[p] - maximum);
+        sum += scores[p];
+    }
+    const float inverse = 1.0f / sum;
+    for (size_t p = 0; p < n; ++p) {
+        scores[p] *= inverse;
+    }
+}
+
 /* One quantised-activation product over all rows with the contract of the matching encoding (O2 / O6); large
  * matrices are split into row ranges over threads, which does not change any row's arithmetic. */
 typedef struct {
@@ -1054,11 +1096,7 @@ int orc_decoder_forward(orc_decoder *d, int32_t slot, int32_t token, int32_t pos
         }
         for (uint32_t head = 0; head < s->heads + s->kv_heads; ++head) {
             float *x = head < s->heads ? q + (size_t)head * s->head_dim : k + (size_t)(head - s->heads) * s->head_dim;
-            for (size_t i = 0; i < half; ++i) {
-                float a = x[i], b = x[i + half];
-                x[i] = a * cosines[i] - b * sines[i];
-                x[i + half] = a * sines[i] + b * cosines[i];
-            }
+            orc_rotate_neox(x, s->head_dim, cosines, sines);
         }
         for (uint32_t kh = 0; kh < s->kv_heads; ++kh) {
             memcpy(d->keys + kv_index(s, (uint32_t)slot, l, kh, (uint32_t)position), k + (size_t)kh * s->head_dim, sizeof(float) * s->head_dim);
@@ -1068,25 +1106,18 @@ int orc_decoder_forward(orc_decoder *d, int32_t slot, int32_t token, int32_t pos
         for (uint32_t head = 0; head < s->heads; ++head) {
             const float *qh = q + (size_t)head * s->head_dim;
             const uint32_t kh = head / group;
-            float maximum = -INFINITY;
             for (int32_t p = 0; p <= position; ++p) {
                 const float *kp = d->keys + kv_index(s, (uint32_t)slot, l, kh, (uint32_t)p);
                 float dot = 0.0f;
                 for (uint32_t i = 0; i < s->head_dim; ++i) dot += qh[i] * kp[i];
                 scores[p] = dot * attention_scale;
-                maximum = fmaxf(maximum, scores[p]);
             }
-            float sum = 0.0f;
-            for (int32_t p = 0; p <= position; ++p) {
-                scores[p] = expf(scores[p] - maximum);
-                sum += scores[p];
-            }
-            const float inverse = 1.0f / sum;
+            orc_softmax(scores, (size_t)position + 1);
             float *out = attn + (size_t)head * s->head_dim;
             for (uint32_t i = 0; i < s->head_dim; ++i) out[i] = 0.0f;
             for (int32_t p = 0; p <= position; ++p) {
                 const float *vp = d->values + kv_index(s, (uint32_t)slot, l, kh, (uint32_t)p);
-                const float weight = scores[p] * inverse;
+                const float weight = scores[p];
                 for (uint32_t i = 0; i < s->head_dim; ++i) out[i] += weight * vp[i];
             }
         }
@@ -1097,10 +1128,7 @@ int orc_decoder_forward(orc_decoder *d, int32_t slot, int32_t token, int32_t pos
         orc_q8_quantize_row(normed, hidden, codes, scales);
         decoder_matmul(d, layer_encoding(L, 4), L->gate, ffn, hidden, codes, scales, gate);
         decoder_matmul(d, layer_encoding(L, 5), L->up, ffn, hidden, codes, scales, up);
-        for (size_t i = 0; i < ffn; ++i) {
-            float value = gate[i];
-            ff[i] = value / (1.0f + expf(-value)) * up[i];
-        }
+        orc_swiglu(gate, up, ffn, ff);
         orc_q8_quantize_row(ff, ffn, codes, scales);
         decoder_matmul(d, layer_encoding(L, 6), L->down, hidden, ffn, codes, scales, normed);
         for (size_t i = 0; i < hidden; ++i) h[i] += normed[i];
