@@ -49,6 +49,9 @@ def parse_args():
                              "fused: every product quantises its FP32 input inside the kernel")
     parser.add_argument("--serial", action="store_true", help="run q/k/v and gate/up one after the other instead of on parallel graph branches")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                        help="N > 1: output slices are stored into every GPU's copy by the product kernel itself (peer), or "
+                             "all-gathered by NCCL after each product")
     parser.add_argument("--no-cpu", action="store_true")
     return parser.parse_args()
 
@@ -209,6 +212,12 @@ def main():
         run_reference_arm(args)
         return
 
+    # Libraries print to standard output (NCCL its version line): the one JSON line must be alone there, so everything
+    # else goes to standard error and the line is written to the saved descriptor at the end.
+    sys.stdout.flush()
+    result_fd = os.dup(1)
+    os.dup2(2, 1)
+
     import torch
     import torch.distributed as dist
 
@@ -253,7 +262,22 @@ def main():
     x_host = {3584: synth.activations(1, 3584, seed=5), 18944: synth.activations(1, 18944, seed=6)}
     x_dev = {k: torch.from_numpy(v).to(device) for k, v in x_host.items()}
     scratch = {k: torch.empty(lib.activation_scratch_bytes(1, k) + 256, dtype=torch.uint8, device=device) for k in x_host}
-    out_full = {(m[0].split(".")[-1], m[2]): torch.zeros(m[2], dtype=torch.float32, device=device) for m in matrices}
+    peers = None
+    if world > 1 and args.gather == "peer":
+        # every rank's full output vectors live in one buffer that all other ranks map: the kernels gather by storing
+        try:
+            peers = sharding.PeerOutputs({f"{m[0].split('.')[-1]}:{m[2]}": m[2] for m in matrices}, device)
+        except Exception as error:
+            sys.stderr.write(f"rank {rank}: peer mapping failed ({error}); gathering with NCCL\n")
+            peers = None
+        agreed = torch.tensor([1 if peers is not None else 0], device=device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) == 0:
+            peers = None
+    if peers is not None:
+        out_full = {(m[0].split(".")[-1], m[2]): peers.view(f"{m[0].split('.')[-1]}:{m[2]}") for m in matrices}
+    else:
+        out_full = {(m[0].split(".")[-1], m[2]): torch.zeros(m[2], dtype=torch.float32, device=device) for m in matrices}
     out_shard = {(m[0].split(".")[-1], m[4]): torch.zeros(m[4], dtype=torch.float32, device=device) for m in matrices}
 
     def aligned(tensor):
@@ -263,6 +287,11 @@ def main():
 
     def product(entry, stream):
         name, ggml_type, rows, columns, shard_rows, matrix = entry
+        if peers is not None:
+            first_row, _ = sharding.shard_rows(rows, world, rank)
+            own, others = peers.pointers(f"{name.split('.')[-1]}:{rows}", first_row)
+            matrix.matmul_q8_gather_device(aligned(scratch[columns]), 1, own, shard_rows, others, stream=stream.cuda_stream)
+            return
         target = out_shard[(name.split(".")[-1], shard_rows)] if world > 1 else out_full[(name.split(".")[-1], rows)]
         if args.quantize == "fused":
             matrix.matvec_device(x_dev[columns].data_ptr(), 1, columns, target.data_ptr(), shard_rows, sb.MODE_XQ8,
@@ -281,7 +310,7 @@ def main():
 
     def parallel(entries, main):
         """Independent products of the same input: the first on the main stream, the others on side streams."""
-        if args.serial or world > 1 or len(entries) == 1:
+        if args.serial or (world > 1 and peers is None) or len(entries) == 1:
             for entry in entries:
                 product(entry, main)
             return
@@ -519,11 +548,13 @@ def main():
                            "activation_contract": "xq8 (Q8_0 activation quantiser reproduced on device)",
                            "layout": "Q4_K file layout; Q6_K repacked to planes at load", "cuda_graph": bool(graph is not None),
                            "quantize": args.quantize, "branches": "serial" if args.serial else "q|k|v and gate|up on parallel graph branches",
-                           "l2": "weights per step exceed L2 35x, no flush", "parallelism": f"row-shard x{world}" if world > 1 else "single gpu",
+                           "l2": "weights per step exceed L2 35x, no flush", "parallelism": (f"row-shard x{world}, " + ("slices stored into every GPU's copy by the product kernel" if peers is not None
+                                                                     else "NCCL all-gather per product")) if world > 1 else "single gpu",
                            "tokens_per_s": 1e3 / ms_per_step},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_per_matrix_calls": per_matrix, "extras": extras, "clocks": clocks,
                 "gpu_launches": int(launches_per_step * args.steps)}
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.write(result_fd, (json.dumps(line) + "\n").encode())
     if world > 1:
         # Captured collectives keep the communicator busy at teardown on some NCCL builds: release the graphs first and
         # do not let a stuck destroy hold the job (the result line is already printed).

@@ -181,6 +181,36 @@ SYN_B200_API int32_t syn_b200_matmul_q8_ex_dev(const syn_b200_matrix *matrix, ui
                                                const void *scratch, uint64_t tokens, float *y, uint64_t out_stride,
                                                const syn_b200_epilogue *epilogue, void *stream);
 
+/* syn_b200_matmul_q8_dev for a row shard of a matrix that is split over several GPUs: the kernel stores every result
+ * into `y` AND at the same position of `peer_count` (at most 7) further vectors, the other GPUs' copies of the output
+ * mapped into this process (CUDA IPC or symmetric memory). `y` and every `peer_outputs[i]` are already offset to the
+ * shard's first row; `peer_outputs` is a host array of device pointers. The gather of the output slices thus happens
+ * inside the product, as plain stores over NVLink, instead of an all-gather after it; the caller still owes the ranks a
+ * synchronisation before anyone reads a full vector. The reference has no multi-GPU path
+ * (native/synapse-gpu/src/Features/GpuKernels/ffi.rs:113-271 drives one device); this is the exchange step of the
+ * row-sharded configuration. */
+SYN_B200_API int32_t syn_b200_matmul_q8_gather_dev(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
+                                                   const void *scratch, uint64_t tokens, float *y, uint64_t out_stride,
+                                                   float *const *peer_outputs, uint32_t peer_count, void *stream);
+
+/* A zero-filled device buffer that other processes on the same box can map (CUDA IPC), for the output vectors of
+ * row-sharded products: create it on the owning GPU, hand the 64-byte handle to the other ranks by any means, and let
+ * each of them open it WITH ITS OWN GPU CURRENT, which maps the memory for that GPU's kernels over NVLink (peer access is
+ * enabled as part of the open). `open` verifies the mapping with a 4-byte copy before it returns; status 3 when the
+ * devices have no peer path or the handle cannot be mapped. `close` takes what `open` returned, `destroy` what `create`
+ * returned. No reference counterpart (single-device ABI). */
+SYN_B200_API int32_t syn_b200_shared_buffer_create(uint64_t bytes, void **device_ptr, uint8_t handle[64]);
+SYN_B200_API int32_t syn_b200_shared_buffer_open(const uint8_t handle[64], void **device_ptr);
+SYN_B200_API void syn_b200_shared_buffer_close(void *device_ptr);
+SYN_B200_API void syn_b200_shared_buffer_destroy(void *device_ptr);
+
+/* Lets kernels of the calling thread's current device read and write memory of `peer_device` (cudaDeviceEnablePeerAccess;
+ * already enabled is not an error). A process that maps another GPU's buffer (CUDA IPC) must call this for that GPU before
+ * it passes a pointer mapped for ANOTHER device to syn_b200_matmul_q8_gather_dev (syn_b200_shared_buffer_open maps for the
+ * current device and needs no further call).
+ * Status 3 when the two devices have no peer path. No reference counterpart (single-device ABI). */
+SYN_B200_API int32_t syn_b200_enable_peer_access(int32_t peer_device);
+
 /* FP32 device activations x matrix rows. XQ8 mode quantises into `scratch` first (required, at least
  * syn_b200_activation_scratch_bytes); XF32 mode ignores scratch. */
 SYN_B200_API int32_t syn_b200_matvec_dev(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,

@@ -79,6 +79,13 @@ _EXPORTS = {
     "syn_b200_quantize_q8_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_uint64, c_void_p, c_uint64, c_void_p]),
     "syn_b200_matmul_q8_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, c_uint32, c_void_p]),
     "syn_b200_matvec_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32, c_uint32, c_void_p, c_uint64, c_void_p]),
+    "syn_b200_shared_buffer_create": (c_int32, [c_uint64, POINTER(c_void_p), POINTER(c_uint8)]),
+    "syn_b200_shared_buffer_open": (c_int32, [POINTER(c_uint8), POINTER(c_void_p)]),
+    "syn_b200_shared_buffer_close": (None, [c_void_p]),
+    "syn_b200_shared_buffer_destroy": (None, [c_void_p]),
+    "syn_b200_enable_peer_access": (c_int32, [c_int32]),
+    "syn_b200_matmul_q8_gather_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, POINTER(c_void_p), c_uint32,
+                                                c_void_p]),
     "syn_b200_matmul_q8_ex_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, POINTER(Epilogue), c_void_p]),
     "syn_b200_matvec_ex_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32, POINTER(Epilogue), c_void_p, c_uint64, c_void_p]),
     "syn_b200_matvec_static": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32, c_void_p]),
@@ -159,6 +166,29 @@ class NativeB200Library:
         info = DeviceInfo()
         self.check(self._h.syn_b200_probe(byref(info)))
         return info
+
+    def shared_buffer_create(self, size: int) -> tuple[int, bytes]:
+        """(device pointer, 64-byte handle) of a zero-filled buffer on the current device that other processes can map."""
+        pointer, handle = c_void_p(), (c_uint8 * 64)()
+        self.check(self._h.syn_b200_shared_buffer_create(size, byref(pointer), handle))
+        return int(pointer.value), bytes(handle)
+
+    def shared_buffer_open(self, handle: bytes) -> int:
+        """Maps another process's shared buffer for the kernels of the current device; returns the device pointer."""
+        pointer, raw = c_void_p(), (c_uint8 * 64).from_buffer_copy(handle)
+        self.check(self._h.syn_b200_shared_buffer_open(raw, byref(pointer)))
+        return int(pointer.value)
+
+    def shared_buffer_close(self, pointer: int) -> None:
+        self._h.syn_b200_shared_buffer_close(pointer)
+
+    def shared_buffer_destroy(self, pointer: int) -> None:
+        self._h.syn_b200_shared_buffer_destroy(pointer)
+
+    def enable_peer_access(self, peer_device: int) -> None:
+        """Lets kernels of the current device store into memory of ``peer_device`` (needed before mapped peer buffers are
+        passed to ``matmul_q8_gather_device``)."""
+        self.check(self._h.syn_b200_enable_peer_access(peer_device))
 
     def launch_count(self, reset: bool = False) -> int:
         return int(self._h.syn_b200_launch_count(1 if reset else 0))
@@ -362,6 +392,15 @@ class QuantizedMatrix:
         epilogue = Epilogue(bias_ptr or None, gate_ptr or None, gate_stride, 1 if accumulate else 0, 0)
         self._lib.check(self._lib.raw.syn_b200_matmul_q8_ex_dev(self.handle, row_start, row_count, scratch_ptr, tokens, y_ptr, out_stride,
                                                                byref(epilogue), stream))
+
+    def matmul_q8_gather_device(self, scratch_ptr: int, tokens: int, y_ptr: int, out_stride: int, peer_ptrs, stream: int = 0,
+                                row_start: int = 0, row_count: int | None = None) -> None:
+        """The product of a row shard whose kernel also stores every result into the other GPUs' copies of the output
+        (``peer_ptrs``: device pointers mapped into this process, offset to the shard's first row like ``y_ptr``)."""
+        row_count = self.rows - row_start if row_count is None else row_count
+        peers = (c_void_p * max(len(peer_ptrs), 1))(*peer_ptrs)
+        self._lib.check(self._lib.raw.syn_b200_matmul_q8_gather_dev(self.handle, row_start, row_count, scratch_ptr, tokens, y_ptr, out_stride,
+                                                                   peers, len(peer_ptrs), stream))
 
     def matvec_static(self, x_ptr: int, tokens: int, in_stride: int, y_ptr: int, out_stride: int, epilogue: int = EPILOGUE_STORE,
                       stream: int = 0, row_start: int = 0, row_count: int | None = None) -> None:

@@ -4,6 +4,7 @@
 // native/synapse-kernels/src/Features/CpuKernels/q8_0.rs:212-246).
 #include <cstdlib>
 #include <exception>
+#include <cstring>
 #include <mutex>
 #include <new>
 #include <string>
@@ -626,6 +627,161 @@ int32_t syn_b200_matmul_q8_ex_dev(const syn_b200_matrix *matrix, uint64_t row_st
         }
         if (reinterpret_cast<uintptr_t>(scratch) & 255) {
             return fail(SYN_B200_INVALID_ARGUMENT, "activation scratch must be 256-byte aligned");
+        }
+        MatvecArgs args{};
+        args.matrix = matrix;
+        args.row_start = row_start;
+        args.row_count = row_count;
+        args.tokens = tokens;
+        args.act = act_view(scratch, tokens, matrix->columns);
+        args.act_ready = true;
+        args.y = y;
+        args.out_stride = out_stride;
+        args.mode = SYN_B200_MODE_XQ8;
+        args.epilogue = SYN_B200_EPILOGUE_STORE;
+        args.fused = fused;
+        cudaError_t error = launch_matvec(args, static_cast<cudaStream_t>(stream));
+        return error == cudaSuccess ? SYN_B200_OK : cuda_fail(error, "launching the matrix-vector kernel");
+    });
+}
+
+int32_t syn_b200_shared_buffer_create(uint64_t bytes, void **device_ptr, uint8_t handle[64])
+{
+    if (!device_ptr || !handle) {
+        return fail(SYN_B200_NULL_POINTER, "buffer or handle output");
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is passed as 64 bytes");
+    return guarded([&]() -> int32_t {
+        if (bytes == 0) {
+            return fail(SYN_B200_INVALID_ARGUMENT, "a shared buffer needs at least one byte");
+        }
+        void *p = nullptr;
+        cudaError_t error = cudaMalloc(&p, bytes);
+        if (error != cudaSuccess) {
+            cudaGetLastError();
+            return error == cudaErrorMemoryAllocation ? fail(SYN_B200_OUT_OF_MEMORY, "allocating the shared buffer")
+                                                      : cuda_fail(error, "allocating the shared buffer");
+        }
+        error = cudaMemset(p, 0, bytes);
+        cudaIpcMemHandle_t ipc;
+        if (error == cudaSuccess) {
+            error = cudaIpcGetMemHandle(&ipc, p);
+        }
+        if (error != cudaSuccess) {
+            cudaGetLastError();
+            cudaFree(p);
+            return cuda_fail(error, "exporting the shared buffer");
+        }
+        memcpy(handle, &ipc, sizeof(ipc));
+        *device_ptr = p;
+        return SYN_B200_OK;
+    });
+}
+
+int32_t syn_b200_shared_buffer_open(const uint8_t handle[64], void **device_ptr)
+{
+    if (!device_ptr || !handle) {
+        return fail(SYN_B200_NULL_POINTER, "handle or buffer output");
+    }
+    return guarded([&]() -> int32_t {
+        cudaIpcMemHandle_t ipc;
+        memcpy(&ipc, handle, sizeof(ipc));
+        void *p = nullptr;
+        // with the CALLER's device current: the mapping is made for this device's kernels, peer access included
+        cudaError_t error = cudaIpcOpenMemHandle(&p, ipc, cudaIpcMemLazyEnablePeerAccess);
+        if (error != cudaSuccess) {
+            cudaGetLastError();
+            return fail(SYN_B200_UNAVAILABLE, std::string("the shared buffer cannot be mapped: ") + cudaGetErrorString(error));
+        }
+        // prove the mapping before any kernel stores through it
+        cudaPointerAttributes attributes{};
+        uint32_t probe = 0;
+        error = cudaPointerGetAttributes(&attributes, p);
+        if (error == cudaSuccess && attributes.type != cudaMemoryTypeDevice) {
+            error = cudaErrorInvalidDevicePointer;
+        }
+        if (error == cudaSuccess) {
+            error = cudaMemcpy(&probe, p, sizeof(probe), cudaMemcpyDeviceToHost);
+        }
+        if (error != cudaSuccess) {
+            cudaGetLastError();
+            cudaIpcCloseMemHandle(p);
+            return fail(SYN_B200_UNAVAILABLE, std::string("the mapped shared buffer is not usable from this device: ") + cudaGetErrorString(error));
+        }
+        *device_ptr = p;
+        return SYN_B200_OK;
+    });
+}
+
+void syn_b200_shared_buffer_close(void *device_ptr)
+{
+    if (device_ptr) {
+        cudaIpcCloseMemHandle(device_ptr);
+    }
+}
+
+void syn_b200_shared_buffer_destroy(void *device_ptr)
+{
+    if (device_ptr) {
+        cudaFree(device_ptr);
+    }
+}
+
+int32_t syn_b200_enable_peer_access(int32_t peer_device)
+{
+    return guarded([&]() -> int32_t {
+        int device = 0, count = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || cudaGetDeviceCount(&count) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(SYN_B200_UNAVAILABLE, "no usable CUDA device");
+        }
+        if (peer_device < 0 || peer_device >= count) {
+            return fail(SYN_B200_INVALID_ARGUMENT, "device " + std::to_string(peer_device) + " does not exist");
+        }
+        if (peer_device == device) {
+            return SYN_B200_OK;
+        }
+        int can = 0;
+        cudaError_t error = cudaDeviceCanAccessPeer(&can, device, peer_device);
+        if (error != cudaSuccess || !can) {
+            cudaGetLastError();
+            return fail(SYN_B200_UNAVAILABLE, "device " + std::to_string(device) + " has no peer path to device " + std::to_string(peer_device));
+        }
+        error = cudaDeviceEnablePeerAccess(peer_device, 0);
+        if (error == cudaErrorPeerAccessAlreadyEnabled) {
+            cudaGetLastError();
+            return SYN_B200_OK;
+        }
+        return error == cudaSuccess ? SYN_B200_OK : cuda_fail(error, "enabling peer access");
+    });
+}
+
+int32_t syn_b200_matmul_q8_gather_dev(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count, const void *scratch,
+                                      uint64_t tokens, float *y, uint64_t out_stride, float *const *peer_outputs, uint32_t peer_count,
+                                      void *stream)
+{
+    if (!matrix || !scratch || !y || (peer_count > 0 && !peer_outputs)) {
+        return fail(SYN_B200_NULL_POINTER, "matrix, scratch, output or peer outputs");
+    }
+    return guarded([&]() -> int32_t {
+        int32_t status = check_product(matrix, row_start, row_count, tokens, out_stride, nullptr);
+        if (status == SYN_B200_OK) status = check_device(matrix);
+        if (status != SYN_B200_OK) {
+            return status;
+        }
+        if (peer_count > 7) {
+            return fail(SYN_B200_INVALID_ARGUMENT, "at most 7 peer outputs, got " + std::to_string(peer_count));
+        }
+        if (reinterpret_cast<uintptr_t>(scratch) & 255) {
+            return fail(SYN_B200_INVALID_ARGUMENT, "activation scratch must be 256-byte aligned");
+        }
+        Epilogue fused;
+        fused.peer_count = peer_count;
+        for (uint32_t i = 0; i < peer_count; ++i) {
+            if (!peer_outputs[i]) {
+                return fail(SYN_B200_NULL_POINTER, "peer output " + std::to_string(i));
+            }
+            fused.peers[i] = peer_outputs[i];
         }
         MatvecArgs args{};
         args.matrix = matrix;

@@ -134,6 +134,10 @@ struct Epilogue {
     const float *gate = nullptr;  // gate projection results, [token][row] with gate_stride, same row origin
     uint64_t gate_stride = 0;
     uint32_t accumulate = 0;
+    // Row-sharded products: every result is also stored at the same position of these vectors (the other GPUs' copies
+    // of the output, peer-mapped), so the gather of the slices happens inside the product.
+    uint32_t peer_count = 0;
+    float *peers[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
 // matvec.cu

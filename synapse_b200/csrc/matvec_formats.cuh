@@ -202,7 +202,11 @@ __device__ __forceinline__ void store_result(const Epilogue &e, float *__restric
         v = g / (1.0f + expf(-g)) * v;
     }
     float *destination = y + token * out_stride + row;
-    *destination = e.accumulate ? *destination + v : v;
+    v = e.accumulate ? *destination + v : v;
+    *destination = v;
+    for (uint32_t peer = 0; peer < e.peer_count; ++peer) {
+        e.peers[peer][token * out_stride + row] = v;  // plain stores over NVLink into the peer's copy
+    }
 }
 
 __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }

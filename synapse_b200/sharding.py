@@ -45,3 +45,68 @@ def gather_outputs(local, full, group=None):
     dist.all_gather_into_tensor(staged.view(-1), local.contiguous().view(-1), group=group)
     full.copy_(staged.permute(1, 0, 2).reshape(tokens, world * count))
     return full
+
+
+class _DeviceArray:
+    """Lets torch wrap a raw device pointer (the CUDA array interface)."""
+
+    def __init__(self, pointer: int, count: int):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (pointer, False), "version": 3}
+
+
+class PeerOutputs:
+    """One flat FP32 device buffer per rank, each mapped into every other rank's process (CUDA IPC, through
+    ``syn_b200_shared_buffer_*``), for the gather that the product kernel performs itself
+    (``syn_b200_matmul_q8_gather_dev``): a rank stores its slice of an output vector into its own buffer and into all
+    peers' buffers at the same offset.
+
+    ``layout`` maps a name to the length of that output vector; all ranks must pass the same layout. The ranks of the
+    group must be GPUs of one box with peer access to each other; every rank must have its own GPU current. Raises
+    ``BackendUnavailableError`` when a peer's buffer cannot be mapped (the caller then gathers with NCCL)."""
+
+    def __init__(self, layout: dict, device, group=None):
+        import torch
+        import torch.distributed as dist
+
+        from . import library
+
+        self.offsets, total = {}, 0
+        for name, length in layout.items():
+            self.offsets[name] = (total, int(length))
+            total += (int(length) + 63) // 64 * 64  # 256-byte aligned vectors
+        total = max(total, 64)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        torch.cuda.set_device(device)
+        self._lib = library()
+        self._own, handle = self._lib.shared_buffer_create(4 * total)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle, group=group)
+        self.bases, self._opened = [], []
+        for r in range(self.world):
+            if r == self.rank:
+                self.bases.append(self._own)
+            else:
+                mapped = self._lib.shared_buffer_open(handles[r])
+                self._opened.append(mapped)
+                self.bases.append(mapped)
+        self.local = torch.as_tensor(_DeviceArray(self._own, total), device=device)
+        dist.barrier(group=group)
+
+    def close(self):
+        for mapped in self._opened:
+            self._lib.shared_buffer_close(mapped)
+        self._opened = []
+        if self._own:
+            self._lib.shared_buffer_destroy(self._own)
+            self._own = 0
+
+    def view(self, name):
+        """This rank's copy of the full output vector ``name``."""
+        offset, length = self.offsets[name]
+        return self.local[offset:offset + length]
+
+    def pointers(self, name, first_row: int):
+        """(own pointer, [peer pointers]) of element ``first_row`` of vector ``name``."""
+        offset, _ = self.offsets[name]
+        at = 4 * (offset + first_row)
+        return self.bases[self.rank] + at, [self.bases[r] + at for r in range(self.world) if r != self.rank]
