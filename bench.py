@@ -272,7 +272,8 @@ def main():
             peers = None
         agreed = torch.tensor([1 if peers is not None else 0], device=device)
         dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
-        if int(agreed.item()) == 0:
+        if int(agreed.item()) == 0 and peers is not None:
+            peers.close()
             peers = None
     if peers is not None:
         out_full = {(m[0].split(".")[-1], m[2]): peers.view(f"{m[0].split('.')[-1]}:{m[2]}") for m in matrices}

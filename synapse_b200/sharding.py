@@ -62,13 +62,15 @@ class PeerOutputs:
 
     ``layout`` maps a name to the length of that output vector; all ranks must pass the same layout. The ranks of the
     group must be GPUs of one box with peer access to each other; every rank must have its own GPU current. Raises
-    ``BackendUnavailableError`` when a peer's buffer cannot be mapped (the caller then gathers with NCCL)."""
+    ``BackendUnavailableError`` when a buffer cannot be created or mapped; because one rank may fail where another does
+    not, the ranks must then agree (one all-reduce) before they rely on it, and synchronise once before the first
+    product so that nobody stores into a buffer that is not mapped yet."""
 
     def __init__(self, layout: dict, device, group=None):
         import torch
         import torch.distributed as dist
 
-        from . import library
+        from . import BackendUnavailableError, library
 
         self.offsets, total = {}, 0
         for name, length in layout.items():
@@ -78,19 +80,36 @@ class PeerOutputs:
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         torch.cuda.set_device(device)
         self._lib = library()
-        self._own, handle = self._lib.shared_buffer_create(4 * total)
+        self._own, self._opened, self.bases = 0, [], []
+        # Collectives are reached by every rank whatever fails locally, and a failure anywhere fails all ranks alike:
+        # a rank that left early would leave the others waiting in the exchange.
+        handle, problem = None, None
+        try:
+            self._own, handle = self._lib.shared_buffer_create(4 * total)
+        except Exception as error:  # reported after the exchange
+            problem = error
         handles = [None] * self.world
         dist.all_gather_object(handles, handle, group=group)
-        self.bases, self._opened = [], []
+        if any(h is None for h in handles):
+            self.close()
+            raise BackendUnavailableError(f"a rank could not create its shared output buffer ({problem or 'another rank'})")
         for r in range(self.world):
             if r == self.rank:
                 self.bases.append(self._own)
-            else:
+                continue
+            try:
                 mapped = self._lib.shared_buffer_open(handles[r])
+            except Exception as error:
+                problem = problem or error
+                mapped = 0
+            if mapped:
                 self._opened.append(mapped)
-                self.bases.append(mapped)
+            self.bases.append(mapped)
+        if problem is not None:
+            # no collective follows in here: the caller agrees with the other ranks on whether everyone got this far
+            self.close()
+            raise BackendUnavailableError(f"a peer's output buffer could not be mapped ({problem})")
         self.local = torch.as_tensor(_DeviceArray(self._own, total), device=device)
-        dist.barrier(group=group)
 
     def close(self):
         for mapped in self._opened:

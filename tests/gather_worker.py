@@ -29,6 +29,7 @@ def main():
         scratch_ptr = (scratch.data_ptr() + 255) // 256 * 256
         sb.quantize_device(x.data_ptr(), 1, columns, columns, scratch_ptr, need, 0)
         peers = sharding.PeerOutputs({"y": rows}, device)
+        dist.barrier()  # every rank has mapped every buffer
         first, count = sharding.shard_rows(rows, world, rank)
         offset, size = sharding.shard_bytes(ggml_type, rows, columns, world, rank)
         with sb.QuantizedMatrix(weights, ggml_type, rows, columns) as whole, \

@@ -116,3 +116,23 @@ def test_single_kernel_step_equals_the_per_operation_kernels(monkeypatch, shape,
                 assert program.forward_argmax([(0, token, position, 0)]) == [int(np.argmax(a))]
                 token = int(np.argmax(a))
     assert lib.device_faults() == 0
+
+
+def test_single_kernel_step_over_a_long_run_and_two_sessions(monkeypatch):
+    """The single-kernel step against the per-operation kernels far into the context (every attention warp has many
+    positions to walk) and with two sessions interleaved in one cache: logits stay bit-identical, so do the caches."""
+    shape = dict(layers=2, hidden=512, feed_forward=1024, heads=4, kv_heads=2, vocabulary=768, context=160)
+    image = dec.ModelImage(**shape, matrix_types=dec.Q4KM_TYPES, embedding_type=synth.Q4_K, output_type=synth.Q4_K, seed=12, session_slots=2)
+    monkeypatch.setenv("SYN_B200_DECODE_PROGRAM", "1")
+    with dec.Decoder(image) as program:
+        monkeypatch.setenv("SYN_B200_DECODE_PROGRAM", "0")
+        with dec.Decoder(image) as kernels:
+            monkeypatch.delenv("SYN_B200_DECODE_PROGRAM")
+            tokens = [3, 5]
+            for position in range(150):
+                for slot in (0, 1):
+                    a = program.forward([(slot, tokens[slot], position, 0)])[0]
+                    b = kernels.forward([(slot, tokens[slot], position, 0)])[0]
+                    assert a.tobytes() == b.tobytes(), (position, slot)
+                    tokens[slot] = int(np.argmax(a)) if position % 7 else (position * 13 + slot) % 768
+    assert sb.library().device_faults() == 0
