@@ -537,6 +537,55 @@ def main():
         extras["qwen2.5-0.5b_q8_0_decode"] = {"tokens_per_s": 32 / seconds, "weight_gbs": small.matrix_bytes * 32 / seconds / 1e9,
                                                "api": "syn_b200_decoder_forward_argmax, one call per token"}
 
+    if extras is not None:
+        # single-kernel figures on the other shapes the baseline names: config 0 (Q8_0 4864x896), config 4's matrices at
+        # batch 1 on one GPU, and the vocabulary projection in both encodings a Q4_K_M file may use for it
+        def kernel_rate(ggml_type, rows, columns, copies):
+            hold = [sb.QuantizedMatrix(synth.matrix(ggml_type, rows, columns, seed=200 + c, name="shape"), ggml_type, rows, columns)
+                    for c in range(copies)]
+            xs = torch.from_numpy(synth.activations(1, columns, seed=7)).to(device)
+            need = lib.activation_scratch_bytes(1, columns)
+            work = torch.empty(need + 256, dtype=torch.uint8, device=device)
+            work_ptr = (work.data_ptr() + 255) // 256 * 256
+            ys = torch.zeros(rows, dtype=torch.float32, device=device)
+            sb.quantize_device(xs.data_ptr(), 1, columns, columns, work_ptr, need, stream.cuda_stream)
+
+            def once(s):
+                for _ in range(4):
+                    for matrix in hold:
+                        matrix.matmul_q8_device(work_ptr, 1, ys.data_ptr(), rows, stream=s.cuda_stream)
+
+            with torch.cuda.stream(stream):
+                once(stream)
+                stream.synchronize()
+            replay = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(replay, stream=stream):
+                once(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    replay.replay()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record(stream)
+                for _ in range(10):
+                    replay.replay()
+                t1.record(stream)
+                stream.synchronize()
+            microseconds = t0.elapsed_time(t1) * 1e3 / (10 * 4 * copies)
+            size = rows * synth.row_bytes(ggml_type, columns)
+            del replay
+            for matrix in hold:
+                matrix.close()
+            return {"us": microseconds, "weight_gbs": size / microseconds / 1e3, "frac_of_hbm_peak": size / microseconds / 1e3 / peak}
+
+        extras["matvec_shapes_batch1"] = {
+            "q8_0 4864x896 (config 0; 40 copies rotate, 185 MB)": kernel_rate(synth.Q8_0, 4864, 896, 40),
+            "q8_0 18944x3584": kernel_rate(synth.Q8_0, 18944, 3584, 3),
+            "q4_k 28672x8192 (config 4)": kernel_rate(synth.Q4_K, 28672, 8192, 2),
+            "q4_k 8192x28672 (config 4)": kernel_rate(synth.Q4_K, 8192, 28672, 2),
+            "q4_k 152064x3584 (vocabulary projection)": kernel_rate(synth.Q4_K, 152064, 3584, 1),
+            "q6_k 152064x3584 (vocabulary projection as Q6_K)": kernel_rate(synth.Q6_K, 152064, 3584, 1),
+        }
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = run_cpu_baseline()

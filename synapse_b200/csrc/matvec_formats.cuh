@@ -204,9 +204,17 @@ __device__ __forceinline__ void store_result(const Epilogue &e, float *__restric
     float *destination = y + token * out_stride + row;
     v = e.accumulate ? *destination + v : v;
     *destination = v;
-    for (uint32_t peer = 0; peer < e.peer_count; ++peer) {
-        e.peers[peer][token * out_stride + row] = v;  // plain stores over NVLink into the peer's copy
+    // plain stores over NVLink into the peers' copies; constant indices, so the epilogue stays in the parameter bank
+#ifndef SYN_NO_PEERS
+    if (e.peer_count != 0) {
+#pragma unroll
+        for (int peer = 0; peer < 7; ++peer) {
+            if ((uint32_t)peer < e.peer_count) {
+                e.peers[peer][token * out_stride + row] = v;
+            }
+        }
     }
+#endif
 }
 
 __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
