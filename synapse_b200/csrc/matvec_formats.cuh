@@ -192,6 +192,9 @@ __device__ __forceinline__ void q6k_codes(uint32_t a, uint32_t b, uint32_t h, ui
 }
 
 // Applies the epilogue to one finished dot product and stores it.
+// GATHER: also store the result into the peer copies of the output (row-sharded products). It is a template
+// parameter because even a never-taken peer branch in the epilogue cost the single-GPU kernels 2-4 %.
+template <bool GATHER = false>
 __device__ __forceinline__ void store_result(const Epilogue &e, float *__restrict__ y, uint64_t token, uint64_t out_stride, uint64_t row, float v)
 {
     if (e.bias) {
@@ -205,8 +208,7 @@ __device__ __forceinline__ void store_result(const Epilogue &e, float *__restric
     v = e.accumulate ? *destination + v : v;
     *destination = v;
     // plain stores over NVLink into the peers' copies; constant indices, so the epilogue stays in the parameter bank
-#ifndef SYN_NO_PEERS
-    if (e.peer_count != 0) {
+    if (GATHER) {
 #pragma unroll
         for (int peer = 0; peer < 7; ++peer) {
             if ((uint32_t)peer < e.peer_count) {
@@ -214,7 +216,6 @@ __device__ __forceinline__ void store_result(const Epilogue &e, float *__restric
             }
         }
     }
-#endif
 }
 
 __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }

@@ -172,7 +172,7 @@ matvec_xq8_team_kernel(WeightView w, ActView act, uint64_t K, uint64_t rows, uin
 #pragma unroll
                     for (int t = 0; t < T; ++t) {
                         if (row0 + r < rows && (uint32_t)t < live) {
-                            store_result(epilogue, y, token0 + t, out_stride, row0 + r, acc[r][t]);
+                            store_result<true>(epilogue, y, token0 + t, out_stride, row0 + r, acc[r][t]);
                         }
                     }
                 }
@@ -197,7 +197,7 @@ matvec_xq8_team_kernel(WeightView w, ActView act, uint64_t K, uint64_t rows, uin
                     total += partial[buffer][team_in_cta * W + k][lane];
                 }
                 if (row0 + r < rows && t < live) {
-                    store_result(epilogue, y, token0 + t, out_stride, row0 + r, total);
+                    store_result<true>(epilogue, y, token0 + t, out_stride, row0 + r, total);
                 }
             }
         }
@@ -301,7 +301,7 @@ __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %
 // CW = consumer warps the CTA is built for: 8 (two such CTAs fit one SM, so the next kernel of the stream can start
 // copying while this one runs) or 16 (one CTA per SM: twice the rows in flight, which is what large matrices need to
 // keep up with HBM).
-template <class F, int T, int W, int UPL, int R, bool REGS, bool FUSED, int CW = kWarps>
+template <class F, int T, int W, int UPL, int R, bool REGS, bool FUSED, int CW = kWarps, bool GATHER = false>
 __global__ void __launch_bounds__((CW / W) * W * 32 + 32, CW > kWarps ? 1 : F::min_ctas(W))
 matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uint64_t in_stride, uint64_t K, uint64_t rows, uint32_t tokens,
                        float *__restrict__ y, uint64_t out_stride, Epilogue epilogue, uint32_t *fault)
@@ -492,7 +492,7 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
 #pragma unroll
                     for (int t = 0; t < T; ++t) {
                         if (row0 + r < rows && (uint32_t)t < live) {
-                            store_result(epilogue, y, token0 + t, out_stride, row0 + r, acc[r][t]);
+                            store_result<GATHER>(epilogue, y, token0 + t, out_stride, row0 + r, acc[r][t]);
                         }
                     }
                 }
@@ -517,7 +517,7 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
                     total += partial[buffer][team_in_cta * W + k][lane];
                 }
                 if (row0 + r < rows && t < live) {
-                    store_result(epilogue, y, token0 + t, out_stride, row0 + r, total);
+                    store_result<GATHER>(epilogue, y, token0 + t, out_stride, row0 + r, total);
                 }
             }
         }
@@ -551,11 +551,11 @@ bool plan_pipe(const MatvecArgs &a, const WeightView &view, uint32_t act_bytes, 
     return true;
 }
 
-template <class F, int T, int W, int UPL, int R, bool REGS, bool FUSED, int CW = kWarps>
+template <class F, int T, int W, int UPL, int R, bool REGS, bool FUSED, int CW = kWarps, bool GATHER = false>
 cudaError_t launch_pipe(const MatvecArgs &a, const PipeArgs &p, cudaStream_t stream)
 {
     constexpr uint64_t G = (uint64_t)(CW / W) * R;
-    auto kernel = matvec_xq8_pipe_kernel<F, T, W, UPL, R, REGS, FUSED, CW>;
+    auto kernel = matvec_xq8_pipe_kernel<F, T, W, UPL, R, REGS, FUSED, CW, GATHER>;
     const uint32_t dynamic = p.act_bytes + p.stages * p.stage_bytes;
     static bool configured = false;
     if (!configured) {
@@ -587,7 +587,13 @@ cudaError_t launch_tokens(const MatvecArgs &a, const WeightView &view, bool one_
     }
     PipeArgs pipe;
     const uint32_t K32 = (uint32_t)a.matrix->columns;
-    if (a.tokens <= 2 && !a.act_ready && plan_pipe<F, W, R>(a, view, shared_act_bytes((uint32_t)a.tokens, K32), pipe)) {
+    // Products that also store into peer copies of the output: one pipelined variant (single token, one pass, ready
+    // activations); every other shape takes the direct-load kernel below, whose epilogue handles peers at run time.
+    const bool gather = a.fused.peer_count != 0;
+    if (gather && a.tokens <= 1 && one_pass && a.act_ready && plan_pipe<F, W, R>(a, view, 0, pipe)) {
+        return launch_pipe<F, 1, W, UPL, R, true, false, kWarps, true>(a, pipe, stream);
+    }
+    if (!gather && a.tokens <= 2 && !a.act_ready && plan_pipe<F, W, R>(a, view, shared_act_bytes((uint32_t)a.tokens, K32), pipe)) {
         // FP32 activations in: the kernel quantises them itself.
         if (a.tokens <= 1) {
             return one_pass ? launch_pipe<F, 1, W, UPL, R, true, true>(a, pipe, stream) : launch_pipe<F, 1, W, UPL, R, false, true>(a, pipe, stream);
@@ -606,10 +612,10 @@ cudaError_t launch_tokens(const MatvecArgs &a, const WeightView &view, bool one_
     // it depends on W and UPL only). Measured on Q4_K: 306 MB in 47.2 against 52.7 us, 153 MB in 25.4 against 30.7 us.
     // A 38 MB projection gains 4 % alone but loses more inside a decode step, where the eight-warp CTAs of two
     // kernels share an SM (parallel branches, and the next kernel's first copies).
-    if (a.tokens <= 1 && one_pass && a.row_count * a.matrix->row_bytes >= kWideBytes && plan_pipe<F, W, 1, 2 * kWarps>(a, view, 0, pipe)) {
+    if (!gather && a.tokens <= 1 && one_pass && a.row_count * a.matrix->row_bytes >= kWideBytes && plan_pipe<F, W, 1, 2 * kWarps>(a, view, 0, pipe)) {
         return launch_pipe<F, 1, W, UPL, 1, true, false, 2 * kWarps>(a, pipe, stream);
     }
-    if (a.tokens <= 2 && plan_pipe<F, W, R>(a, view, 0, pipe)) {
+    if (!gather && a.tokens <= 2 && plan_pipe<F, W, R>(a, view, 0, pipe)) {
         if (a.tokens <= 1) {
             return one_pass ? launch_pipe<F, 1, W, UPL, R, true, false>(a, pipe, stream) : launch_pipe<F, 1, W, UPL, R, false, false>(a, pipe, stream);
         }
