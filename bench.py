@@ -44,10 +44,10 @@ def parse_args():
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--layers", type=int, default=28, help="layers of the model shape (28 = the full config)")
     parser.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
-    parser.add_argument("--quantize", default="shared", choices=["shared", "fused", "mixed"],
-                        help="shared: one quantiser launch per distinct layer input, reused by the projections that read it; "
-                             "fused: every product quantises its FP32 input inside the kernel; mixed: shared where several "
-                             "products read one vector (q|k|v, gate|up), inside the kernel where one does (o, down)")
+    parser.add_argument("--quantize", default="shared", choices=["shared", "fused"],
+                        help="shared: one quantiser launch per distinct layer input, reused by the projections that read it "
+                             "(1.30 ms per step); fused: every product quantises its FP32 input inside the kernel (1.52 ms; "
+                             "fusing only the products that read a vector alone, o and down: 1.46 ms)")
     parser.add_argument("--serial", action="store_true", help="run q/k/v and gate/up one after the other instead of on parallel graph branches")
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--gather", default="peer", choices=["peer", "nccl"],
@@ -287,7 +287,7 @@ def main():
 
     side = [torch.cuda.Stream(device), torch.cuda.Stream(device)]
 
-    def product(entry, stream, fused=False):
+    def product(entry, stream):
         name, ggml_type, rows, columns, shard_rows, matrix = entry
         if peers is not None:
             first_row, _ = sharding.shard_rows(rows, world, rank)
@@ -295,7 +295,7 @@ def main():
             matrix.matmul_q8_gather_device(aligned(scratch[columns]), 1, own, shard_rows, others, stream=stream.cuda_stream)
             return
         target = out_shard[(name.split(".")[-1], shard_rows)] if world > 1 else out_full[(name.split(".")[-1], rows)]
-        if args.quantize == "fused" or fused:
+        if args.quantize == "fused":
             matrix.matvec_device(x_dev[columns].data_ptr(), 1, columns, target.data_ptr(), shard_rows, sb.MODE_XQ8,
                                  scratch_ptr=aligned(scratch[columns]), scratch_bytes=lib.activation_scratch_bytes(1, columns),
                                  stream=stream.cuda_stream)
@@ -305,9 +305,8 @@ def main():
             with torch.cuda.stream(stream):
                 sharding.gather_outputs(target, out_full[(name.split(".")[-1], rows)])
 
-    def quantize(columns, stream, alone=False):
-        """`alone`: the vector feeds a single product (o, down): with --quantize mixed that product quantises it itself."""
-        if args.quantize == "shared" or (args.quantize == "mixed" and (not alone or peers is not None)):
+    def quantize(columns, stream):
+        if args.quantize == "shared":
             sb.quantize_device(x_dev[columns].data_ptr(), 1, columns, columns, aligned(scratch[columns]),
                                lib.activation_scratch_bytes(1, columns), stream.cuda_stream)
 
@@ -315,8 +314,7 @@ def main():
         """Independent products of the same input: the first on the main stream, the others on side streams."""
         if args.serial or (world > 1 and peers is None) or len(entries) == 1:
             for entry in entries:
-                product(entry, main, fused=args.quantize == "mixed" and len(entries) == 1 and peers is None and
-                        not entry[0].endswith("lm_head"))
+                product(entry, main)
             return
         fork = torch.cuda.Event()
         fork.record(main)
@@ -338,11 +336,11 @@ def main():
             get = lambda leaf: by_name[f"blk.{layer}.{leaf}"]
             quantize(3584, main)
             parallel([get("attn_q"), get("attn_k"), get("attn_v")], main)
-            quantize(3584, main, alone=True)
+            quantize(3584, main)
             parallel([get("attn_o")], main)
             quantize(3584, main)
             parallel([get("ffn_gate"), get("ffn_up")], main)
-            quantize(18944, main, alone=True)
+            quantize(18944, main)
             parallel([get("ffn_down")], main)
         quantize(3584, main)
         parallel([by_name["lm_head"]], main)
