@@ -252,6 +252,7 @@ struct Q8PlanarXq8 {
     struct Act { uint4 c; float d; };
     struct W { uint4 c; float d; };
     static constexpr int kPlanes = 2;
+    static constexpr bool kStageTokens = false;  // several tokens: 16-weight units make the staged kernel load-bound; the direct kernels are faster
     static void plane_row_bytes(uint64_t K, uint64_t, uint32_t *out) { out[0] = (uint32_t)K; out[1] = (uint32_t)(K / 16); }
     static constexpr int kMaxUpl = 2, kRows = 2, kCtasPerSm = SYN_DEFAULT_CTAS;
     static constexpr int min_ctas(int) { return 2; }
@@ -295,6 +296,7 @@ struct Q8NaturalXq8 {
     struct Act { uint4 c0, c1; float d; };
     struct W { uint4 c0, c1; float d; };
     static constexpr int kPlanes = 1;
+    static constexpr bool kStageTokens = false;  // as the planar layout
     static constexpr int kMaxUpl = 2, kRows = 2, kCtasPerSm = SYN_DEFAULT_CTAS;
     static constexpr int min_ctas(int) { return 2; }
     static constexpr int ctas_per_sm(int) { return kCtasPerSm; }
@@ -372,6 +374,7 @@ struct Q4KXq8 {
     };
     struct W { uint4 hdr, q[4]; };
     static constexpr int kPlanes = 1;
+    static constexpr bool kStageTokens = true;  // several tokens: their activations are staged in shared memory beside the weight ring
 #ifndef SYN_Q4K_ROWS
 #define SYN_Q4K_ROWS 2
 #endif
@@ -545,6 +548,7 @@ struct Q6KPlanarXq8 {
     using Act = Q6KAct;
     using W = Q6KW;
     static constexpr int kPlanes = 4;
+    static constexpr bool kStageTokens = true;  // as Q4_K
     static constexpr int kMaxUpl = 2, kRows = 2;
     // Single-warp teams (short rows): uncapped registers, one CTA per SM. Wider teams: two CTAs per SM.
     static constexpr int min_ctas(int W) { return W == 1 ? 1 : 2; }
@@ -590,6 +594,7 @@ struct Q6KNaturalXq8 {
     using Act = Q6KAct;
     using W = Q6KW;
     static constexpr int kPlanes = 1;
+    static constexpr bool kStageTokens = true;  // as Q4_K
     static constexpr int kMaxUpl = 2, kRows = 2, kCtasPerSm = SYN_DEFAULT_CTAS;
     static constexpr int min_ctas(int) { return 2; }
     static constexpr int ctas_per_sm(int) { return kCtasPerSm; }

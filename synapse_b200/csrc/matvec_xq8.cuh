@@ -298,11 +298,43 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_
 template <int THREADS>
 __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory"); }
 
+// Launches with several tokens keep all tokens' quantised activations in shared memory and sixteen accumulators per
+// lane: they get an SM to themselves (no register cap, twice the shared memory).
+__host__ __device__ constexpr bool roomy(int T, int CW, bool staged) { return (T > 1 && staged) || CW > kWarps; }
+__host__ __device__ constexpr uint32_t stage_budget(int T, bool staged) { return T > 1 && staged ? 200u * 1024u : kStageBudget; }
+
+// Copies the already quantised activations of `live` tokens (global scratch layout) into the shared layout the
+// kernels read: codes piece-swizzled, scales and code sums as they are. Token slots past `live` repeat the last token.
+template <int T>
+__device__ __forceinline__ void stage_activations(const ActView &act, uint64_t token0, uint32_t K, uint32_t live, uint32_t thread,
+                                                  uint32_t threads, const ActShared &dst)
+{
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+        const uint64_t token = token0 + min((uint32_t)t, live - 1);
+        const uint4 *codes = reinterpret_cast<const uint4 *>(act.codes + token * K);
+        for (uint32_t piece = thread; piece < K / 16; piece += threads) {
+            const uint4 v = __ldg(codes + piece);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst.codes + swizzled_code_offset((uint32_t)t * K + piece * 16)),
+                         "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                         : "memory");
+        }
+        const float *scales = act.scales + token * (K / 32);
+        for (uint32_t i = thread; i < K / 32; i += threads) {
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst.scales + ((uint32_t)t * (K / 32) + i) * 4), "f"(__ldg(scales + i)) : "memory");
+        }
+        const int16_t *sums = act.sums + token * (K / 16);
+        for (uint32_t i = thread; i < K / 16; i += threads) {
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst.sums + ((uint32_t)t * (K / 16) + i) * 2), "h"(__ldg(sums + i)) : "memory");
+        }
+    }
+}
+
 // CW = consumer warps the CTA is built for: 8 (two such CTAs fit one SM, so the next kernel of the stream can start
 // copying while this one runs) or 16 (one CTA per SM: twice the rows in flight, which is what large matrices need to
 // keep up with HBM).
 template <class F, int T, int W, int UPL, int R, bool REGS, bool FUSED, int CW = kWarps, bool GATHER = false>
-__global__ void __launch_bounds__((CW / W) * W * 32 + 32, CW > kWarps ? 1 : F::min_ctas(W))
+__global__ void __launch_bounds__((CW / W) * W * 32 + 32, roomy(T, CW, FUSED) ? 1 : F::min_ctas(W))
 matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uint64_t in_stride, uint64_t K, uint64_t rows, uint32_t tokens,
                        float *__restrict__ y, uint64_t out_stride, Epilogue epilogue, uint32_t *fault)
 {
@@ -384,7 +416,12 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
         shared_act.codes = base;
         shared_act.scales = base + shared_act_codes_bytes(T, (uint32_t)K);
         shared_act.sums = shared_act.scales + shared_act_side_bytes(T, (uint32_t)K);
-        quantize_to_shared<T>(x + token0 * in_stride, in_stride, (uint32_t)K, live, warp_in_cta, kConsumers, lane, shared_act);
+        if (x) {
+            quantize_to_shared<T>(x + token0 * in_stride, in_stride, (uint32_t)K, live, warp_in_cta, kConsumers, lane, shared_act);
+        } else {
+            // the caller quantised already: bring the tokens of this CTA's group into shared memory
+            stage_activations<T>(act, token0, (uint32_t)K, live, threadIdx.x, kConsumers * 32, shared_act);
+        }
         consumer_barrier<kConsumers * 32>();
     }
     typename F::Act held[REGS ? UPL : 1];
@@ -526,7 +563,7 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
 
 // Lays out a stage for this format and row length; false when a group of rows does not fit the stage budget.
 template <class F, int W, int R, int CW = kWarps>
-bool plan_pipe(const MatvecArgs &a, const WeightView &view, uint32_t act_bytes, PipeArgs &p)
+bool plan_pipe(const MatvecArgs &a, const WeightView &view, uint32_t act_bytes, PipeArgs &p, uint32_t budget = kStageBudget)
 {
     constexpr uint64_t G = (uint64_t)(CW / W) * R;
     p.global = view;
@@ -541,12 +578,12 @@ bool plan_pipe(const MatvecArgs &a, const WeightView &view, uint32_t act_bytes, 
         p.plane_offset[k] = 0;
         p.plane_row_bytes[k] = 0;
     }
-    if (act_bytes >= kStageBudget || offset > (kStageBudget - act_bytes) / 2) {
+    if (act_bytes >= budget || offset > (budget - act_bytes) / 2) {
         return false;
     }
     p.act_bytes = act_bytes;
     p.stage_bytes = (uint32_t)offset;
-    uint64_t stages = (kStageBudget - act_bytes) / offset;
+    uint64_t stages = (budget - act_bytes) / offset;
     p.stages = (uint32_t)(stages > kMaxStages ? kMaxStages : stages);
     return true;
 }
@@ -559,7 +596,7 @@ cudaError_t launch_pipe(const MatvecArgs &a, const PipeArgs &p, cudaStream_t str
     const uint32_t dynamic = p.act_bytes + p.stages * p.stage_bytes;
     static bool configured = false;
     if (!configured) {
-        cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStageBudget);
+        cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stage_budget(T, FUSED));
         if (error != cudaSuccess) {
             return error;
         }
@@ -569,7 +606,7 @@ cudaError_t launch_pipe(const MatvecArgs &a, const PipeArgs &p, cudaStream_t str
     // shared memory): the second slot is for the next kernel of the stream, which starts copying its first stages
     // while this one is still running.
     uint64_t ctas = (a.row_count + G - 1) / G;
-    const uint64_t cap = (uint64_t)sm_count(a.matrix->device) * (CW > kWarps ? 1 : F::ctas_per_sm(W));
+    const uint64_t cap = (uint64_t)sm_count(a.matrix->device) * (roomy(T, CW, FUSED) ? 1 : F::ctas_per_sm(W));
     if (ctas > cap) {
         ctas = cap;
     }
@@ -593,12 +630,28 @@ cudaError_t launch_tokens(const MatvecArgs &a, const WeightView &view, bool one_
     if (gather && a.tokens <= 1 && one_pass && a.act_ready && plan_pipe<F, W, R>(a, view, 0, pipe)) {
         return launch_pipe<F, 1, W, UPL, R, true, false, kWarps, true>(a, pipe, stream);
     }
-    if (!gather && a.tokens <= 2 && !a.act_ready && plan_pipe<F, W, R>(a, view, shared_act_bytes((uint32_t)a.tokens, K32), pipe)) {
+    if (!gather && a.tokens <= 1 && !a.act_ready && plan_pipe<F, W, R>(a, view, shared_act_bytes(1, K32), pipe)) {
         // FP32 activations in: the kernel quantises them itself.
-        if (a.tokens <= 1) {
-            return one_pass ? launch_pipe<F, 1, W, UPL, R, true, true>(a, pipe, stream) : launch_pipe<F, 1, W, UPL, R, false, true>(a, pipe, stream);
+        return one_pass ? launch_pipe<F, 1, W, UPL, R, true, true>(a, pipe, stream) : launch_pipe<F, 1, W, UPL, R, false, true>(a, pipe, stream);
+    }
+    if constexpr (F::kStageTokens) if (!gather && a.tokens >= 2) {
+        // Several tokens: groups of 8, 4 or 2 tokens (the largest that is needed and whose quantised activations fit
+        // beside the weight ring) share every weight stage; a group's activations sit in shared memory, quantised there
+        // from FP32 or copied from the caller's scratch. Further groups take further grid rows.
+        MatvecArgs grouped = a;
+        if (a.act_ready) {
+            grouped.x = nullptr;  // tells the kernel to copy instead of quantising
         }
-        return launch_pipe<F, 2, W, UPL, R, false, true>(a, pipe, stream);
+        const uint32_t budget = stage_budget(2, true);
+        if (a.tokens > 4 && plan_pipe<F, W, R>(a, view, shared_act_bytes(8, K32), pipe, budget)) {
+            return launch_pipe<F, 8, W, UPL, R, false, true>(grouped, pipe, stream);
+        }
+        if (a.tokens > 2 && plan_pipe<F, W, R>(a, view, shared_act_bytes(4, K32), pipe, budget)) {
+            return launch_pipe<F, 4, W, UPL, R, false, true>(grouped, pipe, stream);
+        }
+        if (plan_pipe<F, W, R>(a, view, shared_act_bytes(2, K32), pipe, budget)) {
+            return launch_pipe<F, 2, W, UPL, R, false, true>(grouped, pipe, stream);
+        }
     }
     if (!a.act_ready) {
         // Shapes the pipelined kernel does not take: quantise into the caller's scratch first.
@@ -615,11 +668,11 @@ cudaError_t launch_tokens(const MatvecArgs &a, const WeightView &view, bool one_
     if (!gather && a.tokens <= 1 && one_pass && a.row_count * a.matrix->row_bytes >= kWideBytes && plan_pipe<F, W, 1, 2 * kWarps>(a, view, 0, pipe)) {
         return launch_pipe<F, 1, W, UPL, 1, true, false, 2 * kWarps>(a, pipe, stream);
     }
-    if (!gather && a.tokens <= 2 && plan_pipe<F, W, R>(a, view, 0, pipe)) {
-        if (a.tokens <= 1) {
-            return one_pass ? launch_pipe<F, 1, W, UPL, R, true, false>(a, pipe, stream) : launch_pipe<F, 1, W, UPL, R, false, false>(a, pipe, stream);
-        }
-        return launch_pipe<F, 2, W, UPL, R, false, false>(a, pipe, stream);
+    if (!gather && a.tokens <= 1 && plan_pipe<F, W, R>(a, view, 0, pipe)) {
+        return one_pass ? launch_pipe<F, 1, W, UPL, R, true, false>(a, pipe, stream) : launch_pipe<F, 1, W, UPL, R, false, false>(a, pipe, stream);
+    }
+    if constexpr (!F::kStageTokens) if (!gather && a.tokens == 2 && plan_pipe<F, W, R>(a, view, 0, pipe)) {
+        return launch_pipe<F, 2, W, UPL, R, false, false>(a, pipe, stream);  // activations read from the scratch as they are
     }
     // Token group size: the smallest of 1, 2, 4, 8 that holds the tokens (step/projection.rs:82-87).
     if (a.tokens <= 1) {
