@@ -71,6 +71,9 @@ constexpr int kConsumerWarps = 15;  // with the producer warp 512 threads: up to
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
 constexpr uint32_t kRingStagesMax = 16;
+// Warps that share one head's attention: warp w walks positions w, w + kAttentionWarps, ...; the partial results are
+// merged in warp order. Both forms of the step use the same split, so their results agree bit for bit.
+constexpr int kAttentionWarps = 12;
 constexpr uint32_t kStashIterations = 48;  // row groups per CTA of a gate projection whose results stay in shared memory
 constexpr int kNormDepth = 5, kPlainDepth = 10;  // 128-value pieces per warp held in registers while quantising
 constexpr uint32_t kNormQuadsMax = kNormDepth * 15;
@@ -173,7 +176,7 @@ struct Shared {
     double square_sums[8];
     float norm_scale;
     int abort;  // set once a wait gave up: nobody waits any more
-    float merged[4][256 + 2];
+    float merged[kAttentionWarps][256 + 2];
     float query[256], key[256], value[256];
     float best_value[kConsumerWarps];
     int best_index[kConsumerWarps];
@@ -586,9 +589,80 @@ __device__ __noinline__ void quantize_local(const Op *op, Shared &sh, uint32_t a
     consumer_sync();
 }
 
+// One warp's share of a head's attention: positions first, first + kAttentionWarps, ... up to `position`, online softmax in that
+// order (Qwen2CpuAttention.cs:82-173). BATCH positions are loaded at a time so that their latencies overlap (a warp far
+// into the context otherwise spends a load latency per position); the arithmetic and its order are exactly those of a
+// position-at-a-time loop, whatever BATCH is. `current_key/value` (may be null) replace the cache entry of `position`.
+template <int PER, int BATCH>
+__device__ __forceinline__ void attend_positions(const float *qv, uint32_t per_lane, uint32_t lane, int first, int position, uint32_t head_dim,
+                                                 float scale, const float *keys, const float *values, const float *current_key,
+                                                 const float *current_value, float *acc, float &running_max, float &running_sum)
+{
+    for (int p0 = first; p0 <= position; p0 += kAttentionWarps * BATCH) {
+        float k[BATCH][PER], v[BATCH][PER];
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) {
+            const int p = p0 + kAttentionWarps * b;
+            const bool live = p <= position;
+            const bool current = current_key && p == position;
+            const float *key = current ? current_key : keys + (uint64_t)(live ? p : position) * head_dim;
+            const float *value = current ? current_value : values + (uint64_t)(live ? p : position) * head_dim;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) {
+                k[b][j] = (uint32_t)j < per_lane ? key[lane + 32 * j] : 0.0f;
+                v[b][j] = (uint32_t)j < per_lane ? value[lane + 32 * j] : 0.0f;
+            }
+        }
+        float dots[BATCH];
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) {
+            float dot = 0.0f;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) {
+                if ((uint32_t)j < per_lane) {
+                    dot = fmaf(qv[j], k[b][j], dot);
+                }
+            }
+            for (int offset = 16; offset > 0; offset >>= 1) {
+                dot += __shfl_xor_sync(kFull, dot, offset);
+            }
+            dots[b] = dot;
+        }
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) {
+            if (p0 + kAttentionWarps * b <= position) {
+                const float score = dots[b] * scale;
+                const float next_max = fmaxf(running_max, score);
+                const float rescale = expf(running_max - next_max), weight = expf(score - next_max);
+#pragma unroll
+                for (int j = 0; j < PER; ++j) {
+                    if ((uint32_t)j < per_lane) {
+                        acc[j] = fmaf(weight, v[b][j], acc[j] * rescale);
+                    }
+                }
+                running_sum = running_sum * rescale + weight;
+                running_max = next_max;
+            }
+        }
+    }
+}
+// Heads of up to 128 values take four positions at a time, larger heads two (the loaded keys and values live in registers).
+__device__ __forceinline__ void attend_head(const float *qv, uint32_t per_lane, uint32_t lane, int first, int position, uint32_t head_dim,
+                                            float scale, const float *keys, const float *values, const float *current_key,
+                                            const float *current_value, float *acc, float &running_max, float &running_sum)
+{
+    if (per_lane <= 4) {
+        attend_positions<4, 4>(qv, per_lane, lane, first, position, head_dim, scale, keys, values, current_key, current_value, acc, running_max,
+                               running_sum);
+    } else {
+        attend_positions<8, 2>(qv, per_lane, lane, first, position, head_dim, scale, keys, values, current_key, current_value, acc, running_max,
+                               running_sum);
+    }
+}
+
 // One query head of the token: NeoX rotation of the head's query and of its key head (Qwen2CpuState.cs:85-105),
 // append of key and value to the slot's cache (by the first query head of each key head), softmax attention over
-// positions 0..position (Qwen2CpuAttention.cs:82-173) with the four-warp split of attention_kernel.
+// positions 0..position (Qwen2CpuAttention.cs:82-173) with the warp split of attention_kernel.
 __device__ __noinline__ void attention_local(const Op *op, const Params &P, Shared &sh)
 {
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -623,7 +697,7 @@ __device__ __noinline__ void attention_local(const Op *op, const Params &P, Shar
         }
     }
     consumer_sync();
-    if (warp < 4) {
+    if (warp < (uint32_t)kAttentionWarps) {
         constexpr int kPerLane = 8;
         const uint32_t per_lane = head_dim / 32;
         float qv[kPerLane], acc[kPerLane];
@@ -633,32 +707,8 @@ __device__ __noinline__ void attention_local(const Op *op, const Params &P, Shar
             acc[j] = 0.0f;
         }
         float running_max = -INFINITY, running_sum = 0.0f;
-        for (int p = (int)warp; p <= token.position; p += 4) {
-            const bool current = p == token.position;
-            const float *key = current ? sh.key : P.keys + base + (uint64_t)p * head_dim;
-            float dot = 0.0f;
-#pragma unroll
-            for (int j = 0; j < kPerLane; ++j) {
-                if ((uint32_t)j < per_lane) {
-                    dot = fmaf(qv[j], key[lane + 32 * j], dot);
-                }
-            }
-            for (int offset = 16; offset > 0; offset >>= 1) {
-                dot += __shfl_xor_sync(kFull, dot, offset);
-            }
-            const float score = dot * P.attention_scale;
-            const float next_max = fmaxf(running_max, score);
-            const float rescale = expf(running_max - next_max), weight = expf(score - next_max);
-            const float *value = current ? sh.value : P.values + base + (uint64_t)p * head_dim;
-#pragma unroll
-            for (int j = 0; j < kPerLane; ++j) {
-                if ((uint32_t)j < per_lane) {
-                    acc[j] = fmaf(weight, value[lane + 32 * j], acc[j] * rescale);
-                }
-            }
-            running_sum = running_sum * rescale + weight;
-            running_max = next_max;
-        }
+        attend_head(qv, per_lane, lane, (int)warp, token.position, head_dim, P.attention_scale, P.keys + base, P.values + base, sh.key, sh.value,
+                    acc, running_max, running_sum);
 #pragma unroll
         for (int j = 0; j < kPerLane; ++j) {
             if ((uint32_t)j < per_lane) {
@@ -673,15 +723,15 @@ __device__ __noinline__ void attention_local(const Op *op, const Params &P, Shar
     consumer_sync();
     if (threadIdx.x < head_dim) {
         float total_max = -INFINITY;
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < kAttentionWarps; ++w) {
             total_max = fmaxf(total_max, sh.merged[w][256]);
         }
         float total_sum = 0.0f;
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < kAttentionWarps; ++w) {
             total_sum += sh.merged[w][257] * expf(sh.merged[w][256] - total_max);
         }
         float value = 0.0f;
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < kAttentionWarps; ++w) {
             value += sh.merged[w][threadIdx.x] * expf(sh.merged[w][256] - total_max);
         }
         P.attention[(uint64_t)head * head_dim + threadIdx.x] = value / total_sum;

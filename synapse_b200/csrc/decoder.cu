@@ -130,15 +130,15 @@ __global__ void rope_store_kernel(const BatchToken *__restrict__ tokens, float *
 }
 
 // Softmax attention of one token's query head over positions 0..position of its slot (Qwen2CpuAttention.cs:82-173).
-// Grid (heads, tokens), four warps; each warp walks every fourth position with an online softmax, the four partial
+// Grid (heads, tokens), kAttentionWarps warps; each warp walks every kAttentionWarps-th position with an online softmax, the partial
 // results are merged in shared memory. Head dimensions up to 256.
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(32 * prog::kAttentionWarps)
 attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict__ q, const float *__restrict__ keys,
                  const float *__restrict__ values, uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t layer, uint32_t layers,
                  uint32_t context, float scale, int8_t *__restrict__ codes, float *__restrict__ scales, int16_t *__restrict__ sums)
 {
     constexpr int kPerLane = 8;  // head_dim / 32, at most
-    __shared__ float merged[4][256 + 2];
+    __shared__ float merged[prog::kAttentionWarps][256 + 2];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t t = blockIdx.y, head = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -153,31 +153,8 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
         acc[j] = 0.0f;
     }
     float running_max = -INFINITY, running_sum = 0.0f;
-    for (int p = (int)warp; p <= token.position; p += 4) {
-        const float *key = keys + base + (uint64_t)p * head_dim;
-        float dot = 0.0f;
-#pragma unroll
-        for (int j = 0; j < kPerLane; ++j) {
-            if ((uint32_t)j < per_lane) {
-                dot = fmaf(qv[j], key[lane + 32 * j], dot);
-            }
-        }
-        for (int offset = 16; offset > 0; offset >>= 1) {
-            dot += __shfl_xor_sync(0xffffffffu, dot, offset);
-        }
-        const float score = dot * scale;
-        const float next_max = fmaxf(running_max, score);
-        const float rescale = expf(running_max - next_max), weight = expf(score - next_max);
-        const float *value = values + base + (uint64_t)p * head_dim;
-#pragma unroll
-        for (int j = 0; j < kPerLane; ++j) {
-            if ((uint32_t)j < per_lane) {
-                acc[j] = fmaf(weight, value[lane + 32 * j], acc[j] * rescale);
-            }
-        }
-        running_sum = running_sum * rescale + weight;
-        running_max = next_max;
-    }
+    prog::attend_head(qv, per_lane, lane, (int)warp, token.position, head_dim, scale, keys + base, values + base, nullptr, nullptr, acc,
+                      running_max, running_sum);
 #pragma unroll
     for (int j = 0; j < kPerLane; ++j) {
         if ((uint32_t)j < per_lane) {
@@ -190,20 +167,20 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
     }
     __syncthreads();
     float total_max = -INFINITY;
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < prog::kAttentionWarps; ++w) {
         total_max = fmaxf(total_max, merged[w][256]);
     }
     float total_sum = 0.0f;
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < prog::kAttentionWarps; ++w) {
         total_sum += merged[w][257] * expf(merged[w][256] - total_max);  // an idle warp has sum 0 and max -inf: exp(-inf) = 0
     }
     // The head's output is head_dim/32 whole Q8_0 blocks of the attention row: quantise them here (one warp per
     // block, same arithmetic as the activation quantiser) instead of storing FP32 and launching the quantiser.
     const uint32_t hidden = heads * head_dim;
-    for (uint32_t block = warp; block < head_dim / 32; block += 4) {
+    for (uint32_t block = warp; block < head_dim / 32; block += prog::kAttentionWarps) {
         const uint32_t i = block * 32 + lane;
         float value = 0.0f;
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < prog::kAttentionWarps; ++w) {
             value += merged[w][i] * expf(merged[w][256] - total_max);
         }
         value = value / total_sum;
@@ -438,7 +415,7 @@ cudaError_t enqueue_step(syn_b200_decoder *d, uint32_t count, uint32_t logits_ro
             // the attention output replaces the normalised activations of this layer in the same scratch
             const ActLayout layout = act_layout(count, hidden);
             uint8_t *base = static_cast<uint8_t *>(d->act_hidden);
-            SYN_TRY(launch_kernel(attention_kernel, dim3(s.heads, count), dim3(128), 0, d->stream, (const BatchToken *)d->device_tokens,
+            SYN_TRY(launch_kernel(attention_kernel, dim3(s.heads, count), dim3(32 * prog::kAttentionWarps), 0, d->stream, (const BatchToken *)d->device_tokens,
                                   (const float *)d->q, (const float *)d->keys, (const float *)d->values, s.heads, s.kv_heads, s.head_dim, l,
                                   s.layer_count, s.context, 1.0f / sqrtf((float)s.head_dim), reinterpret_cast<int8_t *>(base + layout.codes),
                                   reinterpret_cast<float *>(base + layout.scales), reinterpret_cast<int16_t *>(base + layout.sums)));
