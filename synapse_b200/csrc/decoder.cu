@@ -10,6 +10,7 @@
 // them: it is captured once per token count into a CUDA graph and replayed.
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <vector>
 
 #include "common.cuh"
@@ -273,6 +274,7 @@ struct syn_b200_decoder {
     float *keys = nullptr, *values = nullptr;
     syn::BatchToken *device_tokens = nullptr, *host_tokens = nullptr;
     int32_t *device_argmax = nullptr, *host_argmax = nullptr;
+    float *host_logits = nullptr;  // pinned staging for the logits: a copy into pageable caller memory is slower than this plus a memcpy
     cudaGraphExec_t graphs[kMaxStepTokens + 1] = {};
     uint64_t launches_per_step[kMaxStepTokens + 1] = {};
     uint32_t steps_seen[kMaxStepTokens + 1] = {};  // the first step of a token count runs uncaptured (one-time kernel set-up)
@@ -1002,6 +1004,9 @@ int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_deco
         if (error == cudaSuccess) error = cudaMemset(d->values, 0, cache * 4);
         if (error == cudaSuccess) error = cudaHostAlloc(reinterpret_cast<void **>(&d->host_tokens), T * sizeof(syn::BatchToken), cudaHostAllocDefault);
         if (error == cudaSuccess) error = cudaHostAlloc(reinterpret_cast<void **>(&d->host_argmax), T * sizeof(int32_t), cudaHostAllocDefault);
+        if (error == cudaSuccess) {
+            error = cudaHostAlloc(reinterpret_cast<void **>(&d->host_logits), (uint64_t)s.logits_rows * s.vocabulary * sizeof(float), cudaHostAllocDefault);
+        }
         if (error == cudaSuccess) error = cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking);
         for (int i = 0; i < 2; ++i) {
             if (error == cudaSuccess) error = cudaStreamCreateWithFlags(&d->side[i], cudaStreamNonBlocking);
@@ -1049,6 +1054,7 @@ void syn_b200_decoder_destroy(syn_b200_decoder *d)
     }
     if (d->host_tokens) cudaFreeHost(d->host_tokens);
     if (d->host_argmax) cudaFreeHost(d->host_argmax);
+    if (d->host_logits) cudaFreeHost(d->host_logits);
     for (int i = 0; i < 2; ++i) {
         if (d->side[i]) cudaStreamDestroy(d->side[i]);
         if (d->join[i]) cudaEventDestroy(d->join[i]);
@@ -1076,7 +1082,7 @@ int32_t syn_b200_decoder_forward(syn_b200_decoder *d, const syn_b200_batch_token
         }
         cudaError_t error = cudaSuccess;
         if (rows > 0) {
-            error = cudaMemcpyAsync(logits, d->logits, (uint64_t)rows * d->shape.vocabulary * 4, cudaMemcpyDeviceToHost, d->stream);
+            error = cudaMemcpyAsync(d->host_logits, d->logits, (uint64_t)rows * d->shape.vocabulary * 4, cudaMemcpyDeviceToHost, d->stream);
         }
         if (error == cudaSuccess) {
             error = cudaStreamSynchronize(d->stream);
@@ -1085,6 +1091,7 @@ int32_t syn_b200_decoder_forward(syn_b200_decoder *d, const syn_b200_batch_token
             cudaGetLastError();
             return cuda_fail(error, "reading the logits");
         }
+        memcpy(logits, d->host_logits, (uint64_t)rows * d->shape.vocabulary * 4);
         return SYN_B200_OK;
     } catch (...) {
         return fail(SYN_B200_INTERNAL, "exception at the ABI");

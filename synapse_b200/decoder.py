@@ -173,7 +173,7 @@ class Decoder:
     def forward(self, tokens) -> np.ndarray:
         """``tokens``: (slot, token, position, logits_row) tuples. Returns [logits rows, vocabulary] FP32."""
         rows = sum(1 for t in tokens if t[3] >= 0)
-        logits = np.zeros((max(rows, 1), self.vocabulary), np.float32)
+        logits = np.empty((max(rows, 1), self.vocabulary), np.float32)
         self._lib.check(self._lib.raw.syn_b200_decoder_forward(self._handle, self._batch(tokens), len(tokens), logits.ctypes.data, logits.size))
         return logits[:rows]
 
