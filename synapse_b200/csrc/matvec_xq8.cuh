@@ -240,6 +240,9 @@ cudaError_t launch_team(const MatvecArgs &a, const WeightView &view, uint64_t du
 // kernel bumps the host-mapped fault word, stops waiting and still runs to completion (with wrong results).
 // ------------------------------------------------------------------------------------------------------
 
+#ifndef SYN_MV_GROUP_WARPS
+#define SYN_MV_GROUP_WARPS 12
+#endif
 constexpr int kMaxStages = 8;
 constexpr uint64_t kWideBytes = 96ull << 20;  // matrices from this size on get the sixteen-warp CTA
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -643,14 +646,15 @@ cudaError_t launch_tokens(const MatvecArgs &a, const WeightView &view, bool one_
             grouped.x = nullptr;  // tells the kernel to copy instead of quantising
         }
         const uint32_t budget = stage_budget(2, true);
-        if (a.tokens > 4 && plan_pipe<F, W, R>(a, view, shared_act_bytes(8, K32), pipe, budget)) {
-            return launch_pipe<F, 8, W, UPL, R, false, true>(grouped, pipe, stream);
+        constexpr int kGroupWarps = SYN_MV_GROUP_WARPS;  // consumer warps of these CTAs (they have the SM to themselves)
+        if (a.tokens > 4 && plan_pipe<F, W, R, kGroupWarps>(a, view, shared_act_bytes(8, K32), pipe, budget)) {
+            return launch_pipe<F, 8, W, UPL, R, false, true, kGroupWarps>(grouped, pipe, stream);
         }
-        if (a.tokens > 2 && plan_pipe<F, W, R>(a, view, shared_act_bytes(4, K32), pipe, budget)) {
-            return launch_pipe<F, 4, W, UPL, R, false, true>(grouped, pipe, stream);
+        if (a.tokens > 2 && plan_pipe<F, W, R, kGroupWarps>(a, view, shared_act_bytes(4, K32), pipe, budget)) {
+            return launch_pipe<F, 4, W, UPL, R, false, true, kGroupWarps>(grouped, pipe, stream);
         }
-        if (plan_pipe<F, W, R>(a, view, shared_act_bytes(2, K32), pipe, budget)) {
-            return launch_pipe<F, 2, W, UPL, R, false, true>(grouped, pipe, stream);
+        if (plan_pipe<F, W, R, kGroupWarps>(a, view, shared_act_bytes(2, K32), pipe, budget)) {
+            return launch_pipe<F, 2, W, UPL, R, false, true, kGroupWarps>(grouped, pipe, stream);
         }
     }
     if (!a.act_ready) {
