@@ -541,20 +541,20 @@ def main():
     if extras is not None:
         # single-kernel figures on the other shapes the baseline names: config 0 (Q8_0 4864x896), config 4's matrices at
         # batch 1 on one GPU, and the vocabulary projection in both encodings a Q4_K_M file may use for it
-        def kernel_rate(ggml_type, rows, columns, copies):
+        def kernel_rate(ggml_type, rows, columns, copies, tokens=1):
             hold = [sb.QuantizedMatrix(synth.matrix(ggml_type, rows, columns, seed=200 + c, name="shape"), ggml_type, rows, columns)
                     for c in range(copies)]
-            xs = torch.from_numpy(synth.activations(1, columns, seed=7)).to(device)
-            need = lib.activation_scratch_bytes(1, columns)
+            xs = torch.from_numpy(synth.activations(tokens, columns, seed=7)).to(device)
+            need = lib.activation_scratch_bytes(tokens, columns)
             work = torch.empty(need + 256, dtype=torch.uint8, device=device)
             work_ptr = (work.data_ptr() + 255) // 256 * 256
-            ys = torch.zeros(rows, dtype=torch.float32, device=device)
-            sb.quantize_device(xs.data_ptr(), 1, columns, columns, work_ptr, need, stream.cuda_stream)
+            ys = torch.zeros(tokens * rows, dtype=torch.float32, device=device)
+            sb.quantize_device(xs.data_ptr(), tokens, columns, columns, work_ptr, need, stream.cuda_stream)
 
             def once(s):
                 for _ in range(4):
                     for matrix in hold:
-                        matrix.matmul_q8_device(work_ptr, 1, ys.data_ptr(), rows, stream=s.cuda_stream)
+                        matrix.matmul_q8_device(work_ptr, tokens, ys.data_ptr(), rows, stream=s.cuda_stream)
 
             with torch.cuda.stream(stream):
                 once(stream)
@@ -586,6 +586,8 @@ def main():
             "q4_k 152064x3584 (vocabulary projection)": kernel_rate(synth.Q4_K, 152064, 3584, 1),
             "q6_k 152064x3584 (vocabulary projection as Q6_K)": kernel_rate(synth.Q6_K, 152064, 3584, 1),
         }
+        # several tokens per launch (batched decode, speculative verification): every weight is read once per launch
+        extras["matvec_q4_k_18944x3584_tokens"] = {str(t): kernel_rate(synth.Q4_K, 18944, 3584, 4, tokens=t) for t in (2, 4, 8)}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
