@@ -121,3 +121,24 @@ def test_gather_entry_stores_every_result_into_all_copies(ggml_type):
             assert bool((copy[:share] == -7.0).all()) and bool((copy[2 * share:] == -7.0).all())
         with pytest.raises(sb.KernelError):
             matrix.matmul_q8_gather_device(scratch_ptr, 1, copies[0].data_ptr(), share, [copies[1].data_ptr()] * 8)
+
+
+def test_shared_buffer_and_peer_access_entry_points():
+    """The buffer that other processes map: created zero-filled, usable as an output of the product, and the error
+    paths of the mapping calls (a process cannot map its own export; peer access to oneself is a no-op, to a device
+    that does not exist an error)."""
+    import torch
+
+    lib = sb.library()
+    pointer, handle = lib.shared_buffer_create(4096)
+    try:
+        assert len(handle) == 64 and pointer % 256 == 0
+        with pytest.raises(sb.BackendUnavailableError):
+            lib.shared_buffer_open(handle)
+        lib.enable_peer_access(torch.cuda.current_device())
+        with pytest.raises(sb.KernelError):
+            lib.enable_peer_access(4096)
+        with pytest.raises(sb.KernelError):
+            lib.shared_buffer_create(0)
+    finally:
+        lib.shared_buffer_destroy(pointer)
