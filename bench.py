@@ -10,8 +10,13 @@ so no flush is needed between iterations.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
-With N > 1 (launched under torchrun) every matrix is sharded by output rows across the ranks and the output
-slices are all-gathered over NCCL; the same total work is split, so scaling is "strong".
+One step launches one kernel per fused region of a layer, as the reference's executors do: q | k as two segments of one
+launch with v (another encoding) beside it, o, gate | up with SwiGLU applied in registers, down; `--separate` launches
+every matrix on its own. With N > 1 (launched under torchrun, one rank per GPU) every matrix is sharded by output rows
+across the ranks; by default the product kernels store each result into every GPU's copy of the output vector over
+NVLink (`--gather peer`), `--gather nccl` all-gathers the slices with NCCL after each product instead. The same total
+work is split, so scaling is "strong". Before timing, every rank compares the gathered vectors with whole-matrix
+products computed locally (`gather_verified`).
 """
 from __future__ import annotations
 
@@ -44,11 +49,8 @@ def parse_args():
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--layers", type=int, default=28, help="layers of the model shape (28 = the full config)")
     parser.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
-    parser.add_argument("--quantize", default="shared", choices=["shared", "fused"],
-                        help="shared: one quantiser launch per distinct layer input, reused by the projections that read it "
-                             "(1.30 ms per step); fused: every product quantises its FP32 input inside the kernel (1.52 ms; "
-                             "fusing only the products that read a vector alone, o and down: 1.46 ms)")
-    parser.add_argument("--serial", action="store_true", help="run q/k/v and gate/up one after the other instead of on parallel graph branches")
+    parser.add_argument("--separate", action="store_true",
+                        help="one launch per matrix (q | k | v and gate | up on parallel graph branches) instead of one launch per fused region")
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                         help="N > 1: output slices are stored into every GPU's copy by the product kernel itself (peer), or "
@@ -134,6 +136,23 @@ def measured_peak_hbm():
             return float(json.load(handle)["hbm_gbs"]), "measured"
     except (OSError, KeyError, ValueError):
         return 6650.0, "fallback"
+
+
+def profile_traffic(bytes_per_launch):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the roofline kernel, from the tracked ncu summary whose
+    `traffic_bytes_per_launch` line was captured on a launch of exactly this many algorithmic bytes; None otherwise."""
+    import glob
+    import re
+
+    for path in sorted(glob.glob(os.path.join(ROOT, "profiles", "*.md"))):
+        try:
+            text = open(path).read()
+        except OSError:
+            continue
+        match = re.search(r"traffic_bytes_per_launch:\s*(\d+)\s+algorithmic_bytes_per_launch:\s*(\d+)", text)
+        if match and int(match.group(2)) == bytes_per_launch:
+            return int(match.group(1))
+    return None
 
 
 # ------------------------------------------------------------------------------------------------------------
@@ -248,26 +267,35 @@ def main():
                            bias=True)
     leaf_fields = {"attn_q": "query", "attn_k": "key", "attn_v": "value", "attn_o": "attention_output", "ffn_gate": "gate", "ffn_up": "up",
                    "ffn_down": "down"}
+
+    def image_bytes(name, rows, columns, ggml_type, first_row, row_count):
+        leaf = name.split(".")[-1]
+        base = image.output if leaf == "lm_head" else getattr(image.layers[int(name.split(".")[1])], leaf_fields[leaf])
+        row_bytes = synth.row_bytes(ggml_type, columns)
+        return image.weights[base + first_row * row_bytes:base + (first_row + row_count) * row_bytes]
+
     matrices = []
     total_bytes = 0
     for name, ggml_type, rows, columns in model_matrices(args.layers):
-        leaf = name.split(".")[-1]
-        base = image.output if leaf == "lm_head" else getattr(image.layers[int(name.split(".")[1])], leaf_fields[leaf])
-        _, shard_rows = sharding.shard_rows(rows, world, rank)
-        offset, count = sharding.shard_bytes(ggml_type, rows, columns, world, rank)
-        shard = image.weights[base + offset:base + offset + count]
+        first_row, shard_rows = sharding.shard_rows(rows, world, rank)
+        shard = image_bytes(name, rows, columns, ggml_type, first_row, shard_rows)
         matrices.append((name, ggml_type, rows, columns, shard_rows, sb.QuantizedMatrix(shard, ggml_type, shard_rows, columns)))
         total_bytes += rows * synth.row_bytes(ggml_type, columns)
+    by_name = {m[0]: m for m in matrices}
 
     # ---- activations (resident) and outputs -----------------------------------------------------------------
-    x_host = {3584: synth.activations(1, 3584, seed=5), 18944: synth.activations(1, 18944, seed=6)}
+    # Output vectors of a step, full length on every rank: q | k | v share one vector (the row space of the reference's
+    # QKV region), gate and up produce the feed-forward vector silu(gate) * up.
+    hidden, ffn, kvw, vocabulary = shape["hidden"], shape["feed_forward"], shape["kv_heads"] * (shape["hidden"] // shape["heads"]), shape["vocabulary"]
+    vectors = {"qkv": hidden + 2 * kvw, "attn_o": hidden, "ffn": ffn, "gate": ffn, "up": ffn, "ffn_down": hidden, "lm_head": vocabulary}
+    x_host = {hidden: synth.activations(1, hidden, seed=5), ffn: synth.activations(1, ffn, seed=6)}
     x_dev = {k: torch.from_numpy(v).to(device) for k, v in x_host.items()}
     scratch = {k: torch.empty(lib.activation_scratch_bytes(1, k) + 256, dtype=torch.uint8, device=device) for k in x_host}
     peers = None
     if world > 1 and args.gather == "peer":
         # every rank's full output vectors live in one buffer that all other ranks map: the kernels gather by storing
         try:
-            peers = sharding.PeerOutputs({f"{m[0].split('.')[-1]}:{m[2]}": m[2] for m in matrices}, device)
+            peers = sharding.PeerOutputs(vectors, device)
         except Exception as error:
             sys.stderr.write(f"rank {rank}: peer mapping failed ({error}); gathering with NCCL\n")
             peers = None
@@ -277,73 +305,111 @@ def main():
             peers.close()
             peers = None
     if peers is not None:
-        out_full = {(m[0].split(".")[-1], m[2]): peers.view(f"{m[0].split('.')[-1]}:{m[2]}") for m in matrices}
+        out_full = {name: peers.view(name) for name in vectors}
     else:
-        out_full = {(m[0].split(".")[-1], m[2]): torch.zeros(m[2], dtype=torch.float32, device=device) for m in matrices}
-    out_shard = {(m[0].split(".")[-1], m[4]): torch.zeros(m[4], dtype=torch.float32, device=device) for m in matrices}
+        out_full = {name: torch.zeros(length, dtype=torch.float32, device=device) for name, length in vectors.items()}
+    out_shard = {m[0].split(".")[-1]: torch.zeros(m[4], dtype=torch.float32, device=device) for m in matrices}
+    # one launch per fused region (q | k, gate | up) unless told otherwise; NCCL gathers work per matrix
+    fused_regions = not args.separate and (world == 1 or peers is not None)
 
     def aligned(tensor):
         return (tensor.data_ptr() + 255) // 256 * 256
 
     side = [torch.cuda.Stream(device), torch.cuda.Stream(device)]
 
-    def product(entry, stream):
-        name, ggml_type, rows, columns, shard_rows, matrix = entry
+    def destination(vector, column):
+        """(own pointer, peer pointers) of element `column` of this rank's copy of `vector` and of every other rank's."""
         if peers is not None:
-            first_row, _ = sharding.shard_rows(rows, world, rank)
-            own, others = peers.pointers(f"{name.split('.')[-1]}:{rows}", first_row)
-            matrix.matmul_q8_gather_device(aligned(scratch[columns]), 1, own, shard_rows, others, stream=stream.cuda_stream)
-            return
-        target = out_shard[(name.split(".")[-1], shard_rows)] if world > 1 else out_full[(name.split(".")[-1], rows)]
-        if args.quantize == "fused":
-            matrix.matvec_device(x_dev[columns].data_ptr(), 1, columns, target.data_ptr(), shard_rows, sb.MODE_XQ8,
-                                 scratch_ptr=aligned(scratch[columns]), scratch_bytes=lib.activation_scratch_bytes(1, columns),
-                                 stream=stream.cuda_stream)
-        else:
+            return peers.pointers(vector, column)
+        return out_full[vector].data_ptr() + 4 * column, []
+
+    def product(entry, vector, column, stream, signal=False):
+        """One matrix (this rank's rows of it) into `vector` at `column` + the rank's first row; with `signal` the launch
+        also writes its sequence number into this rank's word of every GPU's signal array of the vector."""
+        name, ggml_type, rows, columns, shard_rows, matrix = entry
+        first_row, _ = sharding.shard_rows(rows, world, rank)
+        if world > 1 and peers is None:
+            target = out_shard[name.split(".")[-1]]
             matrix.matmul_q8_device(aligned(scratch[columns]), 1, target.data_ptr(), shard_rows, stream=stream.cuda_stream)
-        if world > 1:
             with torch.cuda.stream(stream):
-                sharding.gather_outputs(target, out_full[(name.split(".")[-1], rows)])
+                sharding.gather_outputs(target, out_full[vector][column:column + rows])
+            return
+        own, others = destination(vector, column + first_row)
+        if others:
+            words, arrivals = peers.signals(vector) if signal else ((), 0)
+            matrix.matmul_q8_gather_device(aligned(scratch[columns]), 1, own, shard_rows, others, stream=stream.cuda_stream, signal_ptrs=words,
+                                           arrivals_ptr=arrivals)
+        else:
+            matrix.matmul_q8_device(aligned(scratch[columns]), 1, own, shard_rows, stream=stream.cuda_stream)
+
+    def segments(entries, vector, columns_out, stream):
+        """Several matrices of one encoding against the same activations in ONE launch (Q | K)."""
+        parts, peer_lists = [], None
+        for entry, column in zip(entries, columns_out):
+            name, ggml_type, rows, columns, shard_rows, matrix = entry
+            first_row, _ = sharding.shard_rows(rows, world, rank)
+            parts.append((matrix, 0, shard_rows, 0, column + first_row))
+        own, others = destination(vector, 0)
+        sb.matmul_q8_segments_device(parts, aligned(scratch[entries[0][3]]), 1, own, vectors[vector], peer_ptrs=others, stream=stream.cuda_stream)
+
+    def gate_up(gate_entry, up_entry, stream):
+        """silu(gate . x) * (up . x) for this rank's rows in ONE launch."""
+        name, ggml_type, rows, columns, shard_rows, gate_matrix = gate_entry
+        first_row, _ = sharding.shard_rows(rows, world, rank)
+        own, others = destination("ffn", first_row)
+        sb.matmul_q8_swiglu_device(gate_matrix, up_entry[5], aligned(scratch[columns]), 1, own, shard_rows, peer_ptrs=others, stream=stream.cuda_stream)
 
     def quantize(columns, stream):
-        if args.quantize == "shared":
-            sb.quantize_device(x_dev[columns].data_ptr(), 1, columns, columns, aligned(scratch[columns]),
-                               lib.activation_scratch_bytes(1, columns), stream.cuda_stream)
+        sb.quantize_device(x_dev[columns].data_ptr(), 1, columns, columns, aligned(scratch[columns]),
+                           lib.activation_scratch_bytes(1, columns), stream.cuda_stream)
 
-    def parallel(entries, main):
-        """Independent products of the same input: the first on the main stream, the others on side streams."""
-        if args.serial or (world > 1 and peers is None) or len(entries) == 1:
-            for entry in entries:
-                product(entry, main)
+    def parallel(calls, main):
+        """Independent launches that read the same activations: the first on the main stream, the others on side streams
+        (parallel branches of the captured graph)."""
+        if (world > 1 and peers is None) or len(calls) == 1:
+            for call in calls:
+                call(main)
             return
         fork = torch.cuda.Event()
         fork.record(main)
-        for entry, stream in zip(entries[1:], side):
+        for call, stream in zip(calls[1:], side):
             stream.wait_event(fork)
-            product(entry, stream)
-        product(entries[0], main)
-        for _, stream in zip(entries[1:], side):
+            call(stream)
+        calls[0](main)
+        for _, stream in zip(calls[1:], side):
             join = torch.cuda.Event()
             join.record(stream)
             main.wait_event(join)
 
     def step(main):
-        """One pass. Activations are quantised once per distinct input of a layer (as the reference's executor does,
-        Qwen2CpuExecutor.cs:165-185) or inside each product; q/k/v and gate/up are independent and run on parallel
-        branches of the graph, everything else in stream order."""
-        by_name = {m[0]: m for m in matrices}
+        """One pass. Activations are quantised once per distinct input of a layer, as the reference's executor does
+        (Qwen2CpuExecutor.cs:165-185). Q | K run as one launch of two segments with V (Q6_K, another encoding) beside it
+        on a parallel branch, gate | up as one launch that applies SwiGLU in registers; `--separate` launches every matrix
+        on its own (q | k | v and gate | up on parallel branches), the form earlier figures were measured in."""
         for layer in range(args.layers):
             get = lambda leaf: by_name[f"blk.{layer}.{leaf}"]
-            quantize(3584, main)
-            parallel([get("attn_q"), get("attn_k"), get("attn_v")], main)
-            quantize(3584, main)
-            parallel([get("attn_o")], main)
-            quantize(3584, main)
-            parallel([get("ffn_gate"), get("ffn_up")], main)
-            quantize(18944, main)
-            parallel([get("ffn_down")], main)
-        quantize(3584, main)
-        parallel([by_name["lm_head"]], main)
+            quantize(hidden, main)
+            if fused_regions:
+                parallel([lambda s: segments([get("attn_q"), get("attn_k")], "qkv", [0, hidden], s),
+                          lambda s: product(get("attn_v"), "qkv", hidden + kvw, s)], main)
+            else:
+                parallel([lambda s: product(get("attn_q"), "qkv", 0, s), lambda s: product(get("attn_k"), "qkv", hidden, s),
+                          lambda s: product(get("attn_v"), "qkv", hidden + kvw, s)], main)
+            quantize(hidden, main)
+            product(get("attn_o"), "attn_o", 0, main)
+            quantize(hidden, main)
+            if fused_regions:
+                gate_up(get("ffn_gate"), get("ffn_up"), main)
+            else:
+                parallel([lambda s: product(get("ffn_gate"), "gate", 0, s), lambda s: product(get("ffn_up"), "up", 0, s)], main)
+            quantize(ffn, main)
+            product(get("ffn_down"), "ffn_down", 0, main)
+        quantize(hidden, main)
+        product(by_name["lm_head"], "lm_head", 0, main, signal=True)
+        if peers is not None:
+            # The step's completion on this rank: every rank's last product has signalled, and a rank's products are
+            # stream-ordered, so all slices of all vectors of the step have landed in this GPU's copies.
+            sb.gather_wait_device(*peers.wait_arguments("lm_head"), timeout_us=2_000_000, stream=main.cuda_stream)
 
     stream = torch.cuda.Stream(device)
     graph = None
@@ -352,6 +418,55 @@ def main():
         step(stream)
     torch.cuda.synchronize()
     launches_per_step = lib.launch_count(reset=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- N > 1: before anything is timed, every rank checks the vectors the step has just gathered against the same
+    # products of the WHOLE matrices computed locally (the last layer's, whose results the vectors hold, and the
+    # vocabulary projection): they must be equal bit for bit, since a row's value does not depend on its shard.
+    gather_verified = None
+    if world > 1:
+        barrier()  # every rank's stores (or gathers) of the first step have landed
+        last = args.layers - 1
+        checks, mismatches = 0, 0
+
+        def whole(name):
+            _, ggml_type, rows, columns, _, _ = by_name[name]
+            return sb.QuantizedMatrix(image_bytes(name, rows, columns, ggml_type, 0, rows), ggml_type, rows, columns)
+
+        with torch.cuda.stream(stream):
+            expected = {name: torch.zeros(length, dtype=torch.float32, device=device) for name, length in vectors.items()}
+            for columns in (hidden, ffn):
+                quantize(columns, stream)
+            plan = [("qkv", 0, f"blk.{last}.attn_q"), ("qkv", hidden, f"blk.{last}.attn_k"), ("qkv", hidden + kvw, f"blk.{last}.attn_v"),
+                    ("attn_o", 0, f"blk.{last}.attn_o"), ("ffn_down", 0, f"blk.{last}.ffn_down"), ("lm_head", 0, "lm_head")]
+            for vector, column, name in plan:
+                with whole(name) as matrix:
+                    matrix.matmul_q8_device(aligned(scratch[matrix.columns]), 1, expected[vector].data_ptr() + 4 * column, matrix.rows, stream=stream.cuda_stream)
+                    stream.synchronize()
+            with whole(f"blk.{last}.ffn_gate") as gate_whole, whole(f"blk.{last}.ffn_up") as up_whole:
+                if fused_regions:
+                    sb.matmul_q8_swiglu_device(gate_whole, up_whole, aligned(scratch[hidden]), 1, expected["ffn"].data_ptr(), ffn, stream=stream.cuda_stream)
+                else:
+                    gate_whole.matmul_q8_device(aligned(scratch[hidden]), 1, expected["gate"].data_ptr(), ffn, stream=stream.cuda_stream)
+                    up_whole.matmul_q8_device(aligned(scratch[hidden]), 1, expected["up"].data_ptr(), ffn, stream=stream.cuda_stream)
+                stream.synchronize()
+        for name in vectors:
+            if (name in ("gate", "up")) == fused_regions:
+                continue
+            checks += 1
+            if not torch.equal(out_full[name], expected[name]):
+                mismatches += 1
+                sys.stderr.write(f"rank {rank}: gathered vector {name} differs from the whole-matrix product\n")
+        verdict = torch.tensor([mismatches], device=device)
+        dist.all_reduce(verdict)
+        gather_verified = {"ok": int(verdict.item()) == 0, "vectors_per_rank": checks, "ranks": world,
+                           "how": "bitwise equal to the whole-matrix products computed on every rank"}
+        del expected
+
     use_graph = not args.no_graph
     if use_graph:
         try:
@@ -371,11 +486,6 @@ def main():
             graph.replay()
         else:
             step(stream)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
 
     with torch.cuda.stream(stream):
         for _ in range(max(args.warmup, 3)):
@@ -401,15 +511,20 @@ def main():
     ms_per_step = elapsed_ms / args.steps
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
 
-    # ---- roofline of the dominant kernel: the Q4_K matvec on the gate/up matrices (38 MB each) -------------
-    big = [m for m in matrices if m[0].endswith("ffn_gate") or m[0].endswith("ffn_up")]
-    per_launch_bytes = big[0][4] * synth.row_bytes(big[0][1], big[0][3])
-    # Every gate/up matrix once per pass (56 x 38 MB, no L2 reuse), launches back to back in stream order; timed with
+    # ---- roofline of the dominant kernel: the gate | up launch (two Q4_K matrices of 38 MB, one launch) --------
+    gates = [m for m in matrices if m[0].endswith("ffn_gate")]
+    ups = [m for m in matrices if m[0].endswith("ffn_up")]
+    per_matrix_bytes = gates[0][4] * synth.row_bytes(gates[0][1], gates[0][3])
+    per_launch_bytes = (2 if fused_regions else 1) * per_matrix_bytes
+    # Every gate/up pair once per pass (28 x 76 MB, no L2 reuse), launches back to back in stream order; timed with
     # CUDA events on the launch stream around whole passes, so the figure includes the gaps between launches.
     def roofline_pass(main):
-        for name, ggml_type, rows, columns, shard_rows, matrix in big:
-            matrix.matmul_q8_device(aligned(scratch[columns]), 1, out_full[(name.split(".")[-1], rows)].data_ptr(), shard_rows,
-                                    stream=main.cuda_stream)
+        for gate_entry, up_entry in zip(gates, ups):
+            if fused_regions:
+                gate_up(gate_entry, up_entry, main)
+            else:
+                product(gate_entry, "gate", 0, main)
+                product(up_entry, "up", 0, main)
 
     with torch.cuda.stream(stream):
         roofline_pass(stream)
@@ -428,21 +543,53 @@ def main():
             roofline_graph.replay() if roofline_graph is not None else roofline_pass(stream)
         e1.record(stream)
         stream.synchronize()
-    kernel_ms = e0.elapsed_time(e1) / (passes * len(big))
-    durations = [None] * (passes * len(big))
+    launches_timed = passes * len(gates) * (1 if fused_regions else 2)
+    kernel_ms = e0.elapsed_time(e1) / launches_timed
     peak, peak_kind = measured_peak_hbm()
     achieved = per_launch_bytes / (kernel_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "matvec_xq8_kernel<Q4_K, T=1> on ffn_gate/ffn_up (18944x3584)", "achieved": achieved,
-                "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
-                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this matrix shape, from the ncu
-                # capture summarised in profiles/matvec_q4k_18944x3584.md (38,212,352 read, 0 written: outputs stay in L2)
-                "traffic": 38212352 if per_launch_bytes == 38191104 else None,
-                "bytes_per_launch": per_launch_bytes, "us_per_launch": kernel_ms * 1e3, "launches_timed": len(durations)}
+    kernel_name = ("matvec_xq8_pipe_kernel<Q4KXq8, T=1, W=1, UPL=1, R=2, CW=8, kPair> on ffn_gate | ffn_up (2 x 18944x3584, SwiGLU in registers)"
+                   if fused_regions else "matvec_xq8_pipe_kernel<Q4KXq8, T=1, W=1, UPL=1, R=2, CW=8> on ffn_gate / ffn_up (18944x3584)")
+    roofline = {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+                "frac": achieved / peak, "traffic": profile_traffic(per_launch_bytes) if world == 1 else None,
+                "bytes_per_launch": per_launch_bytes, "us_per_launch": kernel_ms * 1e3, "launches_timed": launches_timed}
 
-    # ---- end to end through the host-pointer C ABI: pinned host x in, host y out, per matrix ----------------
+    # ---- end to end, host buffers in and out ----------------------------------------------------------------------
     e2e = None
     per_matrix = None
-    if not args.no_e2e:
+    if not args.no_e2e and world > 1:
+        # N > 1: the row-sharded step through the device entry points with the exchange inside: every step copies the
+        # activations from pinned host memory, runs the gathered step, waits until every rank's slices have landed
+        # (a barrier across the ranks) and reads the gathered vocabulary vector back to the host.
+        host_x = {k: torch.from_numpy(v).pin_memory() for k, v in x_host.items()}
+        host_logits = torch.zeros(vocabulary, dtype=torch.float32).pin_memory()
+
+        def e2e_step():
+            with torch.cuda.stream(stream):
+                for columns, tensor in x_dev.items():
+                    tensor.copy_(host_x[columns].view_as(tensor), non_blocking=True)
+                run_step()
+            barrier()
+            with torch.cuda.stream(stream):
+                host_logits.copy_(out_full["lm_head"], non_blocking=True)
+                stream.synchronize()
+
+        e2e_steps = max(3, min(args.steps, 20))
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        start = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e2e_seconds = time.perf_counter() - start
+        slowest = torch.tensor([e2e_seconds], dtype=torch.float64, device=device)
+        dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+        e2e_seconds = float(slowest.item())
+        e2e = {"value": total_bytes * e2e_steps / e2e_seconds / 1e9, "unit": UNIT, "h2d_bytes_per_step": 4 * (hidden + ffn),
+               "d2h_bytes_per_step": 4 * vocabulary, "ms_per_step": e2e_seconds / e2e_steps * 1e3, "steps": e2e_steps,
+               "api": "row-sharded step through the device entry points (" + ("syn_b200_matmul_q8_segments_dev / _swiglu_dev / _gather_dev storing "
+                      "into every GPU's copy" if peers is not None else "syn_b200_matmul_q8_dev + NCCL all-gather per product") +
+                      "): pinned host activations in, a barrier across the ranks as the completion of the exchange, gathered vocabulary vector out"}
+    if not args.no_e2e and world == 1:
         # (a) the per-projection boundary: one host call per matrix, pinned host x in, host y out
         host_x = {k: torch.from_numpy(v).pin_memory() for k, v in x_host.items()}
         host_y = {m[4]: torch.zeros(m[4], dtype=torch.float32).pin_memory() for m in matrices}
@@ -464,10 +611,6 @@ def main():
             e2e_step()
         barrier()
         e2e_seconds = time.perf_counter() - start
-        if world > 1:
-            slowest = torch.tensor([e2e_seconds], dtype=torch.float64, device=device)
-            dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
-            e2e_seconds = float(slowest.item())
         per_matrix = {"value": total_bytes * e2e_steps / e2e_seconds / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                       "ms_per_step": e2e_seconds / e2e_steps * 1e3, "steps": e2e_steps,
                       "api": "syn_b200_matvec (host FP32 activations in, host FP32 outputs out, one call per matrix)"}
@@ -600,11 +743,13 @@ def main():
                 "config": {"workload": WORKLOAD, "layers": args.layers, "matrices": len(matrices), "bytes_per_step": total_bytes,
                            "activation_contract": "xq8 (Q8_0 activation quantiser reproduced on device)",
                            "layout": "Q4_K file layout; Q6_K repacked to planes at load", "cuda_graph": bool(graph is not None),
-                           "quantize": args.quantize, "branches": "serial" if args.serial else "q|k|v and gate|up on parallel graph branches",
-                           "l2": "weights per step exceed L2 35x, no flush", "parallelism": (f"row-shard x{world}, " + ("slices stored into every GPU's copy by the product kernel" if peers is not None
+                           "launches": ("one per fused region: q|k (two segments) with v beside it, o, gate|up with SwiGLU in registers, down" if fused_regions
+                                        else "one per matrix, q|k|v and gate|up on parallel graph branches"),
+                           "projection_launches_per_step": (5 if fused_regions else 7) * args.layers + 1,
+                           "l2": "weights per step exceed L2 35x, no flush", "parallelism": (f"row-shard x{world}, " + ("slices stored into every GPU's copy by the product kernel; every step ends with a bounded wait for all ranks' completion signals" if peers is not None
                                                                      else "NCCL all-gather per product")) if world > 1 else "single gpu",
                            "tokens_per_s": 1e3 / ms_per_step},
-                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_per_matrix_calls": per_matrix, "extras": extras, "clocks": clocks,
+                "gather_verified": gather_verified, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_per_matrix_calls": per_matrix, "extras": extras, "clocks": clocks,
                 "gpu_launches": int(launches_per_step * args.steps)}
         sys.stdout.flush()
         os.write(result_fd, (json.dumps(line) + "\n").encode())

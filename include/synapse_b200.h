@@ -153,7 +153,9 @@ SYN_B200_API int32_t syn_b200_gemm(const syn_b200_matrix *matrix, const float *x
 
 /* Test hook: the exact integer sub-block dots of the XQ8 contract, HOST buffers.
  * out[(t*row_count + r) * groups + g]; groups per row = columns/32 (Q8_0), columns/32 (Q4_K, one per
- * sub-block), columns/16 (Q6_K). The sums are produced by the same device code as syn_b200_matmul_q8. */
+ * sub-block), columns/16 (Q6_K). The sums come, token by token, out of the kernel variant that a single-token product of
+ * the same rows takes (the pipelined kernel, also its sixteen-warp form for the largest matrices), built with this hook
+ * compiled in. */
 SYN_B200_API int32_t syn_b200_block_dots(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
                             const int8_t *codes, uint64_t tokens, int32_t *out);
 
@@ -181,17 +183,73 @@ SYN_B200_API int32_t syn_b200_matmul_q8_ex_dev(const syn_b200_matrix *matrix, ui
                                                const void *scratch, uint64_t tokens, float *y, uint64_t out_stride,
                                                const syn_b200_epilogue *epilogue, void *stream);
 
+/* Where a row-sharded product puts its results besides `y`, and how it tells the other GPUs that they are there.
+ * `peer_outputs`: `peer_count` (at most 7) DEVICE pointers, the other GPUs' copies of the output mapped into this process
+ * (syn_b200_shared_buffer_open), offset like `y` to the shard's first row; `peer_outputs` itself is a host array.
+ * `signals` (host array, may be null): peer_count + 1 DEVICE pointers to 32-bit words, this rank's word of the product's
+ * signal array in this GPU's memory first, then in each peer's. `arrivals`: two zero-initialised words in THIS GPU's memory
+ * that belong to this product alone. When the last CTA of the launch has stored its results it writes the launch's
+ * sequence number (1, 2, ... per product, counted in arrivals[1]) to every signal word, ordered behind all stores of the
+ * launch at system scope. A GPU whose signal array shows sequence number n in every word holds the n-th gathered vector
+ * complete (syn_b200_gather_wait_dev). Launches that share signal words must be ordered on one stream. */
+typedef struct syn_b200_gather {
+    float *const *peer_outputs;
+    uint32_t peer_count;
+    uint32_t reserved; /* must be 0 */
+    uint32_t *const *signals;
+    uint32_t *arrivals;
+} syn_b200_gather;
+
 /* syn_b200_matmul_q8_dev for a row shard of a matrix that is split over several GPUs: the kernel stores every result
- * into `y` AND at the same position of `peer_count` (at most 7) further vectors, the other GPUs' copies of the output
- * mapped into this process (CUDA IPC or symmetric memory). `y` and every `peer_outputs[i]` are already offset to the
- * shard's first row; `peer_outputs` is a host array of device pointers. The gather of the output slices thus happens
- * inside the product, as plain stores over NVLink, instead of an all-gather after it; the caller still owes the ranks a
- * synchronisation before anyone reads a full vector. The reference has no multi-GPU path
+ * into `y` AND at the same position of the peers' copies of the output -- plain stores over NVLink from the lane that
+ * holds the result, so the gather of the output slices happens inside the product instead of in an all-gather after
+ * it -- and signals completion as `gather` describes. The reference has no multi-GPU path
  * (native/synapse-gpu/src/Features/GpuKernels/ffi.rs:113-271 drives one device); this is the exchange step of the
  * row-sharded configuration. */
 SYN_B200_API int32_t syn_b200_matmul_q8_gather_dev(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
                                                    const void *scratch, uint64_t tokens, float *y, uint64_t out_stride,
-                                                   float *const *peer_outputs, uint32_t peer_count, void *stream);
+                                                   const syn_b200_gather *gather, void *stream);
+
+/* Queues a one-warp kernel that waits until each of the `count` (1..8) words of this GPU's signal array `signals` has
+ * reached the next sequence number, *epoch + 1, and then stores that number to *epoch (a zero-initialised DEVICE word
+ * owned by the waiter, so the call can sit in a replayed CUDA graph). Kernels queued behind it on `stream` see the
+ * complete gathered vector. The wait is bounded: after `timeout_us` microseconds without the signal the kernel gives
+ * up, adds one to the fault count (syn_b200_device_faults) and returns; nothing is left waiting and the context stays
+ * usable. Reusing an output vector for the next product before every rank has read it is the caller's protocol (two
+ * vectors in turn, or a signal back). No reference counterpart (single-device ABI). */
+SYN_B200_API int32_t syn_b200_gather_wait_dev(const uint32_t *signals, uint32_t count, uint32_t *epoch, uint32_t timeout_us,
+                                              void *stream);
+
+/* One row range of a product that multiplies several matrices with the same activations in ONE launch. Mirrors
+ * MatmulSegment (native/synapse-gpu/src/Features/GpuKernels/params.rs:42-61; cuda/kernels/common.cuh:52-69): a result of
+ * row r of the range goes to y[token * out_stride + out_column + r], plus bias[r] when `bias` (DEVICE memory) is set. */
+typedef struct syn_b200_segment {
+    const syn_b200_matrix *matrix;
+    uint64_t row_start, row_count;
+    const float *bias;
+    uint64_t out_column;
+} syn_b200_segment;
+
+/* y[t][out_column_s + r] (+)= W_s[row_start_s + r] . act[t] (+ bias_s[r]) for up to three segments s in one launch:
+ * the Q | K | V dispatch of the reference's GPU step (MatmulArgs with three segments, step/layers.rs:71-94) and the row
+ * space of Qwen2QkvWork (src/Synapse.Runtime/Features/TextGeneration/Qwen2/Qwen2ProjectionWork.cs:7-53). The segments'
+ * matrices must share encoding, layout and width, as in the reference. `accumulate` = 1 adds to y. `gather` as in
+ * syn_b200_matmul_q8_gather_dev (null on one GPU; the peer pointers address column 0 like `y`). Every row is computed
+ * exactly as in a launch of its own, so results are bit-identical to separate products. */
+SYN_B200_API int32_t syn_b200_matmul_q8_segments_dev(const syn_b200_segment *segments, uint32_t count, const void *scratch,
+                                                     uint64_t tokens, float *y, uint64_t out_stride, uint32_t accumulate,
+                                                     const syn_b200_gather *gather, void *stream);
+
+/* y[t][r] = silu(gate[row_start + r] . act[t]) * (up[row_start + r] . act[t]) in one launch: the gate/up region of the
+ * reference's CPU executor (Qwen2GateUpWork, Qwen2ProjectionWork.cs:91-131) and its gate | up dispatch followed by
+ * synapse_swiglu (step/layers.rs:159-177, cuda/kernels/elementwise.cu:100-110). The warp that holds gate row r holds up
+ * row r too, so for single-token products the gate values never go to memory. Several tokens, or rows longer than one
+ * pass of a warp team, run as two launches through `gate_values` (DEVICE, tokens * out_stride floats), which may be null
+ * otherwise. `gather` as in syn_b200_matmul_q8_gather_dev (null on one GPU). Bit-identical to the two-launch form. */
+SYN_B200_API int32_t syn_b200_matmul_q8_swiglu_dev(const syn_b200_matrix *gate, const syn_b200_matrix *up, uint64_t row_start,
+                                                   uint64_t row_count, const void *scratch, uint64_t tokens, float *y,
+                                                   uint64_t out_stride, float *gate_values, const syn_b200_gather *gather,
+                                                   void *stream);
 
 /* A zero-filled device buffer that other processes on the same box can map (CUDA IPC), for the output vectors of
  * row-sharded products: create it on the owning GPU, hand the 64-byte handle to the other ranks by any means, and let
@@ -206,7 +264,7 @@ SYN_B200_API void syn_b200_shared_buffer_destroy(void *device_ptr);
 
 /* Lets kernels of the calling thread's current device read and write memory of `peer_device` (cudaDeviceEnablePeerAccess;
  * already enabled is not an error). A process that maps another GPU's buffer (CUDA IPC) must call this for that GPU before
- * it passes a pointer mapped for ANOTHER device to syn_b200_matmul_q8_gather_dev (syn_b200_shared_buffer_open maps for the
+ * it passes a pointer mapped for ANOTHER device to a gathering product (syn_b200_shared_buffer_open maps for the
  * current device and needs no further call).
  * Status 3 when the two devices have no peer path. No reference counterpart (single-device ABI). */
 SYN_B200_API int32_t syn_b200_enable_peer_access(int32_t peer_device);
@@ -221,12 +279,16 @@ SYN_B200_API int32_t syn_b200_matvec_dev(const syn_b200_matrix *matrix, uint64_t
 /* Same product as syn_b200_matvec_dev in XQ8 mode, for callers that cannot allocate device memory (a decode thread
  * that must not take the allocator's lock, a plugin with a fixed memory budget, a guest in someone else's CUDA
  * context): the scratch for the quantised activations is a fixed array inside the library image, so the call needs
- * nothing beyond the caller's x and y and makes no CUDA allocation. Limits: tokens * columns must not exceed
- * syn_b200_matvec_static_capacity() (262144 values, e.g. 8 tokens of 32768), else SYN_B200_INVALID_ARGUMENT; every
- * call on a device shares the one array (about 328 KB per device, held until the process exits), so two calls that
- * overlap on the GPU race and must be ordered by the caller; the array keeps the last call's contents, which is
- * harmless because each call rewrites what it reads. The first call on a device resolves the array's device address
- * (cudaGetSymbolAddress): make that call outside any stream capture. No counterpart in the reference. */
+ * nothing beyond the caller's x and y and calls neither cudaMalloc nor cudaFree nor any allocating library routine.
+ * Limits: tokens * columns must not exceed syn_b200_matvec_static_capacity() (262144 values, e.g. 8 tokens of 32768),
+ * else SYN_B200_INVALID_ARGUMENT; every call on a device shares the one array (about 328 KB per device, held until the
+ * process exits), so two calls that overlap on the GPU race and must be ordered by the caller; the array keeps the last
+ * call's contents, which is harmless because each call rewrites what it reads. The first call on a device resolves
+ * the array's device address (cudaGetSymbolAddress), and the first launch of each kernel variant makes the CUDA runtime
+ * load that kernel and raise its shared-memory limit, which the runtime may back with memory of its own: make one
+ * warm-up call per matrix shape and device before the region that must not allocate, and outside any stream capture.
+ * Results and launches are those of syn_b200_matvec_dev (one token: a single kernel that quantises x itself).
+ * No counterpart in the reference. */
 SYN_B200_API int32_t syn_b200_matvec_static(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
                                             const float *x, uint64_t tokens, uint64_t in_stride, float *y,
                                             uint64_t out_stride, uint32_t epilogue, void *stream);

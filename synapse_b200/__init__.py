@@ -57,6 +57,37 @@ class Epilogue(ctypes.Structure):
     _fields_ = [("bias", c_void_p), ("gate", c_void_p), ("gate_stride", c_uint64), ("accumulate", c_uint32), ("reserved", c_uint32)]
 
 
+class Segment(ctypes.Structure):
+    """``syn_b200_segment``: one row range of a product that multiplies several matrices in one launch (the reference's
+    ``MatmulSegment``, native/synapse-gpu/src/Features/GpuKernels/params.rs:42-61)."""
+
+    _fields_ = [("matrix", c_void_p), ("row_start", c_uint64), ("row_count", c_uint64), ("bias", c_void_p), ("out_column", c_uint64)]
+
+
+class Gather(ctypes.Structure):
+    """``syn_b200_gather``: the other GPUs' copies of a row-sharded product's output and its completion signal."""
+
+    _fields_ = [("peer_outputs", POINTER(c_void_p)), ("peer_count", c_uint32), ("reserved", c_uint32), ("signals", POINTER(c_void_p)),
+                ("arrivals", c_void_p)]
+
+
+def _gather(peer_ptrs, signal_ptrs=(), arrivals_ptr=0):
+    """A ``Gather`` (with the arrays it points to kept alive on it), or None for a product on one GPU without a signal."""
+    if not peer_ptrs and not signal_ptrs:
+        return None
+    gather = Gather()
+    gather._peers = (c_void_p * max(len(peer_ptrs), 1))(*peer_ptrs)
+    gather.peer_outputs = ctypes.cast(gather._peers, POINTER(c_void_p))
+    gather.peer_count = len(peer_ptrs)
+    if signal_ptrs:
+        if len(signal_ptrs) != len(peer_ptrs) + 1:
+            raise ValueError("a completion signal needs one word per peer plus this GPU's own")
+        gather._signals = (c_void_p * len(signal_ptrs))(*signal_ptrs)
+        gather.signals = ctypes.cast(gather._signals, POINTER(c_void_p))
+        gather.arrivals = arrivals_ptr
+    return gather
+
+
 class DeviceInfo(ctypes.Structure):
     _fields_ = [("name", c_char * 128), ("total_memory_bytes", c_uint64), ("max_buffer_bytes", c_uint64),
                 ("compute_capability", c_uint32), ("multiprocessors", c_uint32)]
@@ -84,9 +115,12 @@ _EXPORTS = {
     "syn_b200_shared_buffer_close": (None, [c_void_p]),
     "syn_b200_shared_buffer_destroy": (None, [c_void_p]),
     "syn_b200_enable_peer_access": (c_int32, [c_int32]),
-    "syn_b200_matmul_q8_gather_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, POINTER(c_void_p), c_uint32,
-                                                c_void_p]),
+    "syn_b200_matmul_q8_gather_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, POINTER(Gather), c_void_p]),
+    "syn_b200_gather_wait_dev": (c_int32, [c_void_p, c_uint32, c_void_p, c_uint32, c_void_p]),
     "syn_b200_matmul_q8_ex_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, POINTER(Epilogue), c_void_p]),
+    "syn_b200_matmul_q8_segments_dev": (c_int32, [POINTER(Segment), c_uint32, c_void_p, c_uint64, c_void_p, c_uint64, c_uint32, POINTER(Gather), c_void_p]),
+    "syn_b200_matmul_q8_swiglu_dev": (c_int32, [c_void_p, c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_void_p, c_uint64, c_void_p, POINTER(Gather),
+                                                c_void_p]),
     "syn_b200_matvec_ex_dev": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32, POINTER(Epilogue), c_void_p, c_uint64, c_void_p]),
     "syn_b200_matvec_static": (c_int32, [c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint64, c_void_p, c_uint64, c_uint32, c_void_p]),
     "syn_b200_matvec_static_capacity": (c_uint64, []),
@@ -394,13 +428,14 @@ class QuantizedMatrix:
                                                                byref(epilogue), stream))
 
     def matmul_q8_gather_device(self, scratch_ptr: int, tokens: int, y_ptr: int, out_stride: int, peer_ptrs, stream: int = 0,
-                                row_start: int = 0, row_count: int | None = None) -> None:
+                                row_start: int = 0, row_count: int | None = None, signal_ptrs=(), arrivals_ptr: int = 0) -> None:
         """The product of a row shard whose kernel also stores every result into the other GPUs' copies of the output
-        (``peer_ptrs``: device pointers mapped into this process, offset to the shard's first row like ``y_ptr``)."""
+        (``peer_ptrs``: device pointers mapped into this process, offset to the shard's first row like ``y_ptr``) and, when
+        ``signal_ptrs`` (this GPU's word first, then each peer's) and ``arrivals_ptr`` are given, signals completion."""
         row_count = self.rows - row_start if row_count is None else row_count
-        peers = (c_void_p * max(len(peer_ptrs), 1))(*peer_ptrs)
+        gather = _gather(peer_ptrs, signal_ptrs, arrivals_ptr)
         self._lib.check(self._lib.raw.syn_b200_matmul_q8_gather_dev(self.handle, row_start, row_count, scratch_ptr, tokens, y_ptr, out_stride,
-                                                                   peers, len(peer_ptrs), stream))
+                                                                   byref(gather) if gather is not None else None, stream))
 
     def matvec_static(self, x_ptr: int, tokens: int, in_stride: int, y_ptr: int, out_stride: int, epilogue: int = EPILOGUE_STORE,
                       stream: int = 0, row_start: int = 0, row_count: int | None = None) -> None:
@@ -421,6 +456,37 @@ class QuantizedMatrix:
                     scratch_bytes: int, precision: int = GEMM_F16, stream: int = 0) -> None:
         self._lib.check(self._lib.raw.syn_b200_gemm_dev(self.handle, x_ptr, tokens, in_stride, y_ptr, out_stride, precision,
                                                        scratch_ptr, scratch_bytes, stream))
+
+
+def matmul_q8_segments_device(segments, scratch_ptr: int, tokens: int, y_ptr: int, out_stride: int, accumulate: bool = False, peer_ptrs=(),
+                              stream: int = 0, signal_ptrs=(), arrivals_ptr: int = 0, lib: NativeB200Library | None = None) -> None:
+    """Up to three row ranges against the same quantised activations in one launch (Q | K | V): ``segments`` is a list of
+    ``(matrix, row_start, row_count, bias_ptr, out_column)``; results of a range go to ``y[t * out_stride + out_column + r]``."""
+    lib = lib or library()
+    packed = (Segment * max(len(segments), 1))()
+    for i, (matrix, row_start, row_count, bias_ptr, out_column) in enumerate(segments):
+        packed[i] = Segment(matrix.handle, row_start, matrix.rows - row_start if row_count is None else row_count, bias_ptr or None, out_column)
+    gather = _gather(peer_ptrs, signal_ptrs, arrivals_ptr)
+    lib.check(lib.raw.syn_b200_matmul_q8_segments_dev(packed, len(segments), scratch_ptr, tokens, y_ptr, out_stride, 1 if accumulate else 0,
+                                                      byref(gather) if gather is not None else None, stream))
+
+
+def matmul_q8_swiglu_device(gate: "QuantizedMatrix", up: "QuantizedMatrix", scratch_ptr: int, tokens: int, y_ptr: int, out_stride: int,
+                            gate_values_ptr: int = 0, peer_ptrs=(), stream: int = 0, row_start: int = 0, row_count: int | None = None,
+                            signal_ptrs=(), arrivals_ptr: int = 0, lib: NativeB200Library | None = None) -> None:
+    """``y = silu(gate . x) * (up . x)`` for the same rows of a gate and an up matrix in one launch (the gate/up region)."""
+    lib = lib or library()
+    row_count = gate.rows - row_start if row_count is None else row_count
+    gather = _gather(peer_ptrs, signal_ptrs, arrivals_ptr)
+    lib.check(lib.raw.syn_b200_matmul_q8_swiglu_dev(gate.handle, up.handle, row_start, row_count, scratch_ptr, tokens, y_ptr, out_stride,
+                                                    gate_values_ptr or None, byref(gather) if gather is not None else None, stream))
+
+
+def gather_wait_device(signals_ptr: int, count: int, epoch_ptr: int, timeout_us: int = 1_000_000, stream: int = 0,
+                       lib: NativeB200Library | None = None) -> None:
+    """Queues the bounded wait for the next complete gathered vector (``syn_b200_gather_wait_dev``)."""
+    lib = lib or library()
+    lib.check(lib.raw.syn_b200_gather_wait_dev(signals_ptr, count, epoch_ptr, timeout_us, stream))
 
 
 def quantize_device(x_ptr: int, tokens: int, columns: int, in_stride: int, scratch_ptr: int, scratch_bytes: int, stream: int = 0,

@@ -38,12 +38,6 @@ int32_t cuda_fail(cudaError_t error, const char *what)
 
 void count_launch() { ++g_launches; }
 
-bool use_pdl()
-{
-    static const bool enabled = std::getenv("SYN_B200_NO_PDL") == nullptr;
-    return enabled;
-}
-
 namespace {
 uint32_t *g_fault_host = nullptr;
 uint32_t *g_fault_device = nullptr;
@@ -100,6 +94,43 @@ int sm_count(int device)
     return cached[device];
 }
 
+// Row range and token checks shared by every product (Q8MatrixKernel.cs:21-44).
+int32_t check_product(const syn_b200_matrix *m, uint64_t row_start, uint64_t row_count, uint64_t tokens,
+                      uint64_t out_stride, uint64_t *out_floats)
+{
+    if (row_count == 0 || row_start > m->rows || row_count > m->rows - row_start) {
+        return fail(SYN_B200_INVALID_ARGUMENT, "rows [" + std::to_string(row_start) + ", +" + std::to_string(row_count) +
+                                                   ") exceed matrix rows " + std::to_string(m->rows));
+    }
+    if (tokens == 0) {
+        return fail(SYN_B200_INVALID_ARGUMENT, "token count is zero");
+    }
+    if (tokens > 1 && out_stride < row_count) {
+        return fail(SYN_B200_INVALID_ARGUMENT, "output stride " + std::to_string(out_stride) + " is below the row count " +
+                                                   std::to_string(row_count));
+    }
+    uint64_t floats = 0;
+    if (__builtin_mul_overflow(tokens - 1, out_stride, &floats) || __builtin_add_overflow(floats, row_count, &floats) ||
+        floats > (UINT64_MAX >> 3)) {
+        return fail(SYN_B200_INVALID_ARGUMENT, "output size overflows");
+    }
+    if (out_floats) {
+        *out_floats = floats;
+    }
+    return SYN_B200_OK;
+}
+
+int32_t check_device(const syn_b200_matrix *m)
+{
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device != m->device) {
+        cudaGetLastError();
+        return fail(SYN_B200_INVALID_ARGUMENT, "the matrix lives on device " + std::to_string(m->device) +
+                                                   ", which is not the calling thread's current device");
+    }
+    return SYN_B200_OK;
+}
+
 namespace {
 
 // The library only carries sm_100a code: any other device cannot run it.
@@ -152,61 +183,10 @@ int32_t ensure_stage(syn_b200_matrix *m, uint64_t bytes)
     return SYN_B200_OK;
 }
 
-// Row range and token checks shared by every product (Q8MatrixKernel.cs:21-44).
-int32_t check_product(const syn_b200_matrix *m, uint64_t row_start, uint64_t row_count, uint64_t tokens,
-                      uint64_t out_stride, uint64_t *out_floats)
-{
-    if (row_count == 0 || row_start > m->rows || row_count > m->rows - row_start) {
-        return fail(SYN_B200_INVALID_ARGUMENT, "rows [" + std::to_string(row_start) + ", +" + std::to_string(row_count) +
-                                                   ") exceed matrix rows " + std::to_string(m->rows));
-    }
-    if (tokens == 0) {
-        return fail(SYN_B200_INVALID_ARGUMENT, "token count is zero");
-    }
-    if (tokens > 1 && out_stride < row_count) {
-        return fail(SYN_B200_INVALID_ARGUMENT, "output stride " + std::to_string(out_stride) + " is below the row count " +
-                                                   std::to_string(row_count));
-    }
-    uint64_t floats = 0;
-    if (!mul_ok(tokens - 1, out_stride, &floats) || __builtin_add_overflow(floats, row_count, &floats) ||
-        floats > (UINT64_MAX >> 3)) {
-        return fail(SYN_B200_INVALID_ARGUMENT, "output size overflows");
-    }
-    if (out_floats) {
-        *out_floats = floats;
-    }
-    return SYN_B200_OK;
-}
-
-int32_t check_device(const syn_b200_matrix *m)
-{
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device != m->device) {
-        cudaGetLastError();
-        return fail(SYN_B200_INVALID_ARGUMENT, "the matrix lives on device " + std::to_string(m->device) +
-                                                   ", which is not the calling thread's current device");
-    }
-    return SYN_B200_OK;
-}
-
-template <class Body>
-int32_t guarded(Body body)
-{
-    try {
-        return body();
-    } catch (const std::bad_alloc &) {
-        return fail(SYN_B200_INTERNAL, "host allocation failed");
-    } catch (const std::exception &e) {
-        return fail(SYN_B200_INTERNAL, e.what());
-    } catch (...) {
-        return fail(SYN_B200_INTERNAL, "unknown exception at the ABI");
-    }
-}
-
-int32_t create_matrix(const void *blocks, bool from_device, uint32_t type, uint64_t rows, uint64_t columns, uint32_t flags,
+int32_t create_matrix(const void *blocks_pointer, bool from_device, uint32_t type, uint64_t rows, uint64_t columns, uint32_t flags,
                       cudaStream_t stream, syn_b200_matrix **out)
 {
-    if (!blocks || !out) {
+    if (!blocks_pointer || !out) {
         return fail(SYN_B200_NULL_POINTER, "blocks or output handle");
     }
     *out = nullptr;
@@ -228,6 +208,16 @@ int32_t create_matrix(const void *blocks, bool from_device, uint32_t type, uint6
     if (!mul_ok(columns / values, block_bytes(type), &row_bytes) || !mul_ok(rows, row_bytes, &total) ||
         rows > (1ull << 31) || columns > (1ull << 31)) {
         return fail(SYN_B200_INVALID_ARGUMENT, "matrix size overflows");
+    }
+    const uint64_t blocks = rows * (columns / values);
+    const std::string type_name = type == kQ8_0 ? "q8_0" : type == kQ4_K ? "q4_k" : "q6_k";
+    if (!from_device) {
+        // The reference refuses a tensor whose blocks hold a non-finite fp16 scale before it decodes anything
+        // (BlockSourceDecoder.Decode, ModelPackages/SourceFormats/SourceTensorDecoders.cs:134-146,161-172).
+        const uint64_t bad = first_invalid_block_host(type, static_cast<const uint8_t *>(blocks_pointer), blocks);
+        if (bad != UINT64_MAX) {
+            return fail(SYN_B200_INVALID_ARGUMENT, type_name + " block " + std::to_string(bad) + " fails validation: InvalidScale");
+        }
     }
     int device = 0;
     int32_t status = require_device(&device);
@@ -251,7 +241,15 @@ int32_t create_matrix(const void *blocks, bool from_device, uint32_t type, uint6
         delete m;
         return cuda_fail(error, "allocating the weight buffer");
     }
-    error = cudaMemcpyAsync(natural, blocks, total, from_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, stream);
+    error = cudaMemcpyAsync(natural, blocks_pointer, total, from_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, stream);
+    uint64_t *first_bad = nullptr;
+    if (error == cudaSuccess && from_device) {
+        // blocks that never were in host memory are validated on the device, before the repack reads them
+        error = cudaMalloc(&first_bad, sizeof(uint64_t));
+        if (error == cudaSuccess) {
+            error = launch_validate_blocks(type, natural, blocks, first_bad, stream);
+        }
+    }
     if (error == cudaSuccess && repack) {
         m->data_bytes = planar_bytes(type, rows, columns, &m->planes);
         error = cudaMalloc(&m->data, m->data_bytes + 64);
@@ -267,16 +265,24 @@ int32_t create_matrix(const void *blocks, bool from_device, uint32_t type, uint6
     if (error == cudaSuccess) {
         error = cudaStreamSynchronize(stream);
     }
+    uint64_t bad = UINT64_MAX;
+    if (error == cudaSuccess && first_bad) {
+        error = cudaMemcpy(&bad, first_bad, sizeof(bad), cudaMemcpyDeviceToHost);
+    }
+    if (first_bad) {
+        cudaFree(first_bad);
+    }
     if (natural) {
         cudaFree(natural);
     }
-    if (error != cudaSuccess) {
+    if (error != cudaSuccess || bad != UINT64_MAX) {
         cudaGetLastError();
         if (m->data) {
             cudaFree(m->data);
         }
         delete m;
-        return cuda_fail(error, "uploading the weights");
+        return error != cudaSuccess ? cuda_fail(error, "uploading the weights")
+                                    : fail(SYN_B200_INVALID_ARGUMENT, type_name + " block " + std::to_string(bad) + " fails validation: InvalidScale");
     }
     *out = m;
     return SYN_B200_OK;
@@ -300,6 +306,44 @@ int32_t convert_epilogue(const syn_b200_epilogue *in, Epilogue &out)
     out.gate = in->gate;
     out.gate_stride = in->gate_stride;
     out.accumulate = in->accumulate;
+    return SYN_B200_OK;
+}
+
+// Peer copies of the output and the completion signal of a row-sharded product; null = a product on one GPU.
+int32_t convert_gather(const syn_b200_gather *in, Epilogue &out)
+{
+    out.peer_count = 0;
+    out.signal_count = 0;
+    out.arrivals = nullptr;
+    if (!in) {
+        return SYN_B200_OK;
+    }
+    if (in->peer_count > 7 || in->reserved != 0) {
+        return fail(SYN_B200_INVALID_ARGUMENT, "at most 7 peer outputs (got " + std::to_string(in->peer_count) + ") and the reserved field 0");
+    }
+    if (in->peer_count > 0 && !in->peer_outputs) {
+        return fail(SYN_B200_NULL_POINTER, "peer outputs");
+    }
+    for (uint32_t i = 0; i < in->peer_count; ++i) {
+        if (!in->peer_outputs[i]) {
+            return fail(SYN_B200_NULL_POINTER, "peer output " + std::to_string(i));
+        }
+        out.peers[i] = in->peer_outputs[i];
+    }
+    out.peer_count = in->peer_count;
+    if (in->signals) {
+        if (!in->arrivals) {
+            return fail(SYN_B200_NULL_POINTER, "a completion signal needs the two local arrival words");
+        }
+        for (uint32_t i = 0; i <= in->peer_count; ++i) {
+            if (!in->signals[i] || (reinterpret_cast<uintptr_t>(in->signals[i]) & 3)) {
+                return fail(SYN_B200_NULL_POINTER, "signal word " + std::to_string(i));
+            }
+            out.signals[i] = in->signals[i];
+        }
+        out.signal_count = in->peer_count + 1;
+        out.arrivals = in->arrivals;
+    }
     return SYN_B200_OK;
 }
 
@@ -757,31 +801,21 @@ int32_t syn_b200_enable_peer_access(int32_t peer_device)
 }
 
 int32_t syn_b200_matmul_q8_gather_dev(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count, const void *scratch,
-                                      uint64_t tokens, float *y, uint64_t out_stride, float *const *peer_outputs, uint32_t peer_count,
-                                      void *stream)
+                                      uint64_t tokens, float *y, uint64_t out_stride, const syn_b200_gather *gather, void *stream)
 {
-    if (!matrix || !scratch || !y || (peer_count > 0 && !peer_outputs)) {
-        return fail(SYN_B200_NULL_POINTER, "matrix, scratch, output or peer outputs");
+    if (!matrix || !scratch || !y) {
+        return fail(SYN_B200_NULL_POINTER, "matrix, scratch or output");
     }
     return guarded([&]() -> int32_t {
         int32_t status = check_product(matrix, row_start, row_count, tokens, out_stride, nullptr);
         if (status == SYN_B200_OK) status = check_device(matrix);
+        Epilogue fused;
+        if (status == SYN_B200_OK) status = convert_gather(gather, fused);
         if (status != SYN_B200_OK) {
             return status;
         }
-        if (peer_count > 7) {
-            return fail(SYN_B200_INVALID_ARGUMENT, "at most 7 peer outputs, got " + std::to_string(peer_count));
-        }
         if (reinterpret_cast<uintptr_t>(scratch) & 255) {
             return fail(SYN_B200_INVALID_ARGUMENT, "activation scratch must be 256-byte aligned");
-        }
-        Epilogue fused;
-        fused.peer_count = peer_count;
-        for (uint32_t i = 0; i < peer_count; ++i) {
-            if (!peer_outputs[i]) {
-                return fail(SYN_B200_NULL_POINTER, "peer output " + std::to_string(i));
-            }
-            fused.peers[i] = peer_outputs[i];
         }
         MatvecArgs args{};
         args.matrix = matrix;
@@ -796,6 +830,181 @@ int32_t syn_b200_matmul_q8_gather_dev(const syn_b200_matrix *matrix, uint64_t ro
         args.epilogue = SYN_B200_EPILOGUE_STORE;
         args.fused = fused;
         cudaError_t error = launch_matvec(args, static_cast<cudaStream_t>(stream));
+        return error == cudaSuccess ? SYN_B200_OK : cuda_fail(error, "launching the matrix-vector kernel");
+    });
+}
+
+int32_t syn_b200_gather_wait_dev(const uint32_t *signals, uint32_t count, uint32_t *epoch, uint32_t timeout_us, void *stream)
+{
+    if (!signals || !epoch) {
+        return fail(SYN_B200_NULL_POINTER, "signal array or epoch word");
+    }
+    return guarded([&]() -> int32_t {
+        if (count == 0 || count > 8 || timeout_us == 0) {
+            return fail(SYN_B200_INVALID_ARGUMENT, "a signal array holds 1 to 8 words and the wait needs a positive limit");
+        }
+        int32_t status = require_device(nullptr);
+        if (status != SYN_B200_OK) {
+            return status;
+        }
+        cudaError_t error = launch_gather_wait(signals, count, epoch, timeout_us, static_cast<cudaStream_t>(stream));
+        return error == cudaSuccess ? SYN_B200_OK : cuda_fail(error, "launching the completion wait");
+    });
+}
+
+int32_t syn_b200_matmul_q8_segments_dev(const syn_b200_segment *segments, uint32_t count, const void *scratch, uint64_t tokens, float *y,
+                                        uint64_t out_stride, uint32_t accumulate, const syn_b200_gather *gather, void *stream)
+{
+    if (!segments || !scratch || !y) {
+        return fail(SYN_B200_NULL_POINTER, "segments, scratch or output");
+    }
+    return guarded([&]() -> int32_t {
+        if (count == 0 || count > 3) {
+            return fail(SYN_B200_INVALID_ARGUMENT, "a product takes 1 to 3 segments, got " + std::to_string(count));
+        }
+        if (accumulate > 1) {
+            return fail(SYN_B200_INVALID_ARGUMENT, "accumulate must be 0 or 1");
+        }
+        if (reinterpret_cast<uintptr_t>(scratch) & 255) {
+            return fail(SYN_B200_INVALID_ARGUMENT, "activation scratch must be 256-byte aligned");
+        }
+        MatvecArgs args{};
+        uint64_t total_rows = 0;
+        for (uint32_t i = 0; i < count; ++i) {
+            const syn_b200_segment &segment = segments[i];
+            if (!segment.matrix) {
+                return fail(SYN_B200_NULL_POINTER, "matrix of segment " + std::to_string(i));
+            }
+            const syn_b200_matrix *first = segments[0].matrix;
+            if (segment.matrix->type != first->type || segment.matrix->layout != first->layout || segment.matrix->columns != first->columns) {
+                // the reference shares a dispatch only between projections of one encoding (step/layers.rs:71-94)
+                return fail(SYN_B200_INVALID_ARGUMENT, "the segments of one product must share encoding, layout and width");
+            }
+            uint64_t end = 0;
+            if (__builtin_add_overflow(segment.out_column, segment.row_count, &end) || (tokens > 1 && end > out_stride)) {
+                return fail(SYN_B200_INVALID_ARGUMENT, "segment " + std::to_string(i) + " does not fit the output stride");
+            }
+            int32_t status = check_product(segment.matrix, segment.row_start, segment.row_count, tokens, out_stride, nullptr);
+            if (status == SYN_B200_OK) status = check_device(segment.matrix);
+            if (status != SYN_B200_OK) {
+                return status;
+            }
+            args.segments[i].matrix = segment.matrix;
+            args.segments[i].row_start = segment.row_start;
+            args.segments[i].row_count = segment.row_count;
+            args.segments[i].bias = segment.bias;
+            args.segments[i].out_column = segment.out_column;
+            total_rows += segment.row_count;
+        }
+        Epilogue fused;
+        if (int32_t status = convert_gather(gather, fused)) {
+            return status;
+        }
+        fused.accumulate = accumulate;
+        const uint32_t peer_count = fused.peer_count;
+        const syn_b200_matrix *m = segments[0].matrix;
+        args.form = 1;
+        args.segment_count = count;
+        args.matrix = m;
+        args.row_start = segments[0].row_start;
+        args.row_count = total_rows;
+        args.tokens = tokens;
+        args.act = act_view(scratch, tokens, m->columns);
+        args.act_ready = true;
+        args.y = y;
+        args.out_stride = out_stride;
+        args.mode = SYN_B200_MODE_XQ8;
+        args.epilogue = SYN_B200_EPILOGUE_STORE;
+        args.fused = fused;
+        cudaError_t error = count > 1 ? launch_matvec(args, static_cast<cudaStream_t>(stream)) : cudaErrorNotSupported;
+        if (error == cudaErrorNotSupported) {
+            // shapes the one-launch form does not take (several tokens, rows longer than one pass of a team): one
+            // launch per segment, same results
+            error = cudaSuccess;
+            for (uint32_t i = 0; i < count && error == cudaSuccess; ++i) {
+                MatvecArgs one = args;
+                one.form = 0;
+                one.matrix = args.segments[i].matrix;
+                one.row_start = args.segments[i].row_start;
+                one.row_count = args.segments[i].row_count;
+                one.y = y + args.segments[i].out_column;
+                one.fused.bias = args.segments[i].bias;
+                for (uint32_t k = 0; k < peer_count; ++k) {
+                    one.fused.peers[k] = fused.peers[k] + args.segments[i].out_column;
+                }
+                if (i + 1 < count) {
+                    one.fused.signal_count = 0;  // the launches are stream-ordered: the last one signals for all of them
+                }
+                error = launch_matvec(one, static_cast<cudaStream_t>(stream));
+            }
+        }
+        return error == cudaSuccess ? SYN_B200_OK : cuda_fail(error, "launching the matrix-vector kernel");
+    });
+}
+
+int32_t syn_b200_matmul_q8_swiglu_dev(const syn_b200_matrix *gate, const syn_b200_matrix *up, uint64_t row_start, uint64_t row_count,
+                                      const void *scratch, uint64_t tokens, float *y, uint64_t out_stride, float *gate_values,
+                                      const syn_b200_gather *gather, void *stream)
+{
+    if (!gate || !up || !scratch || !y) {
+        return fail(SYN_B200_NULL_POINTER, "gate, up, scratch or output");
+    }
+    return guarded([&]() -> int32_t {
+        if (gate->type != up->type || gate->layout != up->layout || gate->columns != up->columns || gate->rows != up->rows) {
+            return fail(SYN_B200_INVALID_ARGUMENT, "the gate and up matrices must share encoding, layout and shape");
+        }
+        int32_t status = check_product(gate, row_start, row_count, tokens, out_stride, nullptr);
+        if (status == SYN_B200_OK) status = check_device(gate);
+        if (status == SYN_B200_OK) status = check_device(up);
+        if (status != SYN_B200_OK) {
+            return status;
+        }
+        if (reinterpret_cast<uintptr_t>(scratch) & 255) {
+            return fail(SYN_B200_INVALID_ARGUMENT, "activation scratch must be 256-byte aligned");
+        }
+        Epilogue fused;
+        status = convert_gather(gather, fused);
+        if (status != SYN_B200_OK) {
+            return status;
+        }
+        MatvecArgs args{};
+        args.form = 2;
+        args.segment_count = 2;
+        args.segments[0].matrix = gate;
+        args.segments[1].matrix = up;
+        args.segments[0].row_start = args.segments[1].row_start = row_start;
+        args.segments[0].row_count = args.segments[1].row_count = row_count;
+        args.matrix = gate;
+        args.row_start = row_start;
+        args.row_count = row_count;
+        args.tokens = tokens;
+        args.act = act_view(scratch, tokens, gate->columns);
+        args.act_ready = true;
+        args.y = y;
+        args.out_stride = out_stride;
+        args.mode = SYN_B200_MODE_XQ8;
+        args.epilogue = SYN_B200_EPILOGUE_STORE;
+        args.fused = fused;
+        cudaError_t error = launch_matvec(args, static_cast<cudaStream_t>(stream));
+        if (error == cudaErrorNotSupported) {
+            // several tokens, or rows longer than one pass of a team: the gate projection goes to memory after all
+            if (!gate_values) {
+                return fail(SYN_B200_INVALID_ARGUMENT, "this shape runs as two launches and needs gate_values (tokens x out_stride floats)");
+            }
+            MatvecArgs one = args;
+            one.form = 0;
+            one.fused = Epilogue{};
+            one.y = gate_values;
+            error = launch_matvec(one, static_cast<cudaStream_t>(stream));
+            if (error == cudaSuccess) {
+                one.matrix = up;
+                one.y = y;
+                one.fused = fused;
+                one.fused.gate = gate_values;
+                one.fused.gate_stride = out_stride;
+                error = launch_matvec(one, static_cast<cudaStream_t>(stream));
+            }
+        }
         return error == cudaSuccess ? SYN_B200_OK : cuda_fail(error, "launching the matrix-vector kernel");
     });
 }

@@ -6,6 +6,8 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <exception>
+#include <new>
 #include <string>
 
 #include "../../include/synapse_b200.h"
@@ -89,13 +91,33 @@ struct Error {
 // Records the message for syn_b200_last_error and returns the status.
 int32_t fail(int32_t status, const std::string &message);
 int32_t cuda_fail(cudaError_t error, const char *what);
+// Row range, token count and output size checks shared by every product (Q8MatrixKernel.cs:21-44); `out_floats`
+// (optional) receives the floats the output spans.
+int32_t check_product(const syn_b200_matrix *m, uint64_t row_start, uint64_t row_count, uint64_t tokens, uint64_t out_stride,
+                      uint64_t *out_floats);
+// The matrix must live on the calling thread's current device.
+int32_t check_device(const syn_b200_matrix *m);
+// Runs `body` and turns any C++ exception into SYN_B200_INTERNAL: nothing is thrown across the ABI (the reference's
+// catch_unwind, native/synapse-gpu/src/Features/GpuKernels/ffi.rs:18-44).
+template <class Body>
+int32_t guarded(Body body)
+{
+    try {
+        return body();
+    } catch (const std::bad_alloc &) {
+        return fail(SYN_B200_INTERNAL, "host allocation failed");
+    } catch (const std::exception &e) {
+        return fail(SYN_B200_INTERNAL, e.what());
+    } catch (...) {
+        return fail(SYN_B200_INTERNAL, "unknown exception at the ABI");
+    }
+}
 void count_launch();
 int sm_count(int device);
-// True unless SYN_B200_NO_PDL is set: kernels are launched with programmatic stream serialization, so a kernel's
-// prologue and first weight copies overlap the tail of the kernel before it.
-bool use_pdl();
 
-// Launches `kernel` on `stream`, with the programmatic-dependent-launch attribute when enabled.
+// Launches `kernel` on `stream` with programmatic stream serialization: its prologue and first weight copies overlap
+// the tail of the kernel before it. Every kernel launched this way executes griddepcontrol.wait before it reads
+// anything an earlier kernel wrote, and before its first global write.
 template <class... Params, class... Args>
 cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream, Args... args)
 {
@@ -108,7 +130,7 @@ cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = use_pdl() ? 1 : 0;
+    config.numAttrs = 1;
     count_launch();
     return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
@@ -126,6 +148,11 @@ uint64_t planar_bytes(uint32_t type, uint64_t rows, uint64_t columns, PlaneOffse
 cudaError_t launch_repack(uint32_t type, const uint8_t *natural, uint64_t rows, uint64_t columns, uint8_t *planar,
                           const PlaneOffsets &planes, cudaStream_t stream);
 
+// Index of the first block with a non-finite fp16 scale field, or UINT64_MAX (host scan of host blocks; the device
+// variant writes the index, or UINT64_MAX, to `first_bad_device`).
+uint64_t first_invalid_block_host(uint32_t type, const uint8_t *data, uint64_t blocks);
+cudaError_t launch_validate_blocks(uint32_t type, const uint8_t *data, uint64_t blocks, uint64_t *first_bad_device, cudaStream_t stream);
+
 // What happens to a finished dot product before it is stored (the fused regions of the reference's CPU executor,
 // Qwen2/Qwen2ProjectionWork.cs:7-131, and `accumulate` of cuda/kernels/common.cuh:52-69):
 //   v = dot (+ bias[row]);  v = silu(gate[token][row]) * v when gate is set;  y = accumulate ? y + v : v
@@ -138,10 +165,36 @@ struct Epilogue {
     // of the output, peer-mapped), so the gather of the slices happens inside the product.
     uint32_t peer_count = 0;
     float *peers[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    // Completion signal of a row-sharded product: the last CTA of the launch to finish its stores writes the launch's
+    // sequence number into signals[0..signal_count): this rank's word of the product's signal array in its own memory
+    // and in every peer's. arrivals[0] counts the CTAs of the running launch, arrivals[1] the launches (both local).
+    uint32_t signal_count = 0;
+    uint32_t *signals[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    uint32_t *arrivals = nullptr;
 };
+
+// One of up to three row ranges that a single launch multiplies with the same activations (MatmulSegment of the
+// reference, native/synapse-gpu/src/Features/GpuKernels/params.rs:42-61): results of row r of the range go to
+// y[token * out_stride + out_column + r], with bias[r] added when a bias is given.
+struct MatvecSegment {
+    const syn_b200_matrix *matrix = nullptr;
+    uint64_t row_start = 0, row_count = 0;
+    const float *bias = nullptr;
+    uint64_t out_column = 0;
+};
+
+// Waits (bounded) until every word of a signal array has reached the next sequence number; see syn_b200_gather_wait_dev.
+cudaError_t launch_gather_wait(const uint32_t *signals, uint32_t count, uint32_t *epoch, uint32_t timeout_us, cudaStream_t stream);
 
 // matvec.cu
 struct MatvecArgs {
+    // What the launch multiplies: 0 one row range of `matrix`; 1 the row ranges in `segments` (same encoding, layout and
+    // width; `matrix` = segments[0].matrix, row_count = all rows together); 2 rows [row_start, +row_count) of
+    // segments[0] (gate) and segments[1] (up) with y = silu(gate . x) * (up . x). Forms 1 and 2 are single-token
+    // products on ready-made activations; launch_matvec returns cudaErrorNotSupported for shapes they do not take.
+    uint32_t form = 0;
+    uint32_t segment_count = 0;
+    MatvecSegment segments[3];
     const syn_b200_matrix *matrix;
     uint64_t row_start, row_count;
     uint64_t tokens;

@@ -415,14 +415,16 @@ __device__ __noinline__ Ring consume_matvec(const Op *op, const Params &P, Share
             for (int j = 0; j < UPL; ++j) {
                 F::template load_w<SharedMem>(view, K, team_in_cta, u[j], lane, wr[j]);
             }
-            // every unit of this warp is in registers: give the stage back to the producer
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(empty0 + 8 * pair);
-            }
 #pragma unroll
             for (int j = 0; j < UPL; ++j) {
                 F::template dot<false>(wr[j], held[j], valid[j], u[j], lane, acc, nullptr);
+            }
+            // Every unit of this warp has been consumed: give the stage back to the producer. The refill is written by the
+            // asynchronous proxy, the loads above went through the generic one: the proxy fence orders them.
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(empty0 + 8 * pair);
             }
         } else if (lane == 0) {
             mbar_arrive(empty0 + 8 * pair);

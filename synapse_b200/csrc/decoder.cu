@@ -394,22 +394,68 @@ cudaError_t enqueue_step(syn_b200_decoder *d, uint32_t count, uint32_t logits_ro
     for (uint32_t l = 0; l < s.layer_count; ++l) {
         const Layer &L = d->layers[l];
         SYN_TRY(norm_quantize(d, d->hidden, L.attention_norm, count, count, false, d->act_hidden));
-        // q | k | v read the same activations and write disjoint outputs: k and v fork onto side streams (parallel
+        // q | k | v read the same activations and write disjoint outputs. Matrices of one encoding share a launch (the
+        // reference's three-segment dispatch, step/layers.rs:71-94); the others fork onto side streams (parallel
         // branches of the captured graph) and join before the rotation.
-        SYN_TRY(cudaEventRecord(d->fork, d->stream));
-        Epilogue bias;
-        bias.bias = L.key_bias;
-        SYN_TRY(cudaStreamWaitEvent(d->side[0], d->fork, 0));
-        SYN_TRY(product(d, L.key, d->act_hidden, count, d->k, kvw, bias, d->side[0]));
-        SYN_TRY(cudaEventRecord(d->join[0], d->side[0]));
-        bias.bias = L.value_bias;
-        SYN_TRY(cudaStreamWaitEvent(d->side[1], d->fork, 0));
-        SYN_TRY(product(d, L.value, d->act_hidden, count, d->v, kvw, bias, d->side[1]));
-        SYN_TRY(cudaEventRecord(d->join[1], d->side[1]));
-        bias.bias = L.query_bias;
-        SYN_TRY(product(d, L.query, d->act_hidden, count, d->q, hidden, bias));
-        SYN_TRY(cudaStreamWaitEvent(d->stream, d->join[0], 0));
-        SYN_TRY(cudaStreamWaitEvent(d->stream, d->join[1], 0));
+        {
+            const syn_b200_matrix *members[3] = {L.query, L.key, L.value};
+            float *outputs[3] = {d->q, d->k, d->v};
+            const float *biases[3] = {L.query_bias, L.key_bias, L.value_bias};
+            const uint64_t strides[3] = {hidden, kvw, kvw};
+            bool done[3] = {false, false, false};
+            if (count == 1) {
+                // one token: q, k and v are three vectors of one buffer only by convention; out_column is relative to d->q
+                MatvecArgs args{};
+                args.form = 1;
+                for (int i = 0; i < 3; ++i) {
+                    if (members[i]->type == L.query->type && members[i]->layout == L.query->layout) {
+                        MatvecSegment &segment = args.segments[args.segment_count++];
+                        segment.matrix = members[i];
+                        segment.row_count = members[i]->rows;
+                        segment.bias = biases[i];
+                        segment.out_column = (uint64_t)(outputs[i] - d->q);
+                        args.row_count += members[i]->rows;
+                        done[i] = true;
+                    }
+                }
+                cudaError_t error = cudaErrorNotSupported;
+                if (args.segment_count > 1) {
+                    args.matrix = L.query;
+                    args.tokens = 1;
+                    args.act = act_view(d->act_hidden, 1, hidden);
+                    args.act_ready = true;
+                    args.y = d->q;
+                    args.out_stride = hidden;
+                    args.mode = SYN_B200_MODE_XQ8;
+                    error = launch_matvec(args, d->stream);
+                }
+                if (error == cudaErrorNotSupported) {
+                    done[0] = done[1] = done[2] = false;
+                } else if (error != cudaSuccess) {
+                    return error;
+                }
+            }
+            int branch = 0;
+            SYN_TRY(cudaEventRecord(d->fork, d->stream));
+            for (int i = 1; i < 3; ++i) {
+                if (!done[i]) {
+                    Epilogue bias;
+                    bias.bias = biases[i];
+                    SYN_TRY(cudaStreamWaitEvent(d->side[branch], d->fork, 0));
+                    SYN_TRY(product(d, members[i], d->act_hidden, count, outputs[i], strides[i], bias, d->side[branch]));
+                    SYN_TRY(cudaEventRecord(d->join[branch], d->side[branch]));
+                    ++branch;
+                }
+            }
+            if (!done[0]) {
+                Epilogue bias;
+                bias.bias = biases[0];
+                SYN_TRY(product(d, members[0], d->act_hidden, count, outputs[0], strides[0], bias));
+            }
+            for (int i = 0; i < branch; ++i) {
+                SYN_TRY(cudaStreamWaitEvent(d->stream, d->join[i], 0));
+            }
+        }
         SYN_TRY(launch_kernel(rope_store_kernel, dim3(s.heads + s.kv_heads, count), dim3(s.head_dim / 2), 0, d->stream,
                               (const BatchToken *)d->device_tokens, d->q, d->k, (const float *)d->v, (const float *)d->cosines,
                               (const float *)d->sines, d->keys, d->values, s.heads, s.kv_heads, s.head_dim, l, s.layer_count, s.context));
@@ -426,11 +472,37 @@ cudaError_t enqueue_step(syn_b200_decoder *d, uint32_t count, uint32_t logits_ro
         residual.accumulate = 1;
         SYN_TRY(product(d, L.output, d->act_hidden, count, d->hidden, hidden, residual));
         SYN_TRY(norm_quantize(d, d->hidden, L.feed_forward_norm, count, count, false, d->act_hidden));
-        SYN_TRY(product(d, L.gate, d->act_hidden, count, d->gate, ffn, Epilogue{}));
-        Epilogue swiglu;
-        swiglu.gate = d->gate;
-        swiglu.gate_stride = ffn;
-        SYN_TRY(product(d, L.up, d->act_hidden, count, d->ff, ffn, swiglu));
+        {
+            // gate | up: one launch whose warps hold gate row r and up row r and apply SwiGLU in registers (single-token
+            // steps of matching encodings); otherwise the gate values go through memory into the up product's epilogue
+            cudaError_t error = cudaErrorNotSupported;
+            if (count == 1 && L.gate->type == L.up->type && L.gate->layout == L.up->layout) {
+                MatvecArgs args{};
+                args.form = 2;
+                args.segment_count = 2;
+                args.segments[0].matrix = L.gate;
+                args.segments[1].matrix = L.up;
+                args.segments[0].row_count = args.segments[1].row_count = ffn;
+                args.matrix = L.gate;
+                args.row_count = ffn;
+                args.tokens = 1;
+                args.act = act_view(d->act_hidden, 1, hidden);
+                args.act_ready = true;
+                args.y = d->ff;
+                args.out_stride = ffn;
+                args.mode = SYN_B200_MODE_XQ8;
+                error = launch_matvec(args, d->stream);
+            }
+            if (error == cudaErrorNotSupported) {
+                SYN_TRY(product(d, L.gate, d->act_hidden, count, d->gate, ffn, Epilogue{}));
+                Epilogue swiglu;
+                swiglu.gate = d->gate;
+                swiglu.gate_stride = ffn;
+                SYN_TRY(product(d, L.up, d->act_hidden, count, d->ff, ffn, swiglu));
+            } else if (error != cudaSuccess) {
+                return error;
+            }
+        }
         SYN_TRY(quantize(d, d->ff, count, ffn, d->act_ffn));
         SYN_TRY(product(d, L.down, d->act_ffn, count, d->hidden, hidden, residual));
     }
@@ -638,13 +710,7 @@ cudaError_t build_program(syn_b200_decoder *d)
     if (largest == 0 || act_bytes + 2 * (uint64_t)largest > kDynamicSharedBudget) {
         return cudaSuccess;
     }
-    uint32_t ring_bytes = (kDynamicSharedBudget - act_bytes) / 128 * 128;
-    if (const char *limit = getenv("SYN_B200_PROGRAM_RING_KB")) {  // tuning aid: a smaller ring
-        const uint32_t wanted = (uint32_t)atoi(limit) * 1024;
-        if (wanted >= 2 * largest && wanted < ring_bytes) {
-            ring_bytes = wanted;
-        }
-    }
+    const uint32_t ring_bytes = (kDynamicSharedBudget - act_bytes) / 128 * 128;
     const uint32_t dynamic = act_bytes + ring_bytes;
     cudaError_t error = cudaFuncSetAttribute(decode_program_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dynamic);
     int resident = 0;
@@ -982,9 +1048,12 @@ int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_deco
         status = device_alloc(d, &d->cosines, (uint64_t)s.context * half);
         if (status == SYN_B200_OK) status = device_alloc(d, &d->sines, (uint64_t)s.context * half);
         if (status == SYN_B200_OK) status = device_alloc(d, &d->hidden, T * s.hidden);
-        if (status == SYN_B200_OK) status = device_alloc(d, &d->q, T * s.hidden);
-        if (status == SYN_B200_OK) status = device_alloc(d, &d->k, T * kvw);
-        if (status == SYN_B200_OK) status = device_alloc(d, &d->v, T * kvw);
+        // q, k and v live in one block, in this order: a launch that computes all three addresses k and v relative to q
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->q, T * (s.hidden + 2ull * kvw));
+        if (status == SYN_B200_OK) {
+            d->k = d->q + T * s.hidden;
+            d->v = d->k + T * kvw;
+        }
         if (status == SYN_B200_OK) status = device_alloc(d, &d->attention, T * s.hidden);
         if (status == SYN_B200_OK) status = device_alloc(d, &d->gate, T * s.feed_forward);
         if (status == SYN_B200_OK) status = device_alloc(d, &d->ff, T * s.feed_forward);

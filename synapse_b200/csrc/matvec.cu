@@ -8,9 +8,9 @@
 namespace syn {
 namespace mv {
 
-cudaError_t launch_xq8_q8_0(const MatvecArgs &a, const WeightView &view, cudaStream_t stream);
-cudaError_t launch_xq8_q4_k(const MatvecArgs &a, const WeightView &view, cudaStream_t stream);
-cudaError_t launch_xq8_q6_k(const MatvecArgs &a, const WeightView &view, cudaStream_t stream);
+cudaError_t launch_xq8_q8_0(const MatvecArgs &a, const WeightView *views, cudaStream_t stream);
+cudaError_t launch_xq8_q4_k(const MatvecArgs &a, const WeightView *views, cudaStream_t stream);
+cudaError_t launch_xq8_q6_k(const MatvecArgs &a, const WeightView *views, cudaStream_t stream);
 
 namespace {
 
@@ -73,10 +73,18 @@ struct Q8NaturalXf32 {
     }
 };
 
+// Q4_K in its file layout, unit = one 32-byte nibble chunk: sub-blocks 2p (low nibbles) and 2p+1 (high nibbles) of
+// super-block u/4, p = u%4.
 struct Q4KXf32 {
-    using W = Q4KPairXq8::W;
+    struct W { uint4 hdr, q0, q1; };
     static __device__ __forceinline__ uint64_t units(uint64_t K) { return K / 64; }
-    static __device__ __forceinline__ void load_w(const WeightView &w, uint64_t K, uint64_t row, uint64_t u, W &out) { Q4KPairXq8::load_w<GlobalMem>(w, K, row, u, 0, out); }
+    static __device__ __forceinline__ void load_w(const WeightView &w, uint64_t, uint64_t row, uint64_t u, W &out)
+    {
+        const uint8_t *block = w.p0 + row * w.row_bytes + (u >> 2) * 144;
+        out.hdr = ld_cached(block);
+        out.q0 = ld_stream(block + 16 + (u & 3) * 32);
+        out.q1 = ld_stream(block + 32 + (u & 3) * 32);
+    }
     static __device__ __forceinline__ void dot(const W &w, const float *x, uint64_t u, float &acc)
     {
         const float *xu = x + u * 64;
@@ -247,10 +255,16 @@ cudaError_t launch_matvec(const MatvecArgs &args, cudaStream_t stream)
     const syn_b200_matrix *m = a.matrix;
     const bool planar = m->layout == Layout::Planar;
     if (a.dump || a.mode == SYN_B200_MODE_XQ8) {
-        const WeightView view = view_of(m, a.row_start);
-        return m->type == kQ8_0 ? launch_xq8_q8_0(a, view, stream)
-               : m->type == kQ4_K ? launch_xq8_q4_k(a, view, stream)
-                                  : launch_xq8_q6_k(a, view, stream);
+        WeightView views[3] = {view_of(m, a.row_start), WeightView{}, WeightView{}};
+        for (uint32_t i = 0; a.form != 0 && i < a.segment_count && i < 3; ++i) {
+            views[i] = view_of(a.segments[i].matrix, a.segments[i].row_start);
+        }
+        return m->type == kQ8_0 ? launch_xq8_q8_0(a, views, stream)
+               : m->type == kQ4_K ? launch_xq8_q4_k(a, views, stream)
+                                  : launch_xq8_q6_k(a, views, stream);
+    }
+    if (a.form != 0) {
+        return cudaErrorNotSupported;
     }
     if (m->type == kQ8_0) {
         return planar ? dispatch_xf32<Q8PlanarXf32>(a, stream) : dispatch_xf32<Q8NaturalXf32>(a, stream);

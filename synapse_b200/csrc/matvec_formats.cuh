@@ -20,13 +20,7 @@
 namespace syn {
 namespace mv {
 
-#ifndef SYN_MV_WARPS
-#define SYN_MV_WARPS 8
-#endif
-constexpr int kWarps = SYN_MV_WARPS;  // most consumer warps a CTA runs
-#ifndef SYN_DEFAULT_CTAS
-#define SYN_DEFAULT_CTAS 2
-#endif
+constexpr int kWarps = 8;  // consumer warps of the ordinary CTA
 constexpr unsigned kFull = 0xffffffffu;
 
 __device__ __forceinline__ uint4 ld_stream(const void *p)
@@ -218,6 +212,31 @@ __device__ __forceinline__ void store_result(const Epilogue &e, float *__restric
     }
 }
 
+// Called by ONE thread of every CTA of a row-sharded product after a CTA barrier behind the CTA's last store. The
+// thread publishes the CTA's stores (its own and, through the barrier, its CTA's; the fence is cumulative) and counts the
+// CTA in; the thread that counts the last CTA of the grid in has thereby observed every other CTA's count, so after one
+// more fence its writes of the launch's sequence number to the signal words are ordered behind ALL stores of the launch,
+// at system scope: whoever acquires a signal word sees the whole slice.
+__device__ __forceinline__ void signal_completion(const Epilogue &e)
+{
+    if (e.signal_count == 0) {
+        return;
+    }
+    __threadfence_system();
+    const uint32_t total = gridDim.x * gridDim.y;
+    if (atomicAdd(e.arrivals, 1u) + 1 == total) {
+        atomicExch(e.arrivals, 0u);  // ready for the next launch (launches that share these words are stream-ordered)
+        const uint32_t sequence = atomicAdd(e.arrivals + 1, 1u) + 1;
+        __threadfence_system();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if ((uint32_t)i < e.signal_count) {
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(e.signals[i]), "r"(sequence) : "memory");
+            }
+        }
+    }
+}
+
 __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
 // Exact integer-to-float conversions on the FMA pipe (a PRMT or IADD plus one FADD) instead of I2F, which runs on the
@@ -254,7 +273,7 @@ struct Q8PlanarXq8 {
     static constexpr int kPlanes = 2;
     static constexpr bool kStageTokens = false;  // several tokens: 16-weight units make the staged kernel load-bound; the direct kernels are faster
     static void plane_row_bytes(uint64_t K, uint64_t, uint32_t *out) { out[0] = (uint32_t)K; out[1] = (uint32_t)(K / 16); }
-    static constexpr int kMaxUpl = 2, kRows = 2, kCtasPerSm = SYN_DEFAULT_CTAS;
+    static constexpr int kMaxUpl = 2, kRows = 2, kCtasPerSm = 2;
     static constexpr int min_ctas(int) { return 2; }
     static constexpr int ctas_per_sm(int) { return kCtasPerSm; }
     static __device__ __forceinline__ uint64_t units(uint64_t K) { return K / 16; }
@@ -297,7 +316,7 @@ struct Q8NaturalXq8 {
     struct W { uint4 c0, c1; float d; };
     static constexpr int kPlanes = 1;
     static constexpr bool kStageTokens = false;  // as the planar layout
-    static constexpr int kMaxUpl = 2, kRows = 2, kCtasPerSm = SYN_DEFAULT_CTAS;
+    static constexpr int kMaxUpl = 2, kRows = 2, kCtasPerSm = 2;
     static constexpr int min_ctas(int) { return 2; }
     static constexpr int ctas_per_sm(int) { return kCtasPerSm; }
     static void plane_row_bytes(uint64_t, uint64_t row_bytes, uint32_t *out) { out[0] = (uint32_t)row_bytes; }
@@ -335,27 +354,6 @@ struct Q8NaturalXq8 {
     }
 };
 
-// Q4_K in its file layout, unit = one 32-byte nibble chunk: sub-blocks 2p (low nibbles) and 2p+1 (high nibbles) of
-// super-block u/4, p = u%4. Only its weight loader is still used (by the FP32-activation kernel).
-struct Q4KPairXq8 {
-    struct Act { uint4 c[4]; float d0, d1; int s0, s1; };
-    struct W { uint4 hdr, q0, q1; };
-    static constexpr int kPlanes = 1;
-    static void plane_row_bytes(uint64_t, uint64_t row_bytes, uint32_t *out) { out[0] = (uint32_t)row_bytes; }
-    static __device__ __forceinline__ uint64_t units(uint64_t K) { return K / 64; }
-    template <class M>
-    static __device__ __forceinline__ void load_w(const typename M::View &w, uint64_t K_, uint64_t row_, uint64_t u_, uint32_t, W &out)
-    {
-        using I = typename M::index;
-        const I K = (I)K_, row = (I)row_, u = (I)u_;
-        (void)K;
-        const typename M::pointer block = w.p0 + row * w.row_bytes + (u >> 2) * 144;
-        out.hdr = M::v4c(block);
-        out.q0 = M::v4(block + 16 + (u & 3) * 32);
-        out.q1 = M::v4(block + 32 + (u & 3) * 32);
-    }
-};
-
 __device__ __forceinline__ int dp4a_us(uint32_t a_unsigned, uint32_t b_signed, int c)
 {
     int d;
@@ -375,17 +373,9 @@ struct Q4KXq8 {
     struct W { uint4 hdr, q[4]; };
     static constexpr int kPlanes = 1;
     static constexpr bool kStageTokens = true;  // several tokens: their activations are staged in shared memory beside the weight ring
-#ifndef SYN_Q4K_ROWS
-#define SYN_Q4K_ROWS 2
-#endif
-#ifndef SYN_Q4K_CTAS
-#define SYN_Q4K_CTAS 1
-#endif
-#ifndef SYN_Q4K_MINCTAS
-#define SYN_Q4K_MINCTAS 2
-#endif
-    static constexpr int kMaxUpl = 1, kRows = SYN_Q4K_ROWS, kCtasPerSm = SYN_Q4K_CTAS;
-    static constexpr int min_ctas(int) { return SYN_Q4K_MINCTAS; }
+    // One CTA per SM is launched, but the kernel is built so that two fit: the second slot is for the next kernel.
+    static constexpr int kMaxUpl = 1, kRows = 2, kCtasPerSm = 1;
+    static constexpr int min_ctas(int) { return 2; }
     static constexpr int ctas_per_sm(int) { return kCtasPerSm; }
     static void plane_row_bytes(uint64_t, uint64_t row_bytes, uint32_t *out) { out[0] = (uint32_t)row_bytes; }
     static __device__ __forceinline__ uint64_t units(uint64_t K) { return K / 128; }
@@ -595,7 +585,7 @@ struct Q6KNaturalXq8 {
     using W = Q6KW;
     static constexpr int kPlanes = 1;
     static constexpr bool kStageTokens = true;  // as Q4_K
-    static constexpr int kMaxUpl = 2, kRows = 2, kCtasPerSm = SYN_DEFAULT_CTAS;
+    static constexpr int kMaxUpl = 2, kRows = 2, kCtasPerSm = 2;
     static constexpr int min_ctas(int) { return 2; }
     static constexpr int ctas_per_sm(int) { return kCtasPerSm; }
     static void plane_row_bytes(uint64_t, uint64_t row_bytes, uint32_t *out) { out[0] = (uint32_t)row_bytes; }

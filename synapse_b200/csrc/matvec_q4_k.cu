@@ -3,10 +3,10 @@
 
 namespace syn {
 namespace mv {
-cudaError_t launch_xq8_q4_k(const MatvecArgs &a, const WeightView &view, cudaStream_t stream)
+cudaError_t launch_xq8_q4_k(const MatvecArgs &a, const WeightView *views, cudaStream_t stream)
 {
     const uint64_t K = a.matrix->columns;
-    return launch_format<Q4KXq8>(a, view, K / 128, K / 32, stream);
+    return launch_format<Q4KXq8>(a, views, K / 128, K / 32, stream);
 }
 }  // namespace mv
 }  // namespace syn

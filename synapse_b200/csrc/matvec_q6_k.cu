@@ -3,11 +3,11 @@
 
 namespace syn {
 namespace mv {
-cudaError_t launch_xq8_q6_k(const MatvecArgs &a, const WeightView &view, cudaStream_t stream)
+cudaError_t launch_xq8_q6_k(const MatvecArgs &a, const WeightView *views, cudaStream_t stream)
 {
     const uint64_t K = a.matrix->columns;
-    return a.matrix->layout == Layout::Planar ? launch_format<Q6KPlanarXq8>(a, view, K / 64, K / 16, stream)
-                                              : launch_format<Q6KNaturalXq8>(a, view, K / 64, K / 16, stream);
+    return a.matrix->layout == Layout::Planar ? launch_format<Q6KPlanarXq8>(a, views, K / 64, K / 16, stream)
+                                              : launch_format<Q6KNaturalXq8>(a, views, K / 64, K / 16, stream);
 }
 }  // namespace mv
 }  // namespace syn

@@ -3,11 +3,11 @@
 
 namespace syn {
 namespace mv {
-cudaError_t launch_xq8_q8_0(const MatvecArgs &a, const WeightView &view, cudaStream_t stream)
+cudaError_t launch_xq8_q8_0(const MatvecArgs &a, const WeightView *views, cudaStream_t stream)
 {
     const uint64_t K = a.matrix->columns;
-    return a.matrix->layout == Layout::Planar ? launch_format<Q8PlanarXq8>(a, view, K / 16, K / 32, stream)
-                                              : launch_format<Q8NaturalXq8>(a, view, K / 32, K / 32, stream);
+    return a.matrix->layout == Layout::Planar ? launch_format<Q8PlanarXq8>(a, views, K / 16, K / 32, stream)
+                                              : launch_format<Q8NaturalXq8>(a, views, K / 32, K / 32, stream);
 }
 }  // namespace mv
 }  // namespace syn

@@ -11,6 +11,8 @@
 // The grid is persistent (a multiple of the SM count); every CTA runs the same number of iterations so the
 // team reduction can use one CTA barrier per iteration with double-buffered partial sums.
 #pragma once
+#include <atomic>
+
 #include "matvec_formats.cuh"
 
 namespace syn {
@@ -202,6 +204,12 @@ matvec_xq8_team_kernel(WeightView w, ActView act, uint64_t K, uint64_t rows, uin
             }
         }
     }
+    if (epilogue.signal_count != 0) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            signal_completion(epilogue);
+        }
+    }
 }
 
 
@@ -212,17 +220,18 @@ cudaError_t launch_team(const MatvecArgs &a, const WeightView &view, uint64_t du
     const uint64_t row_groups = (a.row_count + R - 1) / R;
     uint64_t ctas = (row_groups + kTeams - 1) / kTeams;
     // Persistent grid: exactly as many CTAs as the SMs can hold at once for this instantiation.
-    static int resident = 0;
-    if (resident == 0) {
-        int blocks = 0;
+    // (the occupancy of an instantiation is the same on every device the library runs on: they are all sm_100)
+    static std::atomic<int> resident{0};
+    int blocks = resident.load(std::memory_order_relaxed);
+    if (blocks == 0) {
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, matvec_xq8_team_kernel<F, T, W, UPL, R, REGS, DUMP>, team_warps(W) * 32, 0) !=
                 cudaSuccess || blocks <= 0) {
             cudaGetLastError();
             blocks = 2;
         }
-        resident = blocks;
+        resident.store(blocks, std::memory_order_relaxed);
     }
-    const uint64_t cap = (uint64_t)sm_count(a.matrix->device) * resident;
+    const uint64_t cap = (uint64_t)sm_count(a.matrix->device) * blocks;
     if (ctas > cap) {
         ctas = cap;
     }
@@ -240,16 +249,19 @@ cudaError_t launch_team(const MatvecArgs &a, const WeightView &view, uint64_t du
 // kernel bumps the host-mapped fault word, stops waiting and still runs to completion (with wrong results).
 // ------------------------------------------------------------------------------------------------------
 
-#ifndef SYN_MV_GROUP_WARPS
-#define SYN_MV_GROUP_WARPS 12
-#endif
+constexpr int kGroupWarps = 12;  // consumer warps of the several-token CTAs (they have the SM to themselves)
 constexpr int kMaxStages = 8;
 constexpr uint64_t kWideBytes = 96ull << 20;  // matrices from this size on get the sixteen-warp CTA
 constexpr uint32_t kSpinLimit = 1u << 22;
-#ifndef SYN_MV_STAGE_KB
-#define SYN_MV_STAGE_KB 100
-#endif
-constexpr uint32_t kStageBudget = SYN_MV_STAGE_KB * 1024;  // dynamic shared memory per CTA, so that two CTAs fit one SM
+constexpr uint32_t kStageBudget = 100 * 1024;  // dynamic shared memory per CTA, so that two CTAs fit one SM
+
+struct PipeSegment {
+    WeightView global;     // plane bases at the first row of the segment
+    const float *bias;     // by row of the segment, or null
+    uint32_t rows;
+    uint32_t first_group;  // index of the segment's first row group among the launch's
+    uint64_t out_column;   // a result of row r goes to y[token * out_stride + out_column + r]
+};
 
 struct PipeArgs {
     WeightView global;            // plane bases at the first row of the call
@@ -257,6 +269,14 @@ struct PipeArgs {
     uint32_t plane_offset[4];     // offset of each plane inside a stage
     uint32_t planes, stages, stage_bytes;
     uint32_t act_bytes;           // shared memory reserved for in-kernel quantised activations (0 when not fused)
+    // kSegments: the row ranges of the launch and their number, `groups` row groups in all. kPair: segments[0] is the
+    // gate matrix, segments[1] the up matrix, whose rows sit pair_offset[k] behind the gate's in plane k of a stage.
+    uint32_t segment_count, groups;
+    uint32_t pair_offset[4];
+    PipeSegment segments[3];
+    // integer-dot hook: exact sub-block sums of row r go to dump[r * dump_groups ..]
+    int32_t *dump;
+    uint64_t dump_groups;
 };
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
@@ -333,24 +353,47 @@ __device__ __forceinline__ void stage_activations(const ActView &act, uint64_t t
     }
 }
 
+// What one launch multiplies:
+//   kSingle   - a row range of one matrix;
+//   kSegments - up to three row ranges of matrices with the same encoding and width, each with its own bias and output
+//               column (Q | K | V in one dispatch: MatmulArgs / MatmulSegment of the reference,
+//               native/synapse-gpu/src/Features/GpuKernels/cuda/kernels/common.cuh:52-69, step/layers.rs:71-94);
+//   kPair     - the same rows of a gate and an up matrix: a warp holds gate row r and up row r side by side and stores
+//               silu(gate . x) * (up . x), so the gate values never go to memory (Qwen2GateUpWork,
+//               src/Synapse.Runtime/Features/TextGeneration/Qwen2/Qwen2ProjectionWork.cs:91-131).
+// Every row keeps the team shape and lane assignment it has in a launch of its own, so results are bit-identical.
+enum : int { kSingle = 0, kSegments = 1, kPair = 2 };
+
+__device__ __forceinline__ const PipeSegment &segment_at(const PipeArgs &p, uint32_t index)
+{
+    return index == 0 ? p.segments[0] : index == 1 ? p.segments[1] : p.segments[2];
+}
+// The segment that holds row group `group` of a kSegments launch.
+__device__ __forceinline__ uint32_t segment_of(const PipeArgs &p, uint32_t group)
+{
+    return (p.segment_count > 1 && group >= p.segments[1].first_group ? 1u : 0u) + (p.segment_count > 2 && group >= p.segments[2].first_group ? 1u : 0u);
+}
+
 // CW = consumer warps the CTA is built for: 8 (two such CTAs fit one SM, so the next kernel of the stream can start
 // copying while this one runs) or 16 (one CTA per SM: twice the rows in flight, which is what large matrices need to
 // keep up with HBM).
-template <class F, int T, int W, int UPL, int R, bool REGS, bool FUSED, int CW = kWarps, bool GATHER = false>
+template <class F, int T, int W, int UPL, int R, bool REGS, bool FUSED, int CW = kWarps, bool GATHER = false, int MODE = kSingle, bool DUMP = false>
 __global__ void __launch_bounds__((CW / W) * W * 32 + 32, roomy(T, CW, FUSED) ? 1 : F::min_ctas(W))
 matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uint64_t in_stride, uint64_t K, uint64_t rows, uint32_t tokens,
                        float *__restrict__ y, uint64_t out_stride, Epilogue epilogue, uint32_t *fault)
 {
     static_assert(!REGS || T == 1, "register-resident activations are for single-token launches");
+    static_assert(MODE != kPair || R == 2, "a pair launch holds one gate row and one up row per warp");
+    static_assert(!DUMP || (T == 1 && MODE == kSingle), "the integer-dot hook is a single-token, single-matrix launch");
     constexpr int kTeams = CW / W;
     constexpr int kConsumers = kTeams * W;
-    constexpr uint64_t G = (uint64_t)kTeams * R;  // rows per stage
+    constexpr uint64_t G = MODE == kPair ? (uint64_t)kTeams : (uint64_t)kTeams * R;  // rows of one matrix per stage
     extern __shared__ __align__(128) uint8_t stage_memory[];
     __shared__ float partial[2][kConsumers][R * T];
     __shared__ __align__(8) uint64_t barriers[2 * kMaxStages];  // full[s] then empty[s]
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t warp_in_cta = threadIdx.x >> 5;
-    const uint64_t groups = (rows + G - 1) / G;
+    const uint64_t groups = MODE == kSegments ? (uint64_t)p.groups : (rows + G - 1) / G;
     const uint64_t my_groups = groups > blockIdx.x ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     const uint32_t full0 = smem_u32(&barriers[0]), empty0 = smem_u32(&barriers[kMaxStages]);
     if (threadIdx.x == 0) {
@@ -368,32 +411,52 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
     if (warp_in_cta == kConsumers) {
         // Producer warp: one lane streams this CTA's row groups into the ring.
         if (lane == 0) {
-            const uint8_t *bases[4] = {p.global.p0, p.global.p1, p.global.p2, p.global.p3};
             const uint64_t policy = l2_evict_first_policy();
+            // Calls `visit(source, bytes, offset inside the stage)` for every piece of row group `group`: one piece per
+            // plane (two in a pair launch), cut out on 16-byte boundaries; returns the bytes of the group.
+            auto pieces = [&](uint32_t group, auto visit) -> uint32_t {
+                uint32_t total = 0;
+                constexpr int kSources = MODE == kPair ? 2 : 1;
+#pragma unroll
+                for (int m = 0; m < kSources; ++m) {
+                    uint32_t local = group;
+                    uint64_t limit = rows;
+                    const uint8_t *bases[4] = {p.global.p0, p.global.p1, p.global.p2, p.global.p3};
+                    if (MODE != kSingle) {
+                        const uint32_t index = MODE == kPair ? (uint32_t)m : segment_of(p, group);
+                        const PipeSegment &segment = segment_at(p, index);
+                        bases[0] = segment.global.p0;
+                        bases[1] = segment.global.p1;
+                        bases[2] = segment.global.p2;
+                        bases[3] = segment.global.p3;
+                        if (MODE == kSegments) {
+                            local = group - segment.first_group;
+                            limit = segment.rows;
+                        }
+                    }
+                    const uint64_t row0 = (uint64_t)local * G;
+                    const uint64_t n = min(G, limit - row0);
+#pragma unroll
+                    for (int k = 0; k < F::kPlanes; ++k) {
+                        const uint8_t *source = bases[k] + row0 * p.plane_row_bytes[k];
+                        const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(source) & 15);
+                        const uint32_t bytes = (uint32_t)((shift + n * p.plane_row_bytes[k] + 15) & ~(uint64_t)15);
+                        visit(source - shift, bytes, p.plane_offset[k] + (uint32_t)m * p.pair_offset[k]);
+                        total += bytes;
+                    }
+                }
+                return total;
+            };
             uint32_t s = 0, round = 0;  // ring slot and how many times the ring has wrapped
-            uint64_t row0 = (uint64_t)blockIdx.x * G;
-            for (uint32_t it = 0; it < my_groups; ++it, row0 += (uint64_t)gridDim.x * G) {
+            for (uint32_t it = 0; it < my_groups; ++it) {
                 if (round > 0 && !mbar_wait(empty0 + 8 * s, (round - 1) & 1) && fault) {
                     atomicAdd(fault, 1u);
                 }
-                const uint64_t n = min(G, rows - row0);
-                uint32_t total = 0;
-                uint32_t bytes[4];
-                const uint8_t *sources[4];
-#pragma unroll
-                for (int k = 0; k < F::kPlanes; ++k) {
-                    const uint8_t *source = bases[k] + row0 * p.plane_row_bytes[k];
-                    const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(source) & 15);
-                    sources[k] = source - shift;
-                    bytes[k] = (uint32_t)((shift + n * p.plane_row_bytes[k] + 15) & ~(uint64_t)15);
-                    total += bytes[k];
-                }
+                const uint32_t group = blockIdx.x + it * gridDim.x;
+                const uint32_t total = pieces(group, [](const uint8_t *, uint32_t, uint32_t) {});
                 mbar_expect_tx(full0 + 8 * s, total);
                 const uint32_t stage = smem_u32(ring) + s * p.stage_bytes;
-#pragma unroll
-                for (int k = 0; k < F::kPlanes; ++k) {
-                    bulk_copy(stage + p.plane_offset[k], sources[k], bytes[k], full0 + 8 * s, policy);
-                }
+                pieces(group, [&](const uint8_t *source, uint32_t bytes, uint32_t offset) { bulk_copy(stage + offset, source, bytes, full0 + 8 * s, policy); });
                 if (++s == p.stages) {
                     s = 0;
                     ++round;
@@ -441,29 +504,56 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
     }
 
     uint32_t s = 0, phase = 0;
-    uint64_t group_row0 = (uint64_t)blockIdx.x * G;
-    for (uint32_t it = 0; it < my_groups; ++it, group_row0 += (uint64_t)gridDim.x * G) {
-        const uint64_t row0 = group_row0 + (uint64_t)team_in_cta * R;
+    for (uint32_t it = 0; it < my_groups; ++it) {
+        // Where this group's rows come from, how many there are, and where their results go.
+        uint32_t local = blockIdx.x + it * gridDim.x;
+        uint64_t limit = rows, column = 0;
+        const uint8_t *bases[2][4] = {{p.global.p0, p.global.p1, p.global.p2, p.global.p3}, {nullptr, nullptr, nullptr, nullptr}};
+        Epilogue e = epilogue;
+        if (MODE == kSegments) {
+            const PipeSegment &segment = segment_at(p, segment_of(p, local));
+            local -= segment.first_group;
+            limit = segment.rows;
+            column = segment.out_column;
+            bases[0][0] = segment.global.p0;
+            bases[0][1] = segment.global.p1;
+            bases[0][2] = segment.global.p2;
+            bases[0][3] = segment.global.p3;
+            e.bias = segment.bias ? segment.bias - column : nullptr;  // store_result indexes the bias with the output column
+        } else if (MODE == kPair) {
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                bases[m][0] = p.segments[m].global.p0;
+                bases[m][1] = p.segments[m].global.p1;
+                bases[m][2] = p.segments[m].global.p2;
+                bases[m][3] = p.segments[m].global.p3;
+            }
+        }
+        const uint64_t group_row0 = (uint64_t)local * G;
+        // first row of this team: R consecutive rows, or in a pair launch the same row of both matrices
+        const uint64_t row0 = group_row0 + (uint64_t)team_in_cta * (MODE == kPair ? 1 : R);
         if (!mbar_wait(full0 + 8 * s, phase) && fault && lane == 0) {
             atomicAdd(fault, 1u);
         }
         // The stage holds rows [group_row0, +G) of every plane with the plane's own row pitch; a plane whose rows
-        // are not 16-byte multiples starts `shift` bytes into its slot.
-        SharedView view;
-        view.row_bytes = p.plane_row_bytes[0];
+        // are not 16-byte multiples starts `shift` bytes into its slot. A pair launch has two such sets of rows.
+        SharedView views[MODE == kPair ? 2 : 1];
         {
             const uint32_t stage = smem_u32(ring) + s * p.stage_bytes;
-            const uint8_t *bases[4] = {p.global.p0, p.global.p1, p.global.p2, p.global.p3};
-            uint32_t local[4] = {0, 0, 0, 0};
 #pragma unroll
-            for (int k = 0; k < F::kPlanes; ++k) {
-                const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(bases[k] + group_row0 * p.plane_row_bytes[k]) & 15);
-                local[k] = stage + p.plane_offset[k] + shift;
+            for (int m = 0; m < (MODE == kPair ? 2 : 1); ++m) {
+                uint32_t local_base[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int k = 0; k < F::kPlanes; ++k) {
+                    const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(bases[m][k] + group_row0 * p.plane_row_bytes[k]) & 15);
+                    local_base[k] = stage + p.plane_offset[k] + (uint32_t)m * p.pair_offset[k] + shift;
+                }
+                views[m].row_bytes = p.plane_row_bytes[0];
+                views[m].p0 = local_base[0];
+                views[m].p1 = local_base[1];
+                views[m].p2 = local_base[2];
+                views[m].p3 = local_base[3];
             }
-            view.p0 = local[0];
-            view.p1 = local[1];
-            view.p2 = local[2];
-            view.p3 = local[3];
         }
         float acc[R][T];
 #pragma unroll
@@ -473,6 +563,7 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
                 acc[r][t] = 0.0f;
             }
         }
+        uint32_t release_slot = 0;
         for (uint32_t pass = 0; pass < passes; ++pass) {
             typename F::W wr[R][UPL];
             uint64_t u[UPL];
@@ -484,15 +575,16 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
                 u[j] = valid[j] ? unit : units - 1;
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
-                    F::template load_w<SharedMem>(view, K, (uint64_t)team_in_cta * R + r, u[j], lane, wr[r][j]);
+                    if (MODE == kPair) {
+                        F::template load_w<SharedMem>(views[MODE == kPair ? r : 0], K, (uint64_t)team_in_cta, u[j], lane, wr[r][j]);
+                    } else {
+                        F::template load_w<SharedMem>(views[0], K, (uint64_t)team_in_cta * R + r, u[j], lane, wr[r][j]);
+                    }
                 }
             }
             if (pass + 1 == passes) {
-                // Every unit of this warp is in registers: give the stage back to the producer.
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(empty0 + 8 * s);
-                }
+                // Every unit of this warp is in registers (or on its way there): the stage is released below.
+                release_slot = s;
                 if (++s == p.stages) {
                     s = 0;
                     phase ^= 1;
@@ -513,10 +605,22 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
                     const typename F::Act &a = REGS ? held[j] : loaded;
 #pragma unroll
                     for (int r = 0; r < R; ++r) {
-                        F::template dot<false>(wr[r][j], a, valid[j], u[j], lane, acc[r][t], nullptr);
+                        // rows past the end of the matrix hold whatever the stage held before: they are computed and
+                        // dropped, but must not reach the integer-dot hook
+                        int32_t *target = DUMP ? p.dump + min(row0 + r, rows - 1) * p.dump_groups : nullptr;
+                        F::template dot<DUMP>(wr[r][j], a, valid[j] && (!DUMP || row0 + r < limit), u[j], lane, acc[r][t], target);
                     }
                 }
             }
+        }
+        // Give the stage back to the producer. The bulk copy that refills it writes through the asynchronous proxy, the
+        // loads above read through the generic one: the proxy fence orders the two (without it nothing says that a
+        // load still in flight is performed before the refill lands). Doing this after the dot products, when the loaded
+        // registers have been consumed, makes the fence free; releasing right after the loads was measured no faster.
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(empty0 + 8 * release_slot);
         }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -527,12 +631,22 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
         }
         if (W == 1) {
             if (lane == 0) {
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
+                if (MODE == kPair) {
 #pragma unroll
                     for (int t = 0; t < T; ++t) {
-                        if (row0 + r < rows && (uint32_t)t < live) {
-                            store_result<GATHER>(epilogue, y, token0 + t, out_stride, row0 + r, acc[r][t]);
+                        if (row0 < limit && (uint32_t)t < live) {
+                            const float g = acc[0][t];
+                            store_result<GATHER>(e, y, token0 + t, out_stride, row0, g / (1.0f + expf(-g)) * acc[1][t]);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+#pragma unroll
+                        for (int t = 0; t < T; ++t) {
+                            if (row0 + r < limit && (uint32_t)t < live) {
+                                store_result<GATHER>(e, y, token0 + t, out_stride, column + row0 + r, acc[r][t]);
+                            }
                         }
                     }
                 }
@@ -549,33 +663,57 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
                 }
             }
             consumer_barrier<kConsumers * 32>();
-            if (warp_in_team == 0 && lane < R * T) {
+            if (MODE == kPair) {
+                if (warp_in_team == 0 && lane < T) {
+                    float g = partial[buffer][team_in_cta * W][lane], up = partial[buffer][team_in_cta * W][T + lane];
+#pragma unroll
+                    for (int k = 1; k < W; ++k) {
+                        g += partial[buffer][team_in_cta * W + k][lane];
+                        up += partial[buffer][team_in_cta * W + k][T + lane];
+                    }
+                    if (row0 < limit && lane < live) {
+                        store_result<GATHER>(e, y, token0 + lane, out_stride, row0, g / (1.0f + expf(-g)) * up);
+                    }
+                }
+            } else if (warp_in_team == 0 && lane < R * T) {
                 const uint32_t r = lane / T, t = lane % T;
                 float total = partial[buffer][team_in_cta * W][lane];
 #pragma unroll
                 for (int k = 1; k < W; ++k) {
                     total += partial[buffer][team_in_cta * W + k][lane];
                 }
-                if (row0 + r < rows && t < live) {
-                    store_result<GATHER>(epilogue, y, token0 + t, out_stride, row0 + r, total);
+                if (row0 + r < limit && t < live) {
+                    store_result<GATHER>(e, y, token0 + t, out_stride, column + row0 + r, total);
                 }
             }
+        }
+    }
+    if (GATHER) {
+        // every consumer warp of the CTA has stored its last result (the producer warp left long ago)
+        consumer_barrier<kConsumers * 32>();
+        if (threadIdx.x == 0) {
+            signal_completion(epilogue);
         }
     }
 }
 
 // Lays out a stage for this format and row length; false when a group of rows does not fit the stage budget.
+// `views` holds one view per segment of the launch (one for a plain product).
 template <class F, int W, int R, int CW = kWarps>
-bool plan_pipe(const MatvecArgs &a, const WeightView &view, uint32_t act_bytes, PipeArgs &p, uint32_t budget = kStageBudget)
+bool plan_pipe(const MatvecArgs &a, const WeightView *views, uint32_t act_bytes, PipeArgs &p, uint32_t budget = kStageBudget, int mode = kSingle)
 {
-    constexpr uint64_t G = (uint64_t)(CW / W) * R;
-    p.global = view;
+    constexpr uint64_t kTeams = CW / W;
+    const uint64_t G = mode == kPair ? kTeams : kTeams * R;  // rows of one matrix per stage
+    p = PipeArgs{};
+    p.global = views[0];
     p.planes = F::kPlanes;
     F::plane_row_bytes(a.matrix->columns, a.matrix->row_bytes, p.plane_row_bytes);
     uint64_t offset = 0;
     for (int k = 0; k < F::kPlanes; ++k) {
         p.plane_offset[k] = (uint32_t)offset;
-        offset += align_up(G * p.plane_row_bytes[k] + 16, 128);
+        const uint64_t slot = align_up(G * p.plane_row_bytes[k] + 16, 128);
+        p.pair_offset[k] = mode == kPair ? (uint32_t)slot : 0u;
+        offset += mode == kPair ? 2 * slot : slot;
     }
     for (int k = F::kPlanes; k < 4; ++k) {
         p.plane_offset[k] = 0;
@@ -588,28 +726,60 @@ bool plan_pipe(const MatvecArgs &a, const WeightView &view, uint32_t act_bytes, 
     p.stage_bytes = (uint32_t)offset;
     uint64_t stages = (budget - act_bytes) / offset;
     p.stages = (uint32_t)(stages > kMaxStages ? kMaxStages : stages);
+    p.groups = (uint32_t)((a.row_count + G - 1) / G);
+    if (mode != kSingle) {
+        p.segment_count = a.segment_count;
+        uint64_t groups = 0;
+        for (uint32_t i = 0; i < a.segment_count; ++i) {
+            PipeSegment &segment = p.segments[i];
+            segment.global = views[i];
+            segment.bias = a.segments[i].bias;
+            segment.rows = (uint32_t)a.segments[i].row_count;
+            segment.out_column = a.segments[i].out_column;
+            segment.first_group = (uint32_t)groups;
+            groups += (a.segments[i].row_count + G - 1) / G;
+        }
+        if (mode == kSegments) {
+            p.groups = (uint32_t)groups;
+        }
+    }
+    p.dump = a.dump;
     return true;
 }
 
-template <class F, int T, int W, int UPL, int R, bool REGS, bool FUSED, int CW = kWarps, bool GATHER = false>
+// Device attributes of a kernel (its dynamic shared-memory limit) are per device: `first_use` is true once per
+// device for the object it is called on, from whichever thread gets there first.
+struct PerDevice {
+    std::atomic<uint64_t> seen{0};
+    bool first_use(int device)
+    {
+        const uint64_t bit = 1ull << (device & 63);
+        return (seen.fetch_or(bit) & bit) == 0;
+    }
+    void forget(int device) { seen.fetch_and(~(1ull << (device & 63))); }
+};
+
+template <class F, int T, int W, int UPL, int R, bool REGS, bool FUSED, int CW = kWarps, bool GATHER = false, int MODE = kSingle, bool DUMP = false>
 cudaError_t launch_pipe(const MatvecArgs &a, const PipeArgs &p, cudaStream_t stream)
 {
-    constexpr uint64_t G = (uint64_t)(CW / W) * R;
-    auto kernel = matvec_xq8_pipe_kernel<F, T, W, UPL, R, REGS, FUSED, CW, GATHER>;
+    auto kernel = matvec_xq8_pipe_kernel<F, T, W, UPL, R, REGS, FUSED, CW, GATHER, MODE, DUMP>;
     const uint32_t dynamic = p.act_bytes + p.stages * p.stage_bytes;
-    static bool configured = false;
-    if (!configured) {
+    static PerDevice configured;
+    if (configured.first_use(a.matrix->device)) {
         cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stage_budget(T, FUSED));
         if (error != cudaSuccess) {
+            configured.forget(a.matrix->device);
             return error;
         }
-        configured = true;
     }
     // F::kCtasPerSm CTAs per SM. Where that is one, the kernel is still built so that two fit (registers and
     // shared memory): the second slot is for the next kernel of the stream, which starts copying its first stages
     // while this one is still running.
-    uint64_t ctas = (a.row_count + G - 1) / G;
-    const uint64_t cap = (uint64_t)sm_count(a.matrix->device) * (roomy(T, CW, FUSED) ? 1 : F::ctas_per_sm(W));
+    uint64_t ctas = p.groups;
+    // A launch of several row ranges, or of a gate/up pair, fills both CTA slots of every SM: it stands for the two or three
+    // launches that otherwise run side by side on parallel branches (measured on the 2 x 38 MB gate | up pair: 15.9 us with
+    // two CTAs per SM, 17.2 us with one).
+    const uint64_t cap = (uint64_t)sm_count(a.matrix->device) * (roomy(T, CW, FUSED) ? 1 : MODE != kSingle ? 2 : F::ctas_per_sm(W));
     if (ctas > cap) {
         ctas = cap;
     }
@@ -619,21 +789,65 @@ cudaError_t launch_pipe(const MatvecArgs &a, const PipeArgs &p, cudaStream_t str
 }
 
 template <class F, int W, int UPL>
-cudaError_t launch_tokens(const MatvecArgs &a, const WeightView &view, bool one_pass, uint64_t dump_groups, cudaStream_t stream)
+cudaError_t launch_tokens(const MatvecArgs &a, const WeightView *views, bool one_pass, uint64_t dump_groups, cudaStream_t stream)
 {
     constexpr int R = F::kRows;
-    if (a.dump) {
-        return launch_team<F, 1, W, UPL, 1, false, true>(a, view, dump_groups, stream);
-    }
+    const WeightView &view = views[0];
     PipeArgs pipe;
+    if (a.dump) {
+        // The integer-dot hook: token by token through the very kernel variant a single-token product of this matrix
+        // takes (built with the hook compiled in), so that the sums come out of the code that is timed.
+        const uint64_t K = a.matrix->columns;
+        for (uint64_t t = 0; t < a.tokens; ++t) {
+            MatvecArgs one = a;
+            one.tokens = 1;
+            one.act.codes = a.act.codes + t * K;
+            one.act.scales = a.act.scales + t * (K / 32);
+            one.act.sums = a.act.sums + t * (K / 16);
+            one.y = a.y + t * a.out_stride;
+            one.dump = a.dump + t * a.row_count * dump_groups;
+            cudaError_t error;
+            if (one_pass && a.row_count * a.matrix->row_bytes >= kWideBytes && plan_pipe<F, W, 1, 2 * kWarps>(one, views, 0, pipe)) {
+                pipe.dump_groups = dump_groups;
+                error = launch_pipe<F, 1, W, UPL, 1, true, false, 2 * kWarps, false, kSingle, true>(one, pipe, stream);
+            } else if (one_pass && plan_pipe<F, W, R>(one, views, 0, pipe)) {
+                pipe.dump_groups = dump_groups;
+                error = launch_pipe<F, 1, W, UPL, R, true, false, kWarps, false, kSingle, true>(one, pipe, stream);
+            } else {
+                error = launch_team<F, 1, W, UPL, 1, false, true>(one, view, dump_groups, stream);
+            }
+            if (error != cudaSuccess) {
+                return error;
+            }
+        }
+        return cudaSuccess;
+    }
     const uint32_t K32 = (uint32_t)a.matrix->columns;
+    const bool gather = a.fused.peer_count != 0 || a.fused.signal_count != 0;
+    if (a.form != kSingle) {
+        // Several row ranges, or a gate/up pair, in one launch: single-token products on ready-made activations whose
+        // rows one pass of the team covers. Anything else is refused here and runs as separate launches.
+        if (a.tokens != 1 || !one_pass || !a.act_ready || !plan_pipe<F, W, R>(a, views, 0, pipe, kStageBudget, (int)a.form)) {
+            return cudaErrorNotSupported;
+        }
+        if constexpr (R == 2) {
+            if (a.form == kPair) {
+                return gather ? launch_pipe<F, 1, W, UPL, R, true, false, kWarps, true, kPair>(a, pipe, stream)
+                              : launch_pipe<F, 1, W, UPL, R, true, false, kWarps, false, kPair>(a, pipe, stream);
+            }
+        }
+        if (a.form == kSegments) {
+            return gather ? launch_pipe<F, 1, W, UPL, R, true, false, kWarps, true, kSegments>(a, pipe, stream)
+                          : launch_pipe<F, 1, W, UPL, R, true, false, kWarps, false, kSegments>(a, pipe, stream);
+        }
+        return cudaErrorNotSupported;
+    }
     // Products that also store into peer copies of the output: one pipelined variant (single token, one pass, ready
     // activations); every other shape takes the direct-load kernel below, whose epilogue handles peers at run time.
-    const bool gather = a.fused.peer_count != 0;
-    if (gather && a.tokens <= 1 && one_pass && a.act_ready && plan_pipe<F, W, R>(a, view, 0, pipe)) {
+    if (gather && a.tokens <= 1 && one_pass && a.act_ready && plan_pipe<F, W, R>(a, views, 0, pipe)) {
         return launch_pipe<F, 1, W, UPL, R, true, false, kWarps, true>(a, pipe, stream);
     }
-    if (!gather && a.tokens <= 1 && !a.act_ready && plan_pipe<F, W, R>(a, view, shared_act_bytes(1, K32), pipe)) {
+    if (!gather && a.tokens <= 1 && !a.act_ready && plan_pipe<F, W, R>(a, views, shared_act_bytes(1, K32), pipe)) {
         // FP32 activations in: the kernel quantises them itself.
         return one_pass ? launch_pipe<F, 1, W, UPL, R, true, true>(a, pipe, stream) : launch_pipe<F, 1, W, UPL, R, false, true>(a, pipe, stream);
     }
@@ -646,14 +860,13 @@ cudaError_t launch_tokens(const MatvecArgs &a, const WeightView &view, bool one_
             grouped.x = nullptr;  // tells the kernel to copy instead of quantising
         }
         const uint32_t budget = stage_budget(2, true);
-        constexpr int kGroupWarps = SYN_MV_GROUP_WARPS;  // consumer warps of these CTAs (they have the SM to themselves)
-        if (a.tokens > 4 && plan_pipe<F, W, R, kGroupWarps>(a, view, shared_act_bytes(8, K32), pipe, budget)) {
+        if (a.tokens > 4 && plan_pipe<F, W, R, kGroupWarps>(a, views, shared_act_bytes(8, K32), pipe, budget)) {
             return launch_pipe<F, 8, W, UPL, R, false, true, kGroupWarps>(grouped, pipe, stream);
         }
-        if (a.tokens > 2 && plan_pipe<F, W, R, kGroupWarps>(a, view, shared_act_bytes(4, K32), pipe, budget)) {
+        if (a.tokens > 2 && plan_pipe<F, W, R, kGroupWarps>(a, views, shared_act_bytes(4, K32), pipe, budget)) {
             return launch_pipe<F, 4, W, UPL, R, false, true, kGroupWarps>(grouped, pipe, stream);
         }
-        if (plan_pipe<F, W, R, kGroupWarps>(a, view, shared_act_bytes(2, K32), pipe, budget)) {
+        if (plan_pipe<F, W, R, kGroupWarps>(a, views, shared_act_bytes(2, K32), pipe, budget)) {
             return launch_pipe<F, 2, W, UPL, R, false, true, kGroupWarps>(grouped, pipe, stream);
         }
     }
@@ -669,13 +882,13 @@ cudaError_t launch_tokens(const MatvecArgs &a, const WeightView &view, bool one_
     // it depends on W and UPL only). Measured on Q4_K: 306 MB in 47.2 against 52.7 us, 153 MB in 25.4 against 30.7 us.
     // A 38 MB projection gains 4 % alone but loses more inside a decode step, where the eight-warp CTAs of two
     // kernels share an SM (parallel branches, and the next kernel's first copies).
-    if (!gather && a.tokens <= 1 && one_pass && a.row_count * a.matrix->row_bytes >= kWideBytes && plan_pipe<F, W, 1, 2 * kWarps>(a, view, 0, pipe)) {
+    if (!gather && a.tokens <= 1 && one_pass && a.row_count * a.matrix->row_bytes >= kWideBytes && plan_pipe<F, W, 1, 2 * kWarps>(a, views, 0, pipe)) {
         return launch_pipe<F, 1, W, UPL, 1, true, false, 2 * kWarps>(a, pipe, stream);
     }
-    if (!gather && a.tokens <= 1 && plan_pipe<F, W, R>(a, view, 0, pipe)) {
+    if (!gather && a.tokens <= 1 && plan_pipe<F, W, R>(a, views, 0, pipe)) {
         return one_pass ? launch_pipe<F, 1, W, UPL, R, true, false>(a, pipe, stream) : launch_pipe<F, 1, W, UPL, R, false, false>(a, pipe, stream);
     }
-    if constexpr (!F::kStageTokens) if (!gather && a.tokens == 2 && plan_pipe<F, W, R>(a, view, 0, pipe)) {
+    if constexpr (!F::kStageTokens) if (!gather && a.tokens == 2 && plan_pipe<F, W, R>(a, views, 0, pipe)) {
         return launch_pipe<F, 2, W, UPL, R, false, false>(a, pipe, stream);  // activations read from the scratch as they are
     }
     // Token group size: the smallest of 1, 2, 4, 8 that holds the tokens (step/projection.rs:82-87).
@@ -695,22 +908,22 @@ cudaError_t launch_tokens(const MatvecArgs &a, const WeightView &view, bool one_
 // Team shape from the row length alone: the fewest warps that cover the row in one pass with F::kMaxUpl units per
 // lane (one unit per lane when the row is short enough); eight warps making several passes for very long rows.
 template <class F>
-cudaError_t launch_format(const MatvecArgs &a, const WeightView &view, uint64_t units, uint64_t dump_groups, cudaStream_t stream)
+cudaError_t launch_format(const MatvecArgs &a, const WeightView *views, uint64_t units, uint64_t dump_groups, cudaStream_t stream)
 {
     constexpr int U = F::kMaxUpl;
     if (units <= 32) {
-        return launch_tokens<F, 1, 1>(a, view, true, dump_groups, stream);
+        return launch_tokens<F, 1, 1>(a, views, true, dump_groups, stream);
     }
     switch ((units + 32 * U - 1) / (32 * U)) {
-    case 1: return launch_tokens<F, 1, U>(a, view, true, dump_groups, stream);
-    case 2: return launch_tokens<F, 2, U>(a, view, true, dump_groups, stream);
-    case 3: return launch_tokens<F, 3, U>(a, view, true, dump_groups, stream);
-    case 4: return launch_tokens<F, 4, U>(a, view, true, dump_groups, stream);
-    case 5: return launch_tokens<F, 5, U>(a, view, true, dump_groups, stream);
-    case 6: return launch_tokens<F, 6, U>(a, view, true, dump_groups, stream);
-    case 7: return launch_tokens<F, 7, U>(a, view, true, dump_groups, stream);
-    case 8: return launch_tokens<F, 8, U>(a, view, true, dump_groups, stream);
-    default: return launch_tokens<F, 8, U>(a, view, false, dump_groups, stream);
+    case 1: return launch_tokens<F, 1, U>(a, views, true, dump_groups, stream);
+    case 2: return launch_tokens<F, 2, U>(a, views, true, dump_groups, stream);
+    case 3: return launch_tokens<F, 3, U>(a, views, true, dump_groups, stream);
+    case 4: return launch_tokens<F, 4, U>(a, views, true, dump_groups, stream);
+    case 5: return launch_tokens<F, 5, U>(a, views, true, dump_groups, stream);
+    case 6: return launch_tokens<F, 6, U>(a, views, true, dump_groups, stream);
+    case 7: return launch_tokens<F, 7, U>(a, views, true, dump_groups, stream);
+    case 8: return launch_tokens<F, 8, U>(a, views, true, dump_groups, stream);
+    default: return launch_tokens<F, 8, U>(a, views, false, dump_groups, stream);
     }
 }
 

@@ -61,13 +61,11 @@ extern "C" int32_t syn_b200_matvec_static(const syn_b200_matrix *matrix, uint64_
     if (!matrix || !x || !y) {
         return fail(SYN_B200_NULL_POINTER, "matrix, activations or output");
     }
-    try {
-        if (row_count == 0 || row_start > matrix->rows || row_count > matrix->rows - row_start) {
-            return fail(SYN_B200_INVALID_ARGUMENT, "rows [" + std::to_string(row_start) + ", +" + std::to_string(row_count) +
-                                                       ") exceed matrix rows " + std::to_string(matrix->rows));
-        }
-        if (tokens == 0 || (tokens > 1 && out_stride < row_count)) {
-            return fail(SYN_B200_INVALID_ARGUMENT, "token count is zero or the output stride is below the row count");
+    return guarded([&]() -> int32_t {
+        int32_t status = check_product(matrix, row_start, row_count, tokens, out_stride, nullptr);
+        if (status == SYN_B200_OK) status = check_device(matrix);
+        if (status != SYN_B200_OK) {
+            return status;
         }
         if (epilogue > SYN_B200_EPILOGUE_ACCUMULATE) {
             return fail(SYN_B200_INVALID_ARGUMENT, "unknown epilogue " + std::to_string(epilogue));
@@ -80,45 +78,31 @@ extern "C" int32_t syn_b200_matvec_static(const syn_b200_matrix *matrix, uint64_
         if (in_stride < K || in_stride % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) {
             return fail(SYN_B200_INVALID_ARGUMENT, "device activations must be 16-byte aligned with a stride that covers the row and is a multiple of 4 floats");
         }
-        int device = 0;
-        if (cudaGetDevice(&device) != cudaSuccess || device != matrix->device) {
-            cudaGetLastError();
-            return fail(SYN_B200_INVALID_ARGUMENT, "the matrix lives on device " + std::to_string(matrix->device) +
-                                                       ", which is not the calling thread's current device");
-        }
         void *scratch = nullptr;
-        int32_t status = static_scratch(device, &scratch);
+        status = static_scratch(matrix->device, &scratch);
         if (status != SYN_B200_OK) {
             return status;
         }
-        const ActLayout layout = act_layout(tokens, K);
-        if (layout.total > kStaticScratchBytes) {
+        if (act_layout(tokens, K).total > kStaticScratchBytes) {
             return fail(SYN_B200_INVALID_ARGUMENT, "the activation layout does not fit the built-in scratch");
         }
-        uint8_t *base = static_cast<uint8_t *>(scratch);
-        cudaStream_t s = static_cast<cudaStream_t>(stream);
-        cudaError_t error = launch_quantize(x, tokens, K, in_stride, reinterpret_cast<int8_t *>(base + layout.codes),
-                                            reinterpret_cast<float *>(base + layout.scales), reinterpret_cast<int16_t *>(base + layout.sums), s);
-        if (error != cudaSuccess) {
-            return cuda_fail(error, "launching the activation quantiser");
-        }
+        // Exactly what syn_b200_matvec_dev queues in its quantised-activation mode, with the built-in array as the
+        // scratch: the kernel quantises x itself where it can (one token: a single launch), and the shapes where it
+        // cannot get a quantiser launch into the array first.
         MatvecArgs args{};
         args.matrix = matrix;
         args.row_start = row_start;
         args.row_count = row_count;
         args.tokens = tokens;
         args.act = act_view(scratch, tokens, K);
-        args.act_ready = true;
+        args.act_ready = false;
+        args.x = x;
+        args.in_stride = in_stride;
         args.y = y;
         args.out_stride = out_stride;
         args.mode = SYN_B200_MODE_XQ8;
         args.epilogue = epilogue;
-        error = launch_matvec(args, s);
-        if (error != cudaSuccess) {
-            return cuda_fail(error, "launching the matrix-vector kernel");
-        }
-        return SYN_B200_OK;
-    } catch (...) {
-        return fail(SYN_B200_INTERNAL, "exception at the ABI");
-    }
+        const cudaError_t error = launch_matvec(args, static_cast<cudaStream_t>(stream));
+        return error == cudaSuccess ? SYN_B200_OK : cuda_fail(error, "launching the matrix-vector kernel");
+    });
 }

@@ -11,6 +11,15 @@ namespace {
 
 constexpr int kWarpsPerCta = 8;
 
+int current_sm_count()
+{
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) {
+        cudaGetLastError();
+    }
+    return sm_count(device);
+}
+
 // One warp per 32-value block, one lane per value.
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 quantize_q8_kernel(const float *__restrict__ x, uint64_t blocks_per_row, uint64_t total_blocks, uint64_t in_stride,
@@ -65,7 +74,48 @@ __global__ void group_sums_kernel(const int8_t *__restrict__ codes, uint64_t cou
     }
 }
 
+// One warp; lane i watches word i of the signal array. Every wait is bounded by the nanosecond timer.
+__global__ void gather_wait_kernel(const uint32_t *signals, uint32_t count, uint32_t *epoch, uint64_t timeout_ns, uint32_t *fault)
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t lane = threadIdx.x;
+    const uint32_t expected = *epoch + 1;
+    __syncwarp();
+    bool reached = true;
+    if (lane < count) {
+        uint64_t start;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+        reached = false;
+        while (true) {
+            uint32_t value;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(value) : "l"(signals + lane) : "memory");
+            if ((int32_t)(value - expected) >= 0) {
+                reached = true;
+                break;
+            }
+            uint64_t now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (now - start > timeout_ns) {
+                break;
+            }
+        }
+    }
+    const bool all = __all_sync(0xffffffffu, reached);
+    if (lane == 0) {
+        *epoch = expected;
+        if (!all && fault) {
+            atomicAdd(fault, 1u);
+        }
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_gather_wait(const uint32_t *signals, uint32_t count, uint32_t *epoch, uint32_t timeout_us, cudaStream_t stream)
+{
+    return launch_kernel(gather_wait_kernel, dim3(1), dim3(32), 0, stream, signals, count, epoch, (uint64_t)timeout_us * 1000ull, fault_word_device());
+}
 
 cudaError_t launch_quantize(const float *x, uint64_t tokens, uint64_t columns, uint64_t in_stride, int8_t *codes,
                             float *scales, int16_t *sums, cudaStream_t stream)
@@ -73,8 +123,9 @@ cudaError_t launch_quantize(const float *x, uint64_t tokens, uint64_t columns, u
     const uint64_t blocks_per_row = columns / 32;
     const uint64_t total = tokens * blocks_per_row;
     uint64_t grid = (total + kWarpsPerCta - 1) / kWarpsPerCta;
-    if (grid > 148 * 8) {
-        grid = 148 * 8;
+    const uint64_t cap = (uint64_t)current_sm_count() * 8;
+    if (grid > cap) {
+        grid = cap;
     }
     return launch_kernel(quantize_q8_kernel, dim3((unsigned)grid), dim3(kWarpsPerCta * 32), 0, stream, x, blocks_per_row, total, in_stride,
                          codes, scales, sums);
@@ -83,8 +134,9 @@ cudaError_t launch_quantize(const float *x, uint64_t tokens, uint64_t columns, u
 cudaError_t launch_group_sums(const int8_t *codes, uint64_t count16, int16_t *sums, cudaStream_t stream)
 {
     uint64_t grid = (count16 + 255) / 256;
-    if (grid > 148 * 8) {
-        grid = 148 * 8;
+    const uint64_t cap = (uint64_t)current_sm_count() * 8;
+    if (grid > cap) {
+        grid = cap;
     }
     return launch_kernel(group_sums_kernel, dim3((unsigned)grid), dim3(256), 0, stream, codes, count16, sums);
 }

@@ -99,4 +99,65 @@ cudaError_t launch_repack(uint32_t type, const uint8_t *natural, uint64_t rows, 
     return cudaGetLastError();
 }
 
+
+// ---- block validation at load (BlockSourceDecoder.Decode, ModelPackages/SourceFormats/SourceTensorDecoders.cs:134-146,
+// 161-172): every fp16 field of every block must be finite. Offsets of the fp16 fields inside a block: Q8_0 d at 0;
+// Q4_K d at 0 and dmin at 2; Q6_K d at 208. -----------------------------------------------------------------
+
+namespace {
+
+__host__ __device__ inline bool half_bits_finite(uint32_t bits) { return (bits & 0x7C00u) != 0x7C00u; }
+__host__ __device__ inline bool block_scales_finite(uint32_t type, const uint8_t *block)
+{
+    if (type == kQ6_K) {
+        return half_bits_finite(block[208] | (block[209] << 8));
+    }
+    const bool d = half_bits_finite(block[0] | (block[1] << 8));
+    return type == kQ4_K ? d && half_bits_finite(block[2] | (block[3] << 8)) : d;
+}
+
+__global__ void validate_blocks_kernel(const uint8_t *__restrict__ data, uint32_t type, uint32_t block_bytes, uint64_t blocks,
+                                       unsigned long long *__restrict__ first_bad)
+{
+    uint64_t block = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (; block < blocks; block += stride) {
+        if (!block_scales_finite(type, data + block * block_bytes)) {
+            atomicMin(first_bad, (unsigned long long)block);
+        }
+    }
+}
+
+}  // namespace
+
+uint64_t first_invalid_block_host(uint32_t type, const uint8_t *data, uint64_t blocks)
+{
+    const uint64_t bytes = block_bytes(type);
+    for (uint64_t block = 0; block < blocks; ++block) {
+        if (!block_scales_finite(type, data + block * bytes)) {
+            return block;
+        }
+    }
+    return UINT64_MAX;
+}
+
+cudaError_t launch_validate_blocks(uint32_t type, const uint8_t *data, uint64_t blocks, uint64_t *first_bad_device, cudaStream_t stream)
+{
+    cudaError_t error = cudaMemsetAsync(first_bad_device, 0xFF, sizeof(uint64_t), stream);
+    if (error != cudaSuccess) {
+        return error;
+    }
+    uint64_t grid = (blocks + 255) / 256;
+    int device = 0;
+    cudaGetDevice(&device);
+    const uint64_t cap = (uint64_t)sm_count(device) * 8;
+    if (grid > cap) {
+        grid = cap;
+    }
+    validate_blocks_kernel<<<(unsigned)grid, 256, 0, stream>>>(data, type, (uint32_t)block_bytes(type), blocks,
+                                                              reinterpret_cast<unsigned long long *>(first_bad_device));
+    count_launch();
+    return cudaGetLastError();
+}
+
 }  // namespace syn

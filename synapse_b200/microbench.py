@@ -25,7 +25,8 @@ def main():
     parser.add_argument("--cycles", type=int, default=4, help="times every copy is launched inside one graph (amortises the graph launch)")
     parser.add_argument("--reps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
-    parser.add_argument("--mode", default="xq8", choices=["xq8", "xf32", "gemm", "decode"])
+    parser.add_argument("--mode", default="xq8", choices=["xq8", "xf32", "gemm", "decode", "pair"],
+                        help="pair: consecutive copies are the gate and up matrix of one launch that stores silu(gate . x) * (up . x)")
     parser.add_argument("--layers", type=int, default=4, help="decode mode: layers of the Qwen2.5-7B-shaped Q4_K_M model")
     parser.add_argument("--no-repack", action="store_true")
     parser.add_argument("--fused-quantize", action="store_true", help="time quantise + product together (xq8)")
@@ -69,6 +70,10 @@ def main():
 
     def one_round(stream_ptr):
         for _ in range(args.cycles):
+            if args.mode == "pair":
+                for gate, up in zip(matrices[0::2], matrices[1::2]):
+                    sb.matmul_q8_swiglu_device(gate, up, scratch_ptr, args.tokens, y.data_ptr(), args.rows, stream=stream_ptr)
+                continue
             for matrix in matrices:
                 launch(matrix, stream_ptr)
 
@@ -91,9 +96,10 @@ def main():
             graph.replay() if graph is not None else one_round(stream.cuda_stream)
         end.record(stream)
         stream.synchronize()
-    launches = args.reps * args.copies * args.cycles
+    per_launch = 2 if args.mode == "pair" else 1
+    launches = args.reps * (args.copies // per_launch) * args.cycles
     microseconds = begin.elapsed_time(end) * 1e3 / launches
-    source_bytes = matrices[0].source_bytes
+    source_bytes = matrices[0].source_bytes * per_launch
     print(json.dumps({"type": args.type, "rows": args.rows, "cols": args.cols, "tokens": args.tokens, "mode": args.mode,
                       "repack": not args.no_repack, "copies": args.copies, "cycles": args.cycles, "graph": graph is not None, "us_per_launch": microseconds,
                       "weight_gbs": source_bytes / microseconds / 1e3,

@@ -76,6 +76,13 @@ class PeerOutputs:
         for name, length in layout.items():
             self.offsets[name] = (total, int(length))
             total += (int(length) + 63) // 64 * 64  # 256-byte aligned vectors
+        # Behind the vectors, 32 words (128 bytes) per vector: words 0..world-1 are this GPU's signal array of the vector
+        # (rank r's products write word r, here and in every peer's buffer), words 16 and 17 the local arrival words of
+        # this rank's products, word 24 the local sequence number of this rank's waits.
+        self.control = {}
+        for name in layout:
+            self.control[name] = total
+            total += 32
         total = max(total, 64)
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         torch.cuda.set_device(device)
@@ -123,6 +130,18 @@ class PeerOutputs:
         """This rank's copy of the full output vector ``name``."""
         offset, length = self.offsets[name]
         return self.local[offset:offset + length]
+
+    def signals(self, name):
+        """(signal word pointers, arrivals pointer) for this rank's products into vector ``name``: this rank's word of the
+        vector's signal array in its own buffer first, then the same word in every peer's buffer."""
+        at = 4 * (self.control[name] + self.rank)
+        words = [self.bases[self.rank] + at] + [self.bases[r] + at for r in range(self.world) if r != self.rank]
+        return words, self.bases[self.rank] + 4 * (self.control[name] + 16)
+
+    def wait_arguments(self, name):
+        """(signal array pointer, word count, sequence word pointer) for ``gather_wait_device`` on vector ``name``."""
+        base = self.bases[self.rank] + 4 * self.control[name]
+        return base, self.world, base + 4 * 24
 
     def pointers(self, name, first_row: int):
         """(own pointer, [peer pointers]) of element ``first_row`` of vector ``name``."""

@@ -37,9 +37,10 @@ def main():
             want = torch.zeros(rows, device=device)
             whole.matmul_q8_device(scratch_ptr, 1, want.data_ptr(), rows)
             own, others = peers.pointers("y", first)
-            shard.matmul_q8_gather_device(scratch_ptr, 1, own, count, others)
-            torch.cuda.synchronize()
-            dist.barrier()  # every rank's stores have landed
+            words, arrivals = peers.signals("y")
+            shard.matmul_q8_gather_device(scratch_ptr, 1, own, count, others, signal_ptrs=words, arrivals_ptr=arrivals)
+            # no barrier: the wait returns when every rank's slice has landed in this GPU's copy (or after one second)
+            sb.gather_wait_device(*peers.wait_arguments("y"), timeout_us=1_000_000)
             torch.cuda.synchronize()
             if not torch.equal(peers.view("y"), want):
                 failures += 1

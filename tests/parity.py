@@ -26,3 +26,26 @@ def assert_parity(got, want, exact, magnitude, label=""):
     assert reference_form.all(), f"{label}: {int((~reference_form).sum())} outputs exceed 2e-5 * sum|term| of the FP64 value"
     return {"outside_rel_gate": int((~gate).sum()), "count": int(gate.size),
             "max_normalised": float(np.max(difference / np.maximum(magnitude, 1e-30)))}
+
+
+def rows_in_parallel(function, ggml_type, weights, rows, columns, *operands, threads=None):
+    """Runs an oracle product `function(ggml_type, weights, rows, columns, *operands)` over row chunks on all host
+    threads (every output row is independent, so chunking changes no value) and joins the [tokens, rows] results.
+    Functions that return (value, magnitude) pairs are joined element-wise."""
+    import concurrent.futures
+    import os
+
+    threads = threads or os.cpu_count() or 1
+    row_bytes = weights.size // rows
+    chunk = max(1, -(-rows // (threads * 4)))
+    spans = [(first, min(chunk, rows - first)) for first in range(0, rows, chunk)]
+
+    def run(span):
+        first, count = span
+        return function(ggml_type, weights[first * row_bytes:(first + count) * row_bytes], count, columns, *operands)
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=threads) as pool:
+        parts = list(pool.map(run, spans))
+    if isinstance(parts[0], tuple):
+        return tuple(np.concatenate([p[i] for p in parts], axis=1) for i in range(len(parts[0])))
+    return np.concatenate(parts, axis=1)

@@ -79,6 +79,35 @@ def test_shapes_are_validated_before_any_device_work(lib):
     assert lib.raw.syn_b200_quantize_q8(x.ctypes.data, 1, 33, 33, x.ctypes.data, x.ctypes.data) == 2
 
 
+@pytest.mark.parametrize("ggml_type,block_bytes,offsets", [(8, 34, (0,)), (12, 144, (0, 2)), (14, 210, (208,))])
+def test_blocks_with_a_non_finite_scale_are_refused_at_load(lib, ggml_type, block_bytes, offsets):
+    """BlockSourceDecoder.Decode (src/Synapse.Runtime/Features/ModelPackages/SourceFormats/SourceTensorDecoders.cs:134-146,
+    161-172) validates every block's fp16 fields before decoding; the loader does the same before any device work and
+    names the first offending block."""
+    from synapse_b200 import synth
+
+    rows, columns = 3, 512
+    good = synth.matrix(ggml_type, rows, columns, seed=9)
+    blocks_per_row = columns // sb.BLOCK_VALUES[ggml_type]
+    handle = ctypes.c_void_p()
+    for offset in offsets:
+        for bits in (0x7C00, 0xFC00, 0x7E01):  # +inf, -inf, a NaN
+            bad = good.copy()
+            block = blocks_per_row + 1  # second block of the second row
+            bad[block * block_bytes + offset] = bits & 0xFF
+            bad[block * block_bytes + offset + 1] = bits >> 8
+            assert lib.raw.syn_b200_matrix_create(bad.ctypes.data, ggml_type, rows, columns, 0, ctypes.byref(handle)) == 2
+            assert f"block {block} fails validation: InvalidScale" in lib.last_error()
+            assert not handle.value
+    # the largest finite half is fine: the call gets as far as looking for a device
+    edge = good.copy()
+    edge[offsets[0]], edge[offsets[0] + 1] = 0xFF, 0x7B
+    status = lib.raw.syn_b200_matrix_create(edge.ctypes.data, ggml_type, rows, columns, 0, ctypes.byref(handle))
+    assert status in (0, 3)
+    if status == 0:
+        lib.raw.syn_b200_matrix_destroy(handle)
+
+
 def test_host_wrappers_reject_bad_arguments_without_a_device():
     with pytest.raises(ValueError):
         sb.Q8ActivationBuffer(33)

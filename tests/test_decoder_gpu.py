@@ -136,3 +136,42 @@ def test_single_kernel_step_over_a_long_run_and_two_sessions(monkeypatch):
                     assert a.tobytes() == b.tobytes(), (position, slot)
                     tokens[slot] = int(np.argmax(a)) if position % 7 else (position * 13 + slot) % 768
     assert sb.library().device_faults() == 0
+
+
+def test_7b_shaped_step_in_both_forms_against_the_cpu_executor(oracle, monkeypatch):
+    """The step the end-to-end benchmark figure comes from, cut to two layers: hidden 3584, feed-forward 18944, 28 query
+    and 4 key/value heads of 128, the 152064-row vocabulary, Q4_K_M encodings. Both forms of the step -- one persistent
+    kernel, and one kernel per operation -- are compared with the reference's optimized CPU executor (oracle O8) at
+    positions 0..5 and again beyond position 100, by the reference's GPU-vs-reference criterion: worst error within 0.2 %
+    of the logits range and the same greedy token (MetalBackendTests.cs:59-60). A greedy token may differ only where the
+    oracle's own two best logits are closer together than the deviation measured at that step, which is reported."""
+    shape = dict(dec.QWEN25_7B, layers=2, context=128)
+    image = dec.ModelImage(**shape, matrix_types=dec.Q4KM_TYPES, embedding_type=synth.Q4_K, output_type=synth.Q4_K, seed=17, bias=True)
+    reference = oracle.Decoder(image.desc(), image.shape["vocabulary"])
+    monkeypatch.setenv("SYN_B200_DECODE_PROGRAM", "1")
+    with dec.Decoder(image) as program:
+        monkeypatch.setenv("SYN_B200_DECODE_PROGRAM", "0")
+        with dec.Decoder(image) as kernels:
+            monkeypatch.delenv("SYN_B200_DECODE_PROGRAM")
+            lib = sb.library()
+            before = lib.launch_count()
+            program.decode(11, 0)
+            assert lib.launch_count() - before == 1, "the 7B-shaped single-token step is one kernel launch"
+            token, worst = 11, 0.0
+            for position in range(104):
+                want = reference.decode(token, position)
+                checked = position < 6 or position >= 100
+                a, b = program.decode(token, position), kernels.decode(token, position)
+                assert a.tobytes() == b.tobytes(), f"the two step forms differ at position {position}"
+                if checked:
+                    span = float(want.max() - want.min())
+                    error = float(np.abs(a - want).max() / span)
+                    top2 = np.sort(want)[-2:]
+                    gap = float((top2[1] - top2[0]) / span)
+                    worst = max(worst, error)
+                    assert error <= 2e-3, (position, error)
+                    assert int(np.argmax(a)) == oracle.Decoder.argmax(want) or gap <= 2 * error, (position, error, gap)
+                token = oracle.Decoder.argmax(want) if position % 5 else (position * 7919 + 13) % image.shape["vocabulary"]
+            print(f"7B-shaped two-layer step: worst error {worst:.2e} of the logits range over positions 0..5 and 100..103")
+    reference.close()
+    assert sb.library().device_faults() == 0
