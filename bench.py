@@ -34,6 +34,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+import bench_extras  # noqa: E402
 from synapse_b200 import sharding, synth  # noqa: E402
 
 METRIC = "k-quant decode matvec weight bandwidth (Qwen2.5-7B Q4_K_M set, batch 1)"
@@ -455,8 +456,8 @@ def main():
                     up_whole.matmul_q8_device(aligned(scratch[hidden]), 1, expected["up"].data_ptr(), ffn, stream=stream.cuda_stream)
                 stream.synchronize()
         for name in vectors:
-            if (name in ("gate", "up")) == fused_regions:
-                continue
+            if name in (("gate", "up") if fused_regions else ("ffn",)):
+                continue  # vectors this form of the step does not produce
             checks += 1
             if not torch.equal(out_full[name], expected[name]):
                 mismatches += 1
@@ -645,29 +646,8 @@ def main():
     extras = None
     if world == 1 and not args.no_e2e:
         extras = {}
-        # prefill: the tensor-core product on one gate matrix (18944 x 3584 Q4_K) at 2048 tokens
-        gate_offset = image.layers[0].gate
-        gate_bytes = 18944 * synth.row_bytes(synth.Q4_K, 3584)
-        tokens = 2048
-        with sb.QuantizedMatrix(image.weights[gate_offset:gate_offset + gate_bytes], synth.Q4_K, 18944, 3584) as gate:
-            xs = torch.randn(tokens, 3584, device=device)
-            ys = torch.empty(tokens, 18944, device=device)
-            need = lib.gemm_scratch_bytes(tokens, 3584)
-            work = torch.empty(need + 256, dtype=torch.uint8, device=device)
-            work_ptr = (work.data_ptr() + 255) // 256 * 256
-            with torch.cuda.stream(stream):
-                for _ in range(3):
-                    gate.gemm_device(xs.data_ptr(), tokens, 3584, ys.data_ptr(), 18944, work_ptr, need, stream=stream.cuda_stream)
-                g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                g0.record(stream)
-                for _ in range(10):
-                    gate.gemm_device(xs.data_ptr(), tokens, 3584, ys.data_ptr(), 18944, work_ptr, need, stream=stream.cuda_stream)
-                g1.record(stream)
-                stream.synchronize()
-            gemm_ms = g0.elapsed_time(g1) / 10
-            extras["prefill"] = {"workload": "Q4_K 18944x3584 x 2048 tokens, fp16 operands, FP32 accumulate (activation conversion included)",
-                                 "tflops": 2.0 * tokens * 18944 * 3584 / (gemm_ms * 1e-3) / 1e12, "ms": gemm_ms}
-            del xs, ys, work
+        # config 3: the tensor-core product over the token counts and matrices the baseline names
+        extras["prefill"] = bench_extras.prefill_sweep(sb, lib, torch, device, stream, ROOT)
         # config 1: the Qwen2.5-0.5B-shaped all-Q8_0 decode step through the decoder, greedy pick on the device
         small = dec.ModelImage(**dec.QWEN25_05B, context=64, matrix_types=dec.Q8_TYPES, seed=101)
         with dec.Decoder(small) as model:
@@ -731,10 +711,33 @@ def main():
         }
         # several tokens per launch (batched decode, speculative verification): every weight is read once per launch
         extras["matvec_q4_k_18944x3584_tokens"] = {str(t): kernel_rate(synth.Q4_K, 18944, 3584, 4, tokens=t) for t in (2, 4, 8)}
+        # the FP32-activation contract of the reference backend on the two big layer shapes
+        extras["matvec_xf32_batch1"] = bench_extras.xf32_rates(sb, lib, torch, device, stream, peak)
+
+    # config 4 at this N: the 70B-class shapes and the vocabulary projection, row-sharded, at 1 / 8 / 64 columns
+    if not args.no_e2e:
+        if world > 1:
+            for entry in matrices:
+                entry[5].close()
+            dist.barrier()  # nobody stores into a peer's buffer any more
+            if peers is not None:
+                out_full = None
+                peers.close()
+                peers = None
+            dist.barrier()
+        sweep = bench_extras.config4_sweep(sb, lib, torch, dist, device, stream, world, rank, peak, args.gather == "peer")
+        if extras is None:
+            extras = {}
+        extras["config4_row_sharded_sweep"] = sweep
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = run_cpu_baseline()
+        if extras is not None:
+            # the oracle as the checker (counts for the record; the assertions are in tests/) and the reference's AVX2
+            # Q8_0 x Q8_0 kernel on the host cores for configs 0 and 1
+            extras["parity"] = bench_extras.parity_summary(sb, torch)
+            extras["cpu_avx2_q8_0"] = bench_extras.cpu_avx2_baseline()
 
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),

@@ -63,8 +63,9 @@ extern "C" {
 #define SYN_B200_EPILOGUE_ACCUMULATE 1u /* y += W x (residual add) */
 
 /* Operand precision of the tensor-core product. */
-#define SYN_B200_GEMM_F16 0u  /* weights and activations rounded to fp16, FP32 accumulation */
-#define SYN_B200_GEMM_BF16 1u /* weights and activations rounded to bf16, FP32 accumulation */
+#define SYN_B200_GEMM_F16 0u   /* weights and activations rounded to fp16, FP32 accumulation */
+#define SYN_B200_GEMM_F16X2 1u /* both operands carried as fp16 high + low parts (22 bits), three MMAs per k step: the FP32-activation
+                                  product of the reference up to FP32 accumulation order, at about a third of the F16 rate */
 
 /* Mirrors GpuDeviceInfo (native/synapse-gpu/src/Features/GpuKernels/mod.rs:20-31), 152 bytes. */
 typedef struct syn_b200_device_info {

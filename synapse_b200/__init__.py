@@ -26,7 +26,7 @@ Q8_0, Q4_K, Q6_K = 8, 12, 14
 REPACK = 1
 MODE_XQ8, MODE_XF32 = 0, 1
 EPILOGUE_STORE, EPILOGUE_ACCUMULATE = 0, 1
-GEMM_F16, GEMM_BF16 = 0, 1
+GEMM_F16, GEMM_F16X2 = 0, 1
 EXPECTED_ABI_VERSION = 1
 BLOCK_VALUES = {Q8_0: 32, Q4_K: 256, Q6_K: 256}
 BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q6_K: 210}

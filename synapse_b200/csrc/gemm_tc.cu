@@ -18,6 +18,8 @@
 // completion (with wrong results) instead of hanging, and the tensor memory it holds is always released.
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace syn {
@@ -128,8 +130,9 @@ __device__ __forceinline__ uint32_t swizzled(uint32_t r, uint32_t c) { return r 
 // ------------------------------------------------------------------------------------------------------
 
 __global__ void convert_activations_kernel(const float *__restrict__ x, uint64_t tokens, uint64_t in_stride, uint32_t k_tiles,
-                                           uint32_t token_tiles, uint8_t *__restrict__ tiles)
+                                           uint32_t token_tiles, uint8_t *__restrict__ tiles, uint8_t *__restrict__ low_tiles)
 {
+    // `low_tiles` (null for plain fp16 operands) receives fp16(x - fp16(x)): with it an activation carries 22 bits.
     const uint64_t chunks = (uint64_t)token_tiles * k_tiles * kTileTokens * 8;
     for (uint64_t index = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; index < chunks; index += (uint64_t)gridDim.x * blockDim.x) {
         const uint32_t c = (uint32_t)(index & 7);
@@ -138,7 +141,7 @@ __global__ void convert_activations_kernel(const float *__restrict__ x, uint64_t
         const uint32_t kt = (uint32_t)(tile % k_tiles);
         const uint64_t tt = tile / k_tiles;
         const uint64_t token = tt * kTileTokens + n;
-        uint4 out = make_uint4(0, 0, 0, 0);
+        uint4 out = make_uint4(0, 0, 0, 0), low = make_uint4(0, 0, 0, 0);
         if (token < tokens) {
             const float *source = x + token * in_stride + (uint64_t)kt * kTileK + c * 8;
             const float4 lo = __ldg(reinterpret_cast<const float4 *>(source));
@@ -147,8 +150,18 @@ __global__ void convert_activations_kernel(const float *__restrict__ x, uint64_t
             const __half2 h2 = __floats2half2_rn(hi.x, hi.z), h3 = __floats2half2_rn(hi.y, hi.w);
             out = make_uint4(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1),
                              *reinterpret_cast<const uint32_t *>(&h2), *reinterpret_cast<const uint32_t *>(&h3));
+            if (low_tiles) {
+                const float2 f0 = __half22float2(h0), f1 = __half22float2(h1), f2 = __half22float2(h2), f3 = __half22float2(h3);
+                const __half2 l0 = __floats2half2_rn(lo.x - f0.x, lo.z - f0.y), l1 = __floats2half2_rn(lo.y - f1.x, lo.w - f1.y);
+                const __half2 l2 = __floats2half2_rn(hi.x - f2.x, hi.z - f2.y), l3 = __floats2half2_rn(hi.y - f3.x, hi.w - f3.y);
+                low = make_uint4(*reinterpret_cast<const uint32_t *>(&l0), *reinterpret_cast<const uint32_t *>(&l1),
+                                 *reinterpret_cast<const uint32_t *>(&l2), *reinterpret_cast<const uint32_t *>(&l3));
+            }
         }
         *reinterpret_cast<uint4 *>(tiles + tile * kTileABytes + swizzled(n, c)) = out;
+        if (low_tiles) {
+            *reinterpret_cast<uint4 *>(low_tiles + tile * kTileABytes + swizzled(n, c)) = low;
+        }
     }
 }
 
@@ -192,7 +205,26 @@ __device__ __forceinline__ uint4 load16(const uint8_t *p)
 }
 __device__ __forceinline__ uint32_t load_u16(const uint8_t *p) { return __ldg(reinterpret_cast<const unsigned short *>(p)); }
 
+// Splits eight FP32 weights (times the prescale) into fp16 high and low parts, packed in the (0, 2, 1, 3) order of a chunk.
+__device__ __forceinline__ void split_chunk(const float *w, uint4 &high, uint4 &low)
+{
+    uint32_t h[4], l[4];
+#pragma unroll
+    for (int pair = 0; pair < 4; ++pair) {
+        // values (0, 2), (1, 3), (4, 6), (5, 7)
+        const int first = (pair & 1) + 4 * (pair >> 1);
+        const float a = w[first] * kPrescale, b = w[first + 2] * kPrescale;
+        const __half2 hi = __floats2half2_rn(a, b);
+        const float2 back = __half22float2(hi);
+        h[pair] = h2_bits(hi);
+        l[pair] = h2_bits(__floats2half2_rn(a - back.x, b - back.y));
+    }
+    high = make_uint4(h[0], h[1], h[2], h[3]);
+    low = make_uint4(l[0], l[1], l[2], l[3]);
+}
+
 struct DequantQ4K {
+    static constexpr int kAhead = 3;  // k steps of raw blocks a dequant thread keeps in flight (12 registers each)
     struct Raw {
         uint4 header, q0, q1;
     };
@@ -233,6 +265,21 @@ struct DequantQ4K {
             out[c] = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
         }
     }
+    // The same 32 weights in FP32, exactly as the reference decodes them: (d * sc) * q - dmin * m (GgufKQuantBlocks.cs:99-121).
+    static __device__ __forceinline__ void expand_f32(const Raw &raw, uint32_t kt, uint32_t half, float (&w)[32])
+    {
+        const float d = __half2float(__ushort_as_half((unsigned short)(raw.header.x & 0xffff)));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(raw.header.x >> 16)));
+        uint32_t sc, mn;
+        q4k_scale_min(raw.header.y, raw.header.z, raw.header.w, 2 * (kt & 3) + half, sc, mn);
+        const float d1 = __fmul_rn(d, (float)sc), m1 = __fmul_rn(dmin, (float)mn);
+        const uint32_t words[8] = {raw.q0.x, raw.q0.y, raw.q0.z, raw.q0.w, raw.q1.x, raw.q1.y, raw.q1.z, raw.q1.w};
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const uint32_t q = (words[i / 4] >> (8 * (i & 3) + 4 * half)) & 0xF;
+            w[i] = __fsub_rn(__fmul_rn(d1, (float)q), m1);
+        }
+    }
 };
 
 // Q6_K: k tile kt is quarter kt%4 of super-block kt/4: half h = (kt%4)/2 of the block, nibble g = kt%2 of its 64 ql
@@ -240,6 +287,7 @@ struct DequantQ4K {
 // (GgufKQuantBlocks.cs:155-177). value = d * sc[8h + 4g + i/16] * (q - 32).
 template <bool PLANAR>
 struct DequantQ6K {
+    static constexpr int kAhead = 2;  // 26 registers per step
     struct Raw {
         uint4 ql[4], qh[2];
         uint32_t scales;  // the four int8 scales of this k tile
@@ -300,11 +348,31 @@ struct DequantQ6K {
             out[c] = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
         }
     }
+    // The same 32 weights in FP32 as the reference decodes them: (d * sc) * (q - 32) (GgufKQuantBlocks.cs:155-177).
+    static __device__ __forceinline__ void expand_f32(const Raw &raw, uint32_t kt, uint32_t part, float (&w)[32])
+    {
+        const uint32_t g = kt & 1;
+        const float d = __half2float(__ushort_as_half((unsigned short)raw.d));
+        const uint32_t ql[8] = {part ? raw.ql[2].x : raw.ql[0].x, part ? raw.ql[2].y : raw.ql[0].y, part ? raw.ql[2].z : raw.ql[0].z,
+                                part ? raw.ql[2].w : raw.ql[0].w, part ? raw.ql[3].x : raw.ql[1].x, part ? raw.ql[3].y : raw.ql[1].y,
+                                part ? raw.ql[3].z : raw.ql[1].z, part ? raw.ql[3].w : raw.ql[1].w};
+        const uint32_t qh[8] = {raw.qh[0].x, raw.qh[0].y, raw.qh[0].z, raw.qh[0].w, raw.qh[1].x, raw.qh[1].y, raw.qh[1].z, raw.qh[1].w};
+        const uint32_t high_shift = 4 * g + 2 * part;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int scale = (int)(signed char)((raw.scales >> (8 * (2 * part + i / 16))) & 0xff);
+            const uint32_t byte = (ql[i / 4] >> (8 * (i & 3))) & 0xff;
+            const uint32_t nibble = g ? byte >> 4 : byte & 0xF;
+            const uint32_t high = (qh[i / 4] >> (8 * (i & 3) + high_shift)) & 3;
+            w[i] = __fmul_rn(__fmul_rn(d, (float)scale), (float)((int)(nibble | (high << 4)) - 32));
+        }
+    }
 };
 
 // Q8_0: k tile kt is blocks 2kt and 2kt+1 of the row; value = d * code (GgufLegacyBlocks.cs:85-92).
 template <bool PLANAR>
 struct DequantQ8 {
+    static constexpr int kAhead = 3;
     struct Raw {
         uint4 codes[4];
         uint32_t d0, d1;  // fp16 bits of the two block scales
@@ -354,6 +422,17 @@ struct DequantQ8 {
             out[c] = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
         }
     }
+    // The same 32 weights in FP32: d * code (GgufLegacyBlocks.cs:85-92).
+    static __device__ __forceinline__ void expand_f32(const Raw &raw, uint32_t, uint32_t part, float (&w)[32])
+    {
+        const float d = __half2float(__ushort_as_half((unsigned short)(part ? raw.d1 : raw.d0)));
+        const uint4 lo = part ? raw.codes[2] : raw.codes[0], hi = part ? raw.codes[3] : raw.codes[1];
+        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            w[i] = __fmul_rn(d, (float)(int)(signed char)((words[i / 4] >> (8 * (i & 3))) & 0xff));
+        }
+    }
 };
 
 // ------------------------------------------------------------------------------------------------------
@@ -367,7 +446,8 @@ struct GemmArgs {
     uint64_t columns;
     uint64_t rows, tokens;
     uint32_t k_tiles, row_tiles, token_tiles;
-    const uint8_t *x_tiles;  // converted activations
+    const uint8_t *x_tiles;      // converted activations
+    const uint8_t *x_tiles_low;  // their low parts (two-part fp16 operands), or null
     float *y;
     uint64_t out_stride;
     uint32_t *fault;
@@ -392,13 +472,18 @@ __device__ __forceinline__ typename DequantQ8<PLANAR>::Row DequantQ8<PLANAR>::ro
     return Row{a.weights + row * a.row_bytes, nullptr};
 }
 
-template <class Dequant, int N, int TT>
+// SPLIT: both operands are carried as fp16 high + low parts (22 bits) and a k step issues three MMAs, high x high,
+// low x high and high x low, into the same accumulator: the result then differs from the FP32-activation product of the
+// reference by FP32 accumulation order only. A stage holds A high, A low, B high, B low (16 KB each, N = 128, one token tile).
+template <class Dequant, int N, int TT, bool SPLIT = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
 {
     static_assert(N == 128 || N == 256, "the weight-row tile is 128 or 256");
     static_assert(TT == 1 || TT == 2, "one or two token tiles per CTA tile");
+    static_assert(!SPLIT || (N == 128 && TT == 1), "two-part operands use 128-row tiles and one token tile");
     constexpr uint32_t kTileRows = N;
-    constexpr uint32_t kStages = stage_count(TT), kStageBytes = stage_bytes(TT);
+    constexpr uint32_t kStages = SPLIT ? 3 : stage_count(TT), kStageBytes = SPLIT ? 4 * kTileABytes : stage_bytes(TT);
+    constexpr uint32_t kTileBOffset = SPLIT ? 2 * kTileABytes : TT * kTileABytes;  // where the weight tile starts inside a stage
     constexpr uint32_t kBuffers = TT == 1 ? 2 : 1;  // accumulator sets that can be in flight
     extern __shared__ __align__(1024) uint8_t shared_raw[];
     // the dynamic window is only guaranteed 16-byte alignment; the swizzle needs 1024
@@ -441,10 +526,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                     if (round > 0) {
                         mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.fault);
                     }
-                    mbar_expect_tx(full0 + 8 * s, live * kTileABytes);
+                    mbar_expect_tx(full0 + 8 * s, (SPLIT ? 2 : live) * kTileABytes);
                     for (uint32_t i = 0; i < live; ++i) {
                         bulk_copy(smem_u32(stages + s * kStageBytes + i * kTileABytes), a.x_tiles + ((tt0 + i) * a.k_tiles + kt) * kTileABytes,
                                   kTileABytes, full0 + 8 * s);
+                    }
+                    if (SPLIT) {
+                        bulk_copy(smem_u32(stages + s * kStageBytes + kTileABytes), a.x_tiles_low + (tt0 * a.k_tiles + kt) * kTileABytes, kTileABytes,
+                                  full0 + 8 * s);
                     }
                     if (++s == kStages) {
                         s = 0;
@@ -469,9 +558,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                     mbar_wait(full0 + 8 * s, phase, a.fault);
                     tc_fence_after();
                     const uint32_t stage = smem_u32(stages + s * kStageBytes);
-                    const uint64_t desc_b = smem_desc(stage + TT * kTileABytes);
+                    const uint64_t desc_b = smem_desc(stage + kTileBOffset);
+                    if (SPLIT) {
+                        const uint64_t a_high = smem_desc(stage), a_low = smem_desc(stage + kTileABytes), b_low = smem_desc(stage + kTileBOffset + kTileABytes);
 #pragma unroll
-                    for (uint32_t i = 0; i < (uint32_t)TT; ++i) {
+                        for (uint32_t k = 0; k < kTileK / 16; ++k) {
+                            umma_f16(tmem_d, a_high + 2 * k, desc_b + 2 * k, instr_desc(N), (kt | k) != 0 ? 1u : 0u);
+                            umma_f16(tmem_d, a_low + 2 * k, desc_b + 2 * k, instr_desc(N), 1u);
+                            umma_f16(tmem_d, a_high + 2 * k, b_low + 2 * k, instr_desc(N), 1u);
+                        }
+                    }
+#pragma unroll
+                    for (uint32_t i = 0; i < (SPLIT ? 0u : (uint32_t)TT); ++i) {
                         if (i < live) {
                             const uint64_t desc_a = smem_desc(stage + i * kTileABytes);
 #pragma unroll
@@ -497,25 +595,55 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
         const uint32_t dq = threadIdx.x - 128;
         const uint32_t r = dq % kTileRows, part = dq / kTileRows;  // part is 0 when N = 256
         constexpr uint32_t kParts = 256 / kTileRows;               // threads per row
+        constexpr int kAhead = Dequant::kAhead;                    // k steps whose raw blocks are in flight
         uint32_t s = 0, round = 0;
-        typename Dequant::Raw next;
-        uint64_t tile = blockIdx.x;
-        typename Dequant::Row row{};
-        if (tile < tiles) {
-            row = Dequant::row_of(a, min((tile % a.row_tiles) * kTileRows + r, a.rows - 1));
-            Dequant::load(row, 0, next);
+        const uint32_t my_tiles = tiles > blockIdx.x ? (uint32_t)((tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+        const uint64_t steps = (uint64_t)my_tiles * a.k_tiles;
+        // The raw blocks of the next kAhead k steps (across tile boundaries) are fetched before the current ones are
+        // expanded: with one token tile a k step is shorter than an L2 round trip, and one step of lookahead left the
+        // dequantisers waiting for memory on every step.
+        typename Dequant::Raw ahead[kAhead];
+        uint64_t fetch_tile = blockIdx.x;
+        uint32_t fetch_kt = 0;
+        uint64_t fetched = 0;
+        typename Dequant::Row fetch_row{};
+        auto fetch = [&](typename Dequant::Raw &destination) {
+            if (fetch_kt == 0) {
+                fetch_row = Dequant::row_of(a, min((fetch_tile % a.row_tiles) * kTileRows + r, a.rows - 1));
+            }
+            Dequant::load(fetch_row, fetch_kt, destination);
+            if (++fetch_kt == a.k_tiles) {
+                fetch_kt = 0;
+                fetch_tile += gridDim.x;
+            }
+            ++fetched;
+        };
+#pragma unroll
+        for (int d = 0; d < kAhead; ++d) {
+            if (fetched < steps) {
+                fetch(ahead[d]);
+            }
         }
-        for (; tile < tiles; tile += gridDim.x) {
-            for (uint32_t kt = 0; kt < a.k_tiles; ++kt) {
-                const typename Dequant::Raw raw = next;
-                if (kt + 1 < a.k_tiles) {
-                    Dequant::load(row, kt + 1, next);
-                } else if (tile + gridDim.x < tiles) {
-                    row = Dequant::row_of(a, min(((tile + gridDim.x) % a.row_tiles) * kTileRows + r, a.rows - 1));
-                    Dequant::load(row, 0, next);
+        uint32_t kt = 0;
+        for (uint64_t step0 = 0; step0 < steps; step0 += kAhead) {
+#pragma unroll
+            for (int d = 0; d < kAhead; ++d) {
+                if (step0 + d >= steps) {
+                    break;
+                }
+                const typename Dequant::Raw raw = ahead[d];
+                if (fetched < steps) {
+                    fetch(ahead[d]);
                 }
                 uint4 v[2][4];
-                if (kParts == 1) {
+                if (SPLIT) {
+                    float w[32];
+                    Dequant::expand_f32(raw, kt, part, w);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        split_chunk(w + 8 * c, v[0][c], v[1][c]);
+                    }
+                } else if (kParts == 1) {
                     Dequant::expand(raw, kt, 0, v[0]);
                     Dequant::expand(raw, kt, 1, v[1]);
                 } else {
@@ -524,10 +652,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                 if (round > 0) {
                     mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.fault);
                 }
-                uint8_t *tile_b = stages + s * kStageBytes + TT * kTileABytes;
+                uint8_t *tile_b = stages + s * kStageBytes + kTileBOffset;
 #pragma unroll
                 for (uint32_t c = 0; c < 4; ++c) {
-                    if (kParts == 1) {
+                    if (SPLIT) {
+                        *reinterpret_cast<uint4 *>(tile_b + swizzled(r, 4 * part + c)) = v[0][c];
+                        *reinterpret_cast<uint4 *>(tile_b + kTileABytes + swizzled(r, 4 * part + c)) = v[1][c];
+                    } else if (kParts == 1) {
                         *reinterpret_cast<uint4 *>(tile_b + swizzled(r, c)) = v[0][c];
                         *reinterpret_cast<uint4 *>(tile_b + swizzled(r, 4 + c)) = v[1][c];
                     } else {
@@ -543,6 +674,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                 if (++s == kStages) {
                     s = 0;
                     ++round;
+                }
+                if (++kt == a.k_tiles) {
+                    kt = 0;
                 }
             }
         }
@@ -600,24 +734,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
 constexpr uint32_t kGemmSharedBytes = 4 * stage_bytes(1) + 1024;  // = 3 * stage_bytes(2) + 1024
 static_assert(4 * stage_bytes(1) == 3 * stage_bytes(2), "both tile shapes use the same shared-memory budget");
 
-template <class Dequant, int N, int TT>
+template <class Dequant, int N, int TT, bool SPLIT = false>
 cudaError_t run_gemm_shape(const GemmArgs &a, uint64_t ctas, cudaStream_t stream)
 {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t error = cudaFuncSetAttribute(gemm_tc_kernel<Dequant, N, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSharedBytes);
+    // the shared-memory limit of a kernel is a per-device attribute: set it once on every device the library meets
+    static std::atomic<uint64_t> configured{0};
+    int device = 0;
+    cudaGetDevice(&device);
+    const uint64_t bit = 1ull << (device & 63);
+    if ((configured.load() & bit) == 0) {
+        cudaError_t error = cudaFuncSetAttribute(gemm_tc_kernel<Dequant, N, TT, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSharedBytes);
         if (error != cudaSuccess) {
             return error;
         }
-        configured = true;
+        configured.fetch_or(bit);
     }
-    gemm_tc_kernel<Dequant, N, TT><<<(unsigned)ctas, kGemmThreads, kGemmSharedBytes, stream>>>(a);
+    gemm_tc_kernel<Dequant, N, TT, SPLIT><<<(unsigned)ctas, kGemmThreads, kGemmSharedBytes, stream>>>(a);
     return cudaGetLastError();
 }
 
 template <class Dequant>
 cudaError_t run_gemm(const GemmArgs &a, int n, int tt, uint64_t ctas, cudaStream_t stream)
 {
+    if (a.x_tiles_low) {
+        return run_gemm_shape<Dequant, 128, 1, true>(a, ctas, stream);
+    }
     if (tt == 2) {
         return n == 256 ? run_gemm_shape<Dequant, 256, 2>(a, ctas, stream) : run_gemm_shape<Dequant, 128, 2>(a, ctas, stream);
     }
@@ -630,15 +771,16 @@ uint64_t gemm_scratch_bytes(uint64_t tokens, uint64_t columns)
 {
     const uint64_t token_tiles = (tokens + kTileTokens - 1) / kTileTokens;
     const uint64_t k_tiles = (columns + kTileK - 1) / kTileK;
-    return align_up(token_tiles * k_tiles * kTileABytes, 256);
+    return 2 * align_up(token_tiles * k_tiles * kTileABytes, 256);  // room for the low parts of two-part operands
 }
 
 int32_t launch_gemm(const syn_b200_matrix *m, const float *x, uint64_t tokens, uint64_t in_stride, float *y, uint64_t out_stride,
                     uint32_t precision, void *scratch, uint64_t scratch_bytes, cudaStream_t stream)
 {
-    if (precision != SYN_B200_GEMM_F16) {
-        return fail(SYN_B200_INVALID_ARGUMENT, "only the fp16-operand tensor-core product is built (precision " + std::to_string(precision) + ")");
+    if (precision != SYN_B200_GEMM_F16 && precision != SYN_B200_GEMM_F16X2) {
+        return fail(SYN_B200_INVALID_ARGUMENT, "unknown tensor-core precision " + std::to_string(precision));
     }
+    const bool split = precision == SYN_B200_GEMM_F16X2;
     if (in_stride < m->columns || in_stride % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15)) {
         return fail(SYN_B200_INVALID_ARGUMENT, "device activations must be 16-byte aligned with a stride that covers the row and is a multiple of 4 floats");
     }
@@ -664,12 +806,13 @@ int32_t launch_gemm(const syn_b200_matrix *m, const float *x, uint64_t tokens, u
     // Two token tiles per CTA tile when there are at least two (a weight tile is then dequantised once per 256
     // tokens); 256-row tiles unless that leaves SMs without a tile and 128-row tiles would not.
     const uint64_t sms = (uint64_t)sm_count(m->device);
-    const int tt = a.token_tiles >= 2 ? 2 : 1;
+    const int tt = a.token_tiles >= 2 && !split ? 2 : 1;
     const uint64_t token_groups = (a.token_tiles + tt - 1) / tt;
     const uint64_t tiles256 = ((m->rows + 255) / 256) * token_groups;
-    const int n = tiles256 >= sms ? 256 : 128;
+    const int n = tiles256 >= sms && !split ? 256 : 128;
     a.row_tiles = (uint32_t)((m->rows + n - 1) / n);
     a.x_tiles = static_cast<const uint8_t *>(scratch);
+    a.x_tiles_low = split ? a.x_tiles + need / 2 : nullptr;
     a.y = y;
     a.out_stride = out_stride;
     a.fault = fault_word_device();
@@ -679,7 +822,8 @@ int32_t launch_gemm(const syn_b200_matrix *m, const float *x, uint64_t tokens, u
     if (blocks > sms * 16) {
         blocks = sms * 16;
     }
-    convert_activations_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, tokens, in_stride, a.k_tiles, a.token_tiles, static_cast<uint8_t *>(scratch));
+    convert_activations_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, tokens, in_stride, a.k_tiles, a.token_tiles, static_cast<uint8_t *>(scratch),
+                                                                   split ? static_cast<uint8_t *>(scratch) + need / 2 : nullptr);
     count_launch();
     cudaError_t error = cudaGetLastError();
     if (error != cudaSuccess) {

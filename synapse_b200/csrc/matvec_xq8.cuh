@@ -249,7 +249,6 @@ cudaError_t launch_team(const MatvecArgs &a, const WeightView &view, uint64_t du
 // kernel bumps the host-mapped fault word, stops waiting and still runs to completion (with wrong results).
 // ------------------------------------------------------------------------------------------------------
 
-constexpr int kGroupWarps = 12;  // consumer warps of the several-token CTAs (they have the SM to themselves)
 constexpr int kMaxStages = 8;
 constexpr uint64_t kWideBytes = 96ull << 20;  // matrices from this size on get the sixteen-warp CTA
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -321,37 +320,9 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_
 template <int THREADS>
 __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory"); }
 
-// Launches with several tokens keep all tokens' quantised activations in shared memory and sixteen accumulators per
-// lane: they get an SM to themselves (no register cap, twice the shared memory).
-__host__ __device__ constexpr bool roomy(int T, int CW, bool staged) { return (T > 1 && staged) || CW > kWarps; }
-__host__ __device__ constexpr uint32_t stage_budget(int T, bool staged) { return T > 1 && staged ? 200u * 1024u : kStageBudget; }
-
-// Copies the already quantised activations of `live` tokens (global scratch layout) into the shared layout the
-// kernels read: codes piece-swizzled, scales and code sums as they are. Token slots past `live` repeat the last token.
-template <int T>
-__device__ __forceinline__ void stage_activations(const ActView &act, uint64_t token0, uint32_t K, uint32_t live, uint32_t thread,
-                                                  uint32_t threads, const ActShared &dst)
-{
-#pragma unroll
-    for (int t = 0; t < T; ++t) {
-        const uint64_t token = token0 + min((uint32_t)t, live - 1);
-        const uint4 *codes = reinterpret_cast<const uint4 *>(act.codes + token * K);
-        for (uint32_t piece = thread; piece < K / 16; piece += threads) {
-            const uint4 v = __ldg(codes + piece);
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst.codes + swizzled_code_offset((uint32_t)t * K + piece * 16)),
-                         "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                         : "memory");
-        }
-        const float *scales = act.scales + token * (K / 32);
-        for (uint32_t i = thread; i < K / 32; i += threads) {
-            asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst.scales + ((uint32_t)t * (K / 32) + i) * 4), "f"(__ldg(scales + i)) : "memory");
-        }
-        const int16_t *sums = act.sums + token * (K / 16);
-        for (uint32_t i = thread; i < K / 16; i += threads) {
-            asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst.sums + ((uint32_t)t * (K / 16) + i) * 2), "h"(__ldg(sums + i)) : "memory");
-        }
-    }
-}
+// The sixteen-warp CTA has the SM to itself (no register cap).
+__host__ __device__ constexpr bool roomy(int, int CW, bool) { return CW > kWarps; }
+__host__ __device__ constexpr uint32_t stage_budget(int, bool) { return kStageBudget; }
 
 // What one launch multiplies:
 //   kSingle   - a row range of one matrix;
@@ -482,12 +453,7 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
         shared_act.codes = base;
         shared_act.scales = base + shared_act_codes_bytes(T, (uint32_t)K);
         shared_act.sums = shared_act.scales + shared_act_side_bytes(T, (uint32_t)K);
-        if (x) {
-            quantize_to_shared<T>(x + token0 * in_stride, in_stride, (uint32_t)K, live, warp_in_cta, kConsumers, lane, shared_act);
-        } else {
-            // the caller quantised already: bring the tokens of this CTA's group into shared memory
-            stage_activations<T>(act, token0, (uint32_t)K, live, threadIdx.x, kConsumers * 32, shared_act);
-        }
+        quantize_to_shared<T>(x + token0 * in_stride, in_stride, (uint32_t)K, live, warp_in_cta, kConsumers, lane, shared_act);
         consumer_barrier<kConsumers * 32>();
     }
     typename F::Act held[REGS ? UPL : 1];
@@ -697,6 +663,187 @@ matvec_xq8_pipe_kernel(PipeArgs p, ActView act, const float *__restrict__ x, uin
     }
 }
 
+// ------------------------------------------------------------------------------------------------------
+// Several tokens per launch (batched decode, speculative verification, short prompt runs): the tokens of a group are
+// spread over the warp teams of the CTA instead of being looped over inside a warp. A team keeps ITS token's slice of
+// the quantised activations in registers for the whole launch -- exactly as the single-token kernel does -- and walks
+// the rows of every weight stage: a row costs five shared-memory loads and the dot products, nothing is re-unpacked or
+// re-loaded per token, and every weight byte still crosses HBM once per token group. With `tp` tokens in the group and
+// kTeams teams, kTeams / tp teams share a token and split the rows of a stage between them. A row's summation order is
+// that of a launch of its own (it depends on W and UPL only), so batched results are bit-identical to single-token ones.
+// ------------------------------------------------------------------------------------------------------
+constexpr int kTokenWarps = 16;       // consumer warps of these CTAs (one CTA per SM)
+constexpr uint32_t kTokenStageRows = 16;
+
+template <class F, int W, int UPL, bool GATHER>
+__global__ void __launch_bounds__((kTokenWarps / W) * W * 32 + 32, 1)
+matvec_xq8_tokens_kernel(PipeArgs p, ActView act, uint64_t K, uint64_t rows, uint32_t tokens, uint32_t tp, float *__restrict__ y, uint64_t out_stride,
+                         Epilogue epilogue, uint32_t *fault)
+{
+    constexpr int kTeams = kTokenWarps / W;
+    constexpr int kConsumers = kTeams * W;
+    constexpr uint32_t G = kTokenStageRows;
+    extern __shared__ __align__(128) uint8_t stage_memory[];
+    __shared__ float partial[2][G][kConsumers];
+    __shared__ __align__(8) uint64_t barriers[2 * kMaxStages];  // full[s] then empty[s]
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warp_in_cta = threadIdx.x >> 5;
+    const uint64_t groups = (rows + G - 1) / G;
+    const uint64_t my_groups = groups > blockIdx.x ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t full0 = smem_u32(&barriers[0]), empty0 = smem_u32(&barriers[kMaxStages]);
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.stages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, kConsumers);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    const uint8_t *const bases[4] = {p.global.p0, p.global.p1, p.global.p2, p.global.p3};
+
+    if (warp_in_cta == kConsumers) {
+        if (lane == 0) {
+            const uint64_t policy = l2_evict_first_policy();
+            uint32_t s = 0, round = 0;
+            for (uint32_t it = 0; it < my_groups; ++it) {
+                if (round > 0 && !mbar_wait(empty0 + 8 * s, (round - 1) & 1) && fault) {
+                    atomicAdd(fault, 1u);
+                }
+                const uint64_t row0 = ((uint64_t)blockIdx.x + (uint64_t)it * gridDim.x) * G;
+                const uint64_t n = min((uint64_t)G, rows - row0);
+                uint32_t total = 0, bytes[4];
+                const uint8_t *sources[4];
+#pragma unroll
+                for (int k = 0; k < F::kPlanes; ++k) {
+                    const uint8_t *source = bases[k] + row0 * p.plane_row_bytes[k];
+                    const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(source) & 15);
+                    sources[k] = source - shift;
+                    bytes[k] = (uint32_t)((shift + n * p.plane_row_bytes[k] + 15) & ~(uint64_t)15);
+                    total += bytes[k];
+                }
+                mbar_expect_tx(full0 + 8 * s, total);
+                const uint32_t stage = smem_u32(stage_memory) + s * p.stage_bytes;
+#pragma unroll
+                for (int k = 0; k < F::kPlanes; ++k) {
+                    bulk_copy(stage + p.plane_offset[k], sources[k], bytes[k], full0 + 8 * s, policy);
+                }
+                if (++s == p.stages) {
+                    s = 0;
+                    ++round;
+                }
+            }
+        }
+        return;
+    }
+
+    const uint32_t team_in_cta = warp_in_cta / W;
+    const uint32_t warp_in_team = warp_in_cta % W;
+    const uint32_t sharers = kTeams / tp;                 // teams that share a token (tp <= kTeams)
+    const uint32_t token_slot = team_in_cta % tp;         // which token of the group this team multiplies
+    const uint32_t row_lane = team_in_cta / tp;           // which share of a stage's rows it takes
+    const uint64_t token0 = (uint64_t)blockIdx.y * tp;
+    const uint32_t live = min(tp, tokens - (uint32_t)token0);
+    const bool working = row_lane < sharers && token_slot < live;
+    const uint64_t token = token0 + min(token_slot, live - 1);
+    const uint64_t units = F::units(K);
+
+    pdl_wait();
+    typename F::Act held[UPL];
+    uint64_t u[UPL];
+    bool valid[UPL];
+#pragma unroll
+    for (int j = 0; j < UPL; ++j) {
+        const uint64_t unit = ((uint64_t)warp_in_team * UPL + j) * 32 + lane;
+        valid[j] = unit < units;
+        u[j] = valid[j] ? unit : units - 1;
+        F::template load_act<GlobalMem>(act_global(act), K, token, u[j], held[j]);
+    }
+
+    uint32_t s = 0, phase = 0;
+    for (uint32_t it = 0; it < my_groups; ++it) {
+        const uint64_t group_row0 = ((uint64_t)blockIdx.x + (uint64_t)it * gridDim.x) * G;
+        if (!mbar_wait(full0 + 8 * s, phase) && fault && lane == 0) {
+            atomicAdd(fault, 1u);
+        }
+        SharedView view;
+        view.row_bytes = p.plane_row_bytes[0];
+        {
+            const uint32_t stage = smem_u32(stage_memory) + s * p.stage_bytes;
+            uint32_t local[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int k = 0; k < F::kPlanes; ++k) {
+                const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(bases[k] + group_row0 * p.plane_row_bytes[k]) & 15);
+                local[k] = stage + p.plane_offset[k] + shift;
+            }
+            view.p0 = local[0];
+            view.p1 = local[1];
+            view.p2 = local[2];
+            view.p3 = local[3];
+        }
+        const uint32_t buffer = it & 1;
+        if (working) {
+            for (uint32_t row = row_lane; row < G; row += sharers) {
+                if (group_row0 + row >= rows) {
+                    break;  // rows past the end of the matrix: the stage holds nothing for them
+                }
+                typename F::W wr[UPL];
+#pragma unroll
+                for (int j = 0; j < UPL; ++j) {
+                    F::template load_w<SharedMem>(view, K, (uint64_t)row, u[j], lane, wr[j]);
+                }
+                float acc = 0.0f;
+#pragma unroll
+                for (int j = 0; j < UPL; ++j) {
+                    F::template dot<false>(wr[j], held[j], valid[j], u[j], lane, acc, nullptr);
+                }
+                acc = warp_sum(acc);
+                if (W == 1) {
+                    if (lane == 0) {
+                        store_result<GATHER>(epilogue, y, token, out_stride, group_row0 + row, acc);
+                    }
+                } else if (lane == 0) {
+                    partial[buffer][row][warp_in_cta] = acc;
+                }
+            }
+        }
+        // Give the stage back (see the single-token kernel for the fence).
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(empty0 + 8 * s);
+        }
+        if (++s == p.stages) {
+            s = 0;
+            phase ^= 1;
+        }
+        if (W > 1) {
+            // the team's warps in index order, as in every other kernel; one thread per (row, token) of the stage
+            consumer_barrier<kConsumers * 32>();
+            const uint32_t pairs = G * live;
+            for (uint32_t index = threadIdx.x; index < pairs; index += kConsumers * 32) {
+                const uint32_t row = index / live, slot = index % live;
+                if (group_row0 + row < rows) {
+                    // the team that computed (row, slot): its row lane is row % sharers
+                    const uint32_t team = (row % sharers) * tp + slot;
+                    float total = partial[buffer][row][team * W];
+#pragma unroll
+                    for (int k = 1; k < W; ++k) {
+                        total += partial[buffer][row][team * W + k];
+                    }
+                    store_result<GATHER>(epilogue, y, token0 + slot, out_stride, group_row0 + row, total);
+                }
+            }
+        }
+    }
+    if (GATHER) {
+        consumer_barrier<kConsumers * 32>();
+        if (threadIdx.x == 0) {
+            signal_completion(epilogue);
+        }
+    }
+}
+
 // Lays out a stage for this format and row length; false when a group of rows does not fit the stage budget.
 // `views` holds one view per segment of the launch (one for a plain product).
 template <class F, int W, int R, int CW = kWarps>
@@ -788,6 +935,49 @@ cudaError_t launch_pipe(const MatvecArgs &a, const PipeArgs &p, cudaStream_t str
                          (uint32_t)a.tokens, a.y, a.out_stride, a.fused, fault_word_device());
 }
 
+// The token-parallel kernel on `a.tokens` >= 2 ready-made activations; cudaErrorNotSupported when a stage of
+// kTokenStageRows rows does not fit.
+template <class F, int W, int UPL, bool GATHER>
+cudaError_t launch_token_teams(const MatvecArgs &a, const WeightView &view, cudaStream_t stream)
+{
+    constexpr uint32_t kTeams = kTokenWarps / W;
+    constexpr uint32_t kBudget = 200u * 1024u;
+    PipeArgs p{};
+    p.global = view;
+    p.planes = F::kPlanes;
+    F::plane_row_bytes(a.matrix->columns, a.matrix->row_bytes, p.plane_row_bytes);
+    uint64_t offset = 0;
+    for (int k = 0; k < F::kPlanes; ++k) {
+        p.plane_offset[k] = (uint32_t)offset;
+        offset += align_up((uint64_t)kTokenStageRows * p.plane_row_bytes[k] + 16, 128);
+    }
+    if (offset > kBudget / 2) {
+        return cudaErrorNotSupported;
+    }
+    p.stage_bytes = (uint32_t)offset;
+    const uint64_t stages = kBudget / offset;
+    p.stages = (uint32_t)(stages > kMaxStages ? kMaxStages : stages);
+    auto kernel = matvec_xq8_tokens_kernel<F, W, UPL, GATHER>;
+    static PerDevice configured;
+    if (configured.first_use(a.matrix->device)) {
+        cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBudget);
+        if (error != cudaSuccess) {
+            configured.forget(a.matrix->device);
+            return error;
+        }
+    }
+    // Tokens per group: as many as there are teams at most; fewer tokens leave several teams per token, which split the rows.
+    const uint32_t tp = (uint32_t)(a.tokens < kTeams ? a.tokens : kTeams);
+    uint64_t ctas = (a.row_count + kTokenStageRows - 1) / kTokenStageRows;
+    const uint64_t cap = (uint64_t)sm_count(a.matrix->device);
+    if (ctas > cap) {
+        ctas = cap;
+    }
+    const dim3 grid((unsigned)ctas, (unsigned)((a.tokens + tp - 1) / tp));
+    return launch_kernel(kernel, grid, dim3(kTeams * W * 32 + 32), (size_t)p.stages * p.stage_bytes, stream, p, a.act, a.matrix->columns, a.row_count,
+                         (uint32_t)a.tokens, tp, a.y, a.out_stride, a.fused, fault_word_device());
+}
+
 template <class F, int W, int UPL>
 cudaError_t launch_tokens(const MatvecArgs &a, const WeightView *views, bool one_pass, uint64_t dump_groups, cudaStream_t stream)
 {
@@ -851,30 +1041,20 @@ cudaError_t launch_tokens(const MatvecArgs &a, const WeightView *views, bool one
         // FP32 activations in: the kernel quantises them itself.
         return one_pass ? launch_pipe<F, 1, W, UPL, R, true, true>(a, pipe, stream) : launch_pipe<F, 1, W, UPL, R, false, true>(a, pipe, stream);
     }
-    if constexpr (F::kStageTokens) if (!gather && a.tokens >= 2) {
-        // Several tokens: groups of 8, 4 or 2 tokens (the largest that is needed and whose quantised activations fit
-        // beside the weight ring) share every weight stage; a group's activations sit in shared memory, quantised there
-        // from FP32 or copied from the caller's scratch. Further groups take further grid rows.
-        MatvecArgs grouped = a;
-        if (a.act_ready) {
-            grouped.x = nullptr;  // tells the kernel to copy instead of quantising
-        }
-        const uint32_t budget = stage_budget(2, true);
-        if (a.tokens > 4 && plan_pipe<F, W, R, kGroupWarps>(a, views, shared_act_bytes(8, K32), pipe, budget)) {
-            return launch_pipe<F, 8, W, UPL, R, false, true, kGroupWarps>(grouped, pipe, stream);
-        }
-        if (a.tokens > 2 && plan_pipe<F, W, R, kGroupWarps>(a, views, shared_act_bytes(4, K32), pipe, budget)) {
-            return launch_pipe<F, 4, W, UPL, R, false, true, kGroupWarps>(grouped, pipe, stream);
-        }
-        if (plan_pipe<F, W, R, kGroupWarps>(a, views, shared_act_bytes(2, K32), pipe, budget)) {
-            return launch_pipe<F, 2, W, UPL, R, false, true, kGroupWarps>(grouped, pipe, stream);
-        }
-    }
     if (!a.act_ready) {
-        // Shapes the pipelined kernel does not take: quantise into the caller's scratch first.
+        // Shapes the pipelined kernel does not quantise for: quantise into the caller's scratch first.
         cudaError_t error = launch_quantize(a.x, a.tokens, a.matrix->columns, a.in_stride, const_cast<int8_t *>(a.act.codes),
                                             const_cast<float *>(a.act.scales), const_cast<int16_t *>(a.act.sums), stream);
         if (error != cudaSuccess) {
+            return error;
+        }
+    }
+    // (rows so long that the sixteen warps form fewer teams than there are tokens would need several passes over the
+    // weights: those keep the direct-load kernels, which loop over the tokens inside a warp)
+    if (F::kTokenTeams && a.tokens >= 2 && one_pass && (uint64_t)(kTokenWarps / W) >= (a.tokens < 8 ? a.tokens : 8)) {
+        // Several tokens: one team of warps per token, every team with its token's activations in registers.
+        const cudaError_t error = gather ? launch_token_teams<F, W, UPL, true>(a, view, stream) : launch_token_teams<F, W, UPL, false>(a, view, stream);
+        if (error != cudaErrorNotSupported) {
             return error;
         }
     }
@@ -887,9 +1067,6 @@ cudaError_t launch_tokens(const MatvecArgs &a, const WeightView *views, bool one
     }
     if (!gather && a.tokens <= 1 && plan_pipe<F, W, R>(a, views, 0, pipe)) {
         return one_pass ? launch_pipe<F, 1, W, UPL, R, true, false>(a, pipe, stream) : launch_pipe<F, 1, W, UPL, R, false, false>(a, pipe, stream);
-    }
-    if constexpr (!F::kStageTokens) if (!gather && a.tokens == 2 && plan_pipe<F, W, R>(a, views, 0, pipe)) {
-        return launch_pipe<F, 2, W, UPL, R, false, false>(a, pipe, stream);  // activations read from the scratch as they are
     }
     // Token group size: the smallest of 1, 2, 4, 8 that holds the tokens (step/projection.rs:82-87).
     if (a.tokens <= 1) {

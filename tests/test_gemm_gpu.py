@@ -62,7 +62,43 @@ def test_tensor_core_product_respects_strides_and_leaves_gaps_alone():
         assert np.array_equal(strided[:, :rows], dense) and np.all(strided[:, rows:] == 12345.0)
         assert lib.raw.syn_b200_gemm(matrix.handle, x.ctypes.data, tokens, columns, strided.ctypes.data, rows - 1, sb.GEMM_F16) == 2
         assert lib.raw.syn_b200_gemm(matrix.handle, x.ctypes.data, tokens, columns, strided.ctypes.data, rows + 8, 7) == 2
+        assert lib.raw.syn_b200_gemm(matrix.handle, x.ctypes.data, tokens, columns, strided.ctypes.data, rows + 8, sb.GEMM_F16X2) == 0
     ragged = synth.matrix(sb.Q8_0, 8, 96, seed=63)
     with sb.QuantizedMatrix(ragged, sb.Q8_0, 8, 96) as matrix:
         with pytest.raises(sb.BackendUnavailableError, match="multiple of 64"):
             matrix.gemm(synth.activations(2, 96, seed=64))
+
+
+SPLIT_CASES = [(sb.Q4_K, 512, 3584, 128), (sb.Q4_K, 300, 1024, 7), (sb.Q6_K, 384, 18944, 140), (sb.Q6_K, 300, 768, 5), (sb.Q8_0, 4864, 896, 64),
+               (sb.Q4_K, 1024, 8192, 200)]
+
+
+@pytest.mark.parametrize("ggml_type,rows,columns,tokens", SPLIT_CASES)
+@pytest.mark.parametrize("repack", [True, False])
+def test_two_part_operands_meet_the_reference_kernel_tolerance(oracle, ggml_type, rows, columns, tokens, repack):
+    """SYN_B200_GEMM_F16X2 carries weights and activations as fp16 high + low parts, so what is left is the accumulation
+    inside the tensor cores: every output must be within the reference's own kernel tolerance of the FP64 value,
+    |y - exact| <= 2e-5 * sum|term| (native/synapse-kernels/tests/Features/CpuKernels/q8_0_tests.rs:116) -- in fact
+    within a tenth of it --, at least 99 % of the outputs must meet 1e-3 relative / 1e-5 absolute against the
+    FP32-activation oracle (the rest are sums that cancel to a small value), and the worst error must be more than
+    twenty times smaller than with plain fp16 operands."""
+    if not repack and ggml_type == sb.Q4_K:
+        pytest.skip("Q4_K has one layout")
+    weights = synth.matrix(ggml_type, rows, columns, seed=51)
+    x = synth.activations(tokens, columns, seed=52)
+    with sb.QuantizedMatrix(weights, ggml_type, rows, columns, repack=repack) as matrix:
+        y = matrix.gemm(x, sb.GEMM_F16X2)
+        coarse = matrix.gemm(x, sb.GEMM_F16)
+        assert sb.library().device_faults() == 0
+    picks = np.unique(np.linspace(0, tokens - 1, min(tokens, 16)).astype(int))
+    exact, magnitude = oracle.f32_exact(ggml_type, weights, rows, columns, x[picks])
+    want = oracle.f32_matmul_threads(ggml_type, weights, rows, columns, x[picks], 8)
+    normalised = np.abs(y[picks].astype(np.float64) - exact) / magnitude
+    assert normalised.max() <= 2e-6, f"worst error {normalised.max():.3e} of sum|term|"
+    inside = float(np.mean(np.abs(y[picks] - want) <= 1e-5 + 1e-3 * np.abs(want)))
+    assert inside >= 0.99, inside
+    fine = np.abs(y[picks] - exact).max(), np.abs(coarse[picks] - exact).max()
+    print(f"rows {rows} cols {columns} tokens {tokens}: {inside:.2%} inside 1e-3 relative, worst error {normalised.max():.2e} of sum|term|; "
+          f"worst |y - exact| {fine[0]:.3e} against {fine[1]:.3e} with plain fp16 operands")
+    assert fine[0] * 20 < fine[1]
+    assert np.all(np.isfinite(y)) and np.all(np.abs(y).sum(axis=1) > 0)
