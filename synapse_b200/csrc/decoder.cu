@@ -21,7 +21,11 @@ namespace syn {
 namespace {
 
 constexpr uint64_t kNoTensor = 0xFFFFFFFFFFFFFFFFull;
-constexpr uint32_t kMaxStepTokens = 8;
+// Tokens of one step: decode tokens of several sessions and prompt runs (the reference's prefill chunks hold up to 64
+// tokens, src/Synapse.Runtime/Features/ModelLoading/ModelLoadOptions.cs:57). Steps of up to kMaxGraphTokens tokens are
+// captured into a CUDA graph per token count.
+constexpr uint32_t kMaxStepTokens = 64;
+constexpr uint32_t kMaxGraphTokens = 8;
 
 using prog::BatchToken;
 using prog::decode_element;
@@ -275,9 +279,9 @@ struct syn_b200_decoder {
     syn::BatchToken *device_tokens = nullptr, *host_tokens = nullptr;
     int32_t *device_argmax = nullptr, *host_argmax = nullptr;
     float *host_logits = nullptr;  // pinned staging for the logits: a copy into pageable caller memory is slower than this plus a memcpy
-    cudaGraphExec_t graphs[kMaxStepTokens + 1] = {};
-    uint64_t launches_per_step[kMaxStepTokens + 1] = {};
-    uint32_t steps_seen[kMaxStepTokens + 1] = {};  // the first step of a token count runs uncaptured (one-time kernel set-up)
+    cudaGraphExec_t graphs[kMaxGraphTokens + 1] = {};
+    uint64_t launches_per_step[kMaxGraphTokens + 1] = {};
+    uint32_t steps_seen[kMaxGraphTokens + 1] = {};  // the first step of a token count runs uncaptured (one-time kernel set-up)
     // Single-token steps run as one persistent kernel when the model fits it (decode_program.cuh).
     bool program_ready = false;
     syn::prog::Op *program_ops = nullptr;
@@ -922,7 +926,7 @@ int32_t run_step(syn_b200_decoder *d, const syn_b200_batch_token *tokens, uint64
     cudaError_t error = cudaSuccess;
     if (d->program_ready && count == 1 && rows == 1) {
         error = enqueue_program(d);
-    } else if (graphable && rows == count && d->steps_seen[count]++ > 0) {
+    } else if (graphable && rows == count && count <= kMaxGraphTokens && d->steps_seen[count]++ > 0) {
         if (!d->graphs[count]) {
             fault_word_device();
             const uint64_t before = syn_b200_launch_count(0);

@@ -175,3 +175,38 @@ def test_7b_shaped_step_in_both_forms_against_the_cpu_executor(oracle, monkeypat
             print(f"7B-shaped two-layer step: worst error {worst:.2e} of the logits range over positions 0..5 and 100..103")
     reference.close()
     assert sb.library().device_faults() == 0
+
+
+@pytest.mark.parametrize("types,embedding,output", [(dec.Q8_TYPES, synth.Q8_0, synth.Q8_0), (dec.Q4KM_TYPES, synth.Q4_K, synth.Q6_K)])
+def test_prompt_runs_in_chunks_of_1_2_and_64_give_identical_logits(oracle, types, embedding, output):
+    """tests/Synapse.IntegrationTests/Features/CpuKernels/OptimizedQwen2Tests.cs:41-54 (BatchedPrefillMatchesSequentialPrefill):
+    a prompt evaluated one token per step, two per step, and as one run of up to 64 tokens yields the same logits bit for
+    bit at every position; the last position also matches the CPU executor (oracle O8) by the GPU-vs-reference criterion."""
+    shape = dict(layers=2, hidden=256, feed_forward=512, heads=4, kv_heads=2, vocabulary=512, context=64)
+    image = dec.ModelImage(**shape, matrix_types=types, embedding_type=embedding, output_type=output, seed=21, step_tokens=64)
+    prompt = [int(t) for t in synth.rng_for(22, "prompt").integers(0, 512, 37)]
+    reference = oracle.Decoder(image.desc(), 512)
+    for position, token in enumerate(prompt):
+        want_last = reference.decode(token, position)
+    reference.close()
+    results = {}
+    for chunk in (1, 2, 64):
+        with dec.Decoder(image) as model:
+            rows = []
+            for first in range(0, len(prompt), chunk):
+                part = prompt[first:first + chunk]
+                logits = model.forward([(0, token, first + i, i) for i, token in enumerate(part)])
+                rows.extend(logits[i].copy() for i in range(len(part)))
+            results[chunk] = np.stack(rows)
+    assert results[2].tobytes() == results[1].tobytes()
+    assert results[64].tobytes() == results[1].tobytes()
+    span = float(want_last.max() - want_last.min())
+    assert np.abs(results[64][-1] - want_last).max() <= 2e-3 * span
+    assert int(np.argmax(results[64][-1])) == oracle.Decoder.argmax(want_last)
+    # a run whose tokens ask for no logits except the last (how a generation loop prefills)
+    with dec.Decoder(image) as model:
+        only_last = model.forward([(0, token, i, 0 if i == len(prompt) - 1 else -1) for i, token in enumerate(prompt)])
+        assert only_last.shape[0] == 1 and only_last[0].tobytes() == results[1][-1].tobytes()
+        with pytest.raises(sb.KernelError):
+            model.forward([(0, 1, 40 + i, -1) for i in range(65)])
+    assert sb.library().device_faults() == 0
