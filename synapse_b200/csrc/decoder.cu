@@ -45,14 +45,19 @@ __global__ void embed_kernel(const BatchToken *__restrict__ tokens, const uint8_
 }
 
 // RMSNorm with an FP64 sum of squares (Q8Operators.cs:101-123) fused with the Q8_0 activation quantiser
-// (Q8ActivationQuantizer.cs:34-57), one CTA per token. With `by_logits_row` the token's activations go to row
-// tokens[t].logits_row and tokens without a logits row are skipped (Qwen2CpuExecutor.cs:202-222).
-__global__ void __launch_bounds__(256)
+// (Q8ActivationQuantizer.cs:34-57), one CTA of 32 warps per token. Every value is loaded once and stays in registers: a
+// lane takes four consecutive values, eight lanes one 32-value block, a warp one 128-value piece per round (rows of up
+// to 32768 values take eight rounds). The sum of squares is formed per piece and the pieces are added in index order,
+// the order every normalising kernel of the library uses, so all of them produce the same bits. With `by_logits_row` the
+// token's activations go to row tokens[t].logits_row and tokens without a logits row are skipped
+// (Qwen2CpuExecutor.cs:202-222).
+constexpr int kNormWarps = 32, kNormRounds = 8;
+__global__ void __launch_bounds__(kNormWarps * 32)
 rmsnorm_quantize_kernel(const BatchToken *__restrict__ tokens, const float *__restrict__ x, const float *__restrict__ weight, float epsilon,
                         uint32_t n, uint32_t rows, uint32_t by_logits_row, int8_t *__restrict__ codes, float *__restrict__ scales,
                         int16_t *__restrict__ sums)
 {
-    __shared__ double quad_sums[256];  // rows of up to 32768 values
+    __shared__ double quad_sums[kNormWarps * kNormRounds];  // rows of up to 32768 values
     __shared__ float shared_scale;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -65,14 +70,21 @@ rmsnorm_quantize_kernel(const BatchToken *__restrict__ tokens, const float *__re
         }
     }
     const float *row = x + (uint64_t)t * n;
-    // sums of squares per 128-value piece, pieces added in index order: the order every normalising kernel uses
     const uint32_t quads = (n + 127) / 128;
-    for (uint32_t quad = warp; quad < quads; quad += 8) {
-        const uint32_t first = quad * 128 + lane * 4;
-        const float4 v = first < n ? *reinterpret_cast<const float4 *>(row + first) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        const double s = prog::quad_square_sum(v);
-        if (lane == 0) {
-            quad_sums[quad] = s;
+    float4 v[kNormRounds];
+#pragma unroll
+    for (int i = 0; i < kNormRounds; ++i) {
+        const uint32_t first = (warp + i * kNormWarps) * 128 + lane * 4;
+        v[i] = first < n ? *reinterpret_cast<const float4 *>(row + first) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+#pragma unroll
+    for (int i = 0; i < kNormRounds; ++i) {
+        const uint32_t quad = warp + i * kNormWarps;
+        if (quad < quads) {  // the same for the whole warp
+            const double s = prog::quad_square_sum(v[i]);
+            if (lane == 0) {
+                quad_sums[quad] = s;
+            }
         }
     }
     __syncthreads();
@@ -82,26 +94,35 @@ rmsnorm_quantize_kernel(const BatchToken *__restrict__ tokens, const float *__re
     __syncthreads();
     const float scale = shared_scale;
     const uint32_t blocks = n / 32;
-    for (uint32_t b = warp; b < blocks; b += 8) {
-        const uint32_t i = b * 32 + lane;
-        const float value = __fmul_rn(__fmul_rn(row[i], scale), weight[i]);
-        float amax = fabsf(value);
-        for (int offset = 16; offset > 0; offset >>= 1) {
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+#pragma unroll
+    for (int i = 0; i < kNormRounds; ++i) {
+        const uint32_t first = (warp + i * kNormWarps) * 128 + lane * 4;
+        if (warp + i * kNormWarps >= quads) {
+            break;  // the same for the whole warp
         }
+        const float4 w = first < n ? __ldg(reinterpret_cast<const float4 *>(weight + first)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const float a = __fmul_rn(__fmul_rn(v[i].x, scale), w.x), b = __fmul_rn(__fmul_rn(v[i].y, scale), w.y);
+        const float c = __fmul_rn(__fmul_rn(v[i].z, scale), w.z), e = __fmul_rn(__fmul_rn(v[i].w, scale), w.w);
+        float amax = fmaxf(fmaxf(fabsf(a), fabsf(b)), fmaxf(fabsf(c), fabsf(e)));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
         const float d = __fdiv_rn(amax, 127.0f);
         const float inverse = d == 0.0f ? 0.0f : __fdiv_rn(1.0f, d);
-        const int code = __float2int_rn(__fmul_rn(value, inverse));
-        codes[(uint64_t)target * n + i] = (int8_t)code;
-        int group = code;
-        for (int offset = 8; offset > 0; offset >>= 1) {
-            group += __shfl_xor_sync(0xffffffffu, group, offset);
-        }
-        if ((lane & 15) == 0) {
-            sums[(uint64_t)target * (n / 16) + b * 2 + (lane >> 4)] = (int16_t)group;
-        }
-        if (lane == 0) {
-            scales[(uint64_t)target * blocks + b] = __half2float(__float2half_rn(d));
+        const int c0 = __float2int_rn(__fmul_rn(a, inverse)), c1 = __float2int_rn(__fmul_rn(b, inverse));
+        const int c2 = __float2int_rn(__fmul_rn(c, inverse)), c3 = __float2int_rn(__fmul_rn(e, inverse));
+        int group = (c0 + c1) + (c2 + c3);
+        group += __shfl_xor_sync(0xffffffffu, group, 1);
+        group += __shfl_xor_sync(0xffffffffu, group, 2);
+        if (first < n) {
+            const uint32_t packed = (uint32_t)(c0 & 0xff) | ((uint32_t)(c1 & 0xff) << 8) | ((uint32_t)(c2 & 0xff) << 16) | ((uint32_t)c3 << 24);
+            *reinterpret_cast<uint32_t *>(codes + (uint64_t)target * n + first) = packed;
+            if ((lane & 3) == 0) {
+                sums[(uint64_t)target * (n / 16) + first / 16] = (int16_t)group;
+            }
+            if ((lane & 7) == 0) {
+                scales[(uint64_t)target * blocks + first / 32] = __half2float(__float2half_rn(d));
+            }
         }
     }
 }
@@ -212,43 +233,76 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
 }
 
 // First maximum of each logits row (Q8Operators.cs:152-173): larger value wins, equal values keep the lower index.
-__global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ logits, uint32_t vocabulary, int32_t *__restrict__ out)
+// Grid (kArgmaxSlices, logits rows): every CTA reduces one slice of the row and leaves its best in `partial`; the CTA
+// that finishes last (an arrival counter per row, reset for the next step) reduces the slices.
+constexpr uint32_t kArgmaxSlices = 64;
+__global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ logits, uint32_t vocabulary, float *__restrict__ partial_value,
+                                                     int32_t *__restrict__ partial_index, uint32_t *__restrict__ arrivals, int32_t *__restrict__ out)
 {
-    __shared__ float best_value[32];
-    __shared__ int best_index[32];
+    __shared__ float best_value[8];
+    __shared__ int best_index[8];
+    __shared__ bool last;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const float *row = logits + (uint64_t)blockIdx.x * vocabulary;
+    const float *row = logits + (uint64_t)blockIdx.y * vocabulary;
+    const uint32_t slice = (vocabulary + kArgmaxSlices - 1) / kArgmaxSlices;
+    const uint32_t begin = blockIdx.x * slice, end = min(vocabulary, begin + slice);
     float value = -INFINITY;
     int index = 0x7fffffff;
-    for (uint32_t i = threadIdx.x; i < vocabulary; i += blockDim.x) {
+    auto better = [](float v, int i, float value, int index) { return v > value || (v == value && i < index); };
+    for (uint32_t i = begin + threadIdx.x; i < end; i += blockDim.x) {
         const float v = row[i];
-        if (v > value || (v == value && (int)i < index)) {
+        if (better(v, (int)i, value, index)) {
             value = v;
             index = (int)i;
         }
     }
-    for (int offset = 16; offset > 0; offset >>= 1) {
-        const float other_value = __shfl_xor_sync(0xffffffffu, value, offset);
-        const int other_index = __shfl_xor_sync(0xffffffffu, index, offset);
-        if (other_value > value || (other_value == value && other_index < index)) {
-            value = other_value;
-            index = other_index;
-        }
-    }
-    if ((threadIdx.x & 31) == 0) {
-        best_value[threadIdx.x >> 5] = value;
-        best_index[threadIdx.x >> 5] = index;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
-            if (best_value[w] > value || (best_value[w] == value && best_index[w] < index)) {
-                value = best_value[w];
-                index = best_index[w];
+    auto reduce_cta = [&]() {
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            const float other_value = __shfl_xor_sync(0xffffffffu, value, offset);
+            const int other_index = __shfl_xor_sync(0xffffffffu, index, offset);
+            if (better(other_value, other_index, value, index)) {
+                value = other_value;
+                index = other_index;
             }
         }
-        out[blockIdx.x] = index;
+        if ((threadIdx.x & 31) == 0) {
+            best_value[threadIdx.x >> 5] = value;
+            best_index[threadIdx.x >> 5] = index;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
+                if (better(best_value[w], best_index[w], value, index)) {
+                    value = best_value[w];
+                    index = best_index[w];
+                }
+            }
+        }
+    };
+    reduce_cta();
+    if (threadIdx.x == 0) {
+        partial_value[blockIdx.y * kArgmaxSlices + blockIdx.x] = value;
+        partial_index[blockIdx.y * kArgmaxSlices + blockIdx.x] = index;
+        __threadfence();
+        last = atomicAdd(arrivals + blockIdx.y, 1u) + 1 == gridDim.x;
+    }
+    __syncthreads();
+    if (!last) {
+        return;
+    }
+    __threadfence();
+    value = -INFINITY;
+    index = 0x7fffffff;
+    if (threadIdx.x < kArgmaxSlices) {
+        value = __ldcg(partial_value + blockIdx.y * kArgmaxSlices + threadIdx.x);
+        index = __ldcg(partial_index + blockIdx.y * kArgmaxSlices + threadIdx.x);
+    }
+    __syncthreads();
+    reduce_cta();
+    if (threadIdx.x == 0) {
+        out[blockIdx.y] = index;
+        arrivals[blockIdx.y] = 0;
     }
 }
 
@@ -278,6 +332,9 @@ struct syn_b200_decoder {
     float *keys = nullptr, *values = nullptr;
     syn::BatchToken *device_tokens = nullptr, *host_tokens = nullptr;
     int32_t *device_argmax = nullptr, *host_argmax = nullptr;
+    float *argmax_value = nullptr;       // per logits row and slice: the slice's best value and its index
+    int32_t *argmax_index = nullptr;
+    uint32_t *argmax_arrivals = nullptr;  // per logits row: slices done (zero between steps)
     float *host_logits = nullptr;  // pinned staging for the logits: a copy into pageable caller memory is slower than this plus a memcpy
     cudaGraphExec_t graphs[kMaxGraphTokens + 1] = {};
     uint64_t launches_per_step[kMaxGraphTokens + 1] = {};
@@ -375,7 +432,7 @@ cudaError_t norm_quantize(syn_b200_decoder *d, const float *x, const float *weig
     const uint32_t n = d->shape.hidden;
     const ActLayout layout = act_layout(rows, n);
     uint8_t *base = static_cast<uint8_t *>(act);
-    return launch_kernel(rmsnorm_quantize_kernel, dim3(tokens), dim3(256), 0, d->stream, (const BatchToken *)d->device_tokens, x, weight,
+    return launch_kernel(rmsnorm_quantize_kernel, dim3(tokens), dim3(kNormWarps * 32), 0, d->stream, (const BatchToken *)d->device_tokens, x, weight,
                          d->shape.rms_epsilon, n, rows, by_logits_row ? 1u : 0u, reinterpret_cast<int8_t *>(base + layout.codes),
                          reinterpret_cast<float *>(base + layout.scales), reinterpret_cast<int16_t *>(base + layout.sums));
 }
@@ -513,7 +570,8 @@ cudaError_t enqueue_step(syn_b200_decoder *d, uint32_t count, uint32_t logits_ro
     if (logits_rows > 0) {
         SYN_TRY(norm_quantize(d, d->hidden, d->output_norm, count, logits_rows, true, d->act_hidden));
         SYN_TRY(product(d, d->output, d->act_hidden, logits_rows, d->logits, s.vocabulary, Epilogue{}));
-        SYN_TRY(launch_kernel(argmax_kernel, dim3(logits_rows), dim3(1024), 0, d->stream, (const float *)d->logits, s.vocabulary, d->device_argmax));
+        SYN_TRY(launch_kernel(argmax_kernel, dim3(kArgmaxSlices, logits_rows), dim3(256), 0, d->stream, (const float *)d->logits, s.vocabulary,
+                              d->argmax_value, d->argmax_index, d->argmax_arrivals, d->device_argmax));
     }
     return cudaSuccess;
 }
@@ -1068,11 +1126,15 @@ int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_deco
         if (status == SYN_B200_OK) status = device_alloc(d, &d->values, cache);
         if (status == SYN_B200_OK) status = device_alloc(d, &d->device_tokens, T);
         if (status == SYN_B200_OK) status = device_alloc(d, &d->device_argmax, T);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->argmax_value, T * kArgmaxSlices);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->argmax_index, T * kArgmaxSlices);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->argmax_arrivals, T);
         if (status != SYN_B200_OK) return fail_out(status);
         d->act_hidden = act_hidden;
         d->act_ffn = act_ffn;
         cudaError_t error = cudaMemcpy(d->cosines, s.rope_cosines, (uint64_t)s.context * half * 4, cudaMemcpyHostToDevice);
         if (error == cudaSuccess) error = cudaMemcpy(d->sines, s.rope_sines, (uint64_t)s.context * half * 4, cudaMemcpyHostToDevice);
+        if (error == cudaSuccess) error = cudaMemset(d->argmax_arrivals, 0, T * sizeof(uint32_t));
         if (error == cudaSuccess) error = cudaMemset(d->keys, 0, cache * 4);
         if (error == cudaSuccess) error = cudaMemset(d->values, 0, cache * 4);
         if (error == cudaSuccess) error = cudaHostAlloc(reinterpret_cast<void **>(&d->host_tokens), T * sizeof(syn::BatchToken), cudaHostAllocDefault);
