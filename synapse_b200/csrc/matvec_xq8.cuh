@@ -926,7 +926,10 @@ cudaError_t launch_pipe(const MatvecArgs &a, const PipeArgs &p, cudaStream_t str
     // A launch of several row ranges, or of a gate/up pair, fills both CTA slots of every SM: it stands for the two or three
     // launches that otherwise run side by side on parallel branches (measured on the 2 x 38 MB gate | up pair: 15.9 us with
     // two CTAs per SM, 17.2 us with one).
-    const uint64_t cap = (uint64_t)sm_count(a.matrix->device) * (roomy(T, CW, FUSED) ? 1 : MODE != kSingle ? 2 : F::ctas_per_sm(W));
+    // So does a matrix small enough that two CTAs per SM leave every CTA a single row group (7 MB projections: one
+    // stage per CTA instead of two one after the other).
+    const uint64_t sms = (uint64_t)sm_count(a.matrix->device);
+    const uint64_t cap = sms * (roomy(T, CW, FUSED) ? 1 : (MODE != kSingle || p.groups <= 2 * sms) ? 2 : F::ctas_per_sm(W));
     if (ctas > cap) {
         ctas = cap;
     }
