@@ -160,6 +160,41 @@ SYN_B200_API int32_t syn_b200_gemm(const syn_b200_matrix *matrix, const float *x
 SYN_B200_API int32_t syn_b200_block_dots(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
                             const int8_t *codes, uint64_t tokens, int32_t *out);
 
+/* ---- GGUF files: the tensor table and per-tensor loading on the native side. Replaces the header reader and tensor
+ * table of the reference's runtime (src/Synapse.Runtime/Features/ModelLoading/Gguf/GgufHeaderReader.cs:20-154,
+ * GgufTensorInfo.cs) for callers that hand the library a file instead of block pointers, and the whole-file device copy
+ * of the reference's CUDA backend (native/synapse-gpu/src/Features/GpuKernels/cuda/decoder.rs:59-60): tensors are
+ * uploaded one by one from the mapped file. Same rules as the reference: GGUF version 2 or 3; at most 1,000,000 tensors
+ * and metadata entries; rank 1 to 8; general.alignment a power of two (default 32); F32, Q8_0, Q4_K and Q6_K tensors
+ * (anything else: SYN_B200_UNAVAILABLE); a tensor outside the file or a truncated header: SYN_B200_INVALID_ARGUMENT. ---- */
+
+typedef struct syn_b200_gguf syn_b200_gguf;
+
+/* One entry of the tensor table (GgufTensorInfo): `dimensions[0]` is the row length, `offset` is absolute in the file. */
+typedef struct syn_b200_gguf_tensor {
+    char name[128]; /* NUL-terminated (longer names are cut) */
+    uint32_t ggml_type;
+    uint32_t rank;
+    uint64_t dimensions[8]; /* unused entries are 1 */
+    uint64_t offset;
+    uint64_t bytes;
+} syn_b200_gguf_tensor;
+
+SYN_B200_API int32_t syn_b200_gguf_open(const char *path, syn_b200_gguf **out); /* maps the file read-only and parses its header */
+SYN_B200_API void syn_b200_gguf_close(syn_b200_gguf *gguf);                     /* null is ignored */
+SYN_B200_API uint64_t syn_b200_gguf_tensor_count(const syn_b200_gguf *gguf);
+SYN_B200_API int32_t syn_b200_gguf_tensor_at(const syn_b200_gguf *gguf, uint64_t index, syn_b200_gguf_tensor *out);
+SYN_B200_API int32_t syn_b200_gguf_find(const syn_b200_gguf *gguf, const char *name, syn_b200_gguf_tensor *out);
+/* The mapped file (valid until close), its length and the offset of its data section: what syn_b200_decoder_desc.weights
+ * and the tensor offsets refer to when a decoder is created from a file. */
+SYN_B200_API const uint8_t *syn_b200_gguf_mapping(const syn_b200_gguf *gguf, uint64_t *length, uint64_t *data_offset);
+/* syn_b200_matrix_create for the two-dimensional tensor `name` (rows = dimensions[1], columns = dimensions[0], as
+ * src/Synapse.Runtime/Features/CpuKernels/Q8Matrix.cs:51-54). With `cache_directory` (may be null) a repacked device image is
+ * written there after the first load and read back instead of repacking on later loads; entries are keyed by a digest of
+ * the file's header and length and by the tensor's name and offset, and a cache that cannot be read or written is ignored. */
+SYN_B200_API int32_t syn_b200_gguf_load_matrix(const syn_b200_gguf *gguf, const char *name, uint32_t flags, const char *cache_directory,
+                                               syn_b200_matrix **out);
+
 /* ---- Device-resident variants: every pointer is DEVICE memory on the matrix's device; work is queued on
  * `stream` (a cudaStream_t, null = default stream) and not synchronised. These are what a resident decode
  * loop calls; they replace the launches of step/projection.rs without the per-step host copies of

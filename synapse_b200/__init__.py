@@ -88,6 +88,13 @@ def _gather(peer_ptrs, signal_ptrs=(), arrivals_ptr=0):
     return gather
 
 
+class GgufTensor(ctypes.Structure):
+    """``syn_b200_gguf_tensor``: one entry of a GGUF file's tensor table (the reference's ``GgufTensorInfo``)."""
+
+    _fields_ = [("name", c_char * 128), ("ggml_type", c_uint32), ("rank", c_uint32), ("dimensions", c_uint64 * 8), ("offset", c_uint64),
+                ("bytes", c_uint64)]
+
+
 class DeviceInfo(ctypes.Structure):
     _fields_ = [("name", c_char * 128), ("total_memory_bytes", c_uint64), ("max_buffer_bytes", c_uint64),
                 ("compute_capability", c_uint32), ("multiprocessors", c_uint32)]
@@ -131,6 +138,13 @@ _EXPORTS = {
     "syn_b200_decoder_forward_argmax": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p]),
     "syn_b200_decoder_destroy": (None, [c_void_p]),
     "syn_b200_decoder_kv_bytes": (c_uint64, [c_void_p]),
+    "syn_b200_gguf_open": (c_int32, [ctypes.c_char_p, POINTER(c_void_p)]),
+    "syn_b200_gguf_close": (None, [c_void_p]),
+    "syn_b200_gguf_tensor_count": (c_uint64, [c_void_p]),
+    "syn_b200_gguf_tensor_at": (c_int32, [c_void_p, c_uint64, POINTER(GgufTensor)]),
+    "syn_b200_gguf_find": (c_int32, [c_void_p, ctypes.c_char_p, POINTER(GgufTensor)]),
+    "syn_b200_gguf_mapping": (c_void_p, [c_void_p, POINTER(c_uint64), POINTER(c_uint64)]),
+    "syn_b200_gguf_load_matrix": (c_int32, [c_void_p, ctypes.c_char_p, c_uint32, ctypes.c_char_p, POINTER(c_void_p)]),
     "syn_b200_launch_count": (c_uint64, [c_uint32]),
     "syn_b200_device_faults": (c_uint32, [c_uint32]),
 }
@@ -456,6 +470,64 @@ class QuantizedMatrix:
                     scratch_bytes: int, precision: int = GEMM_F16, stream: int = 0) -> None:
         self._lib.check(self._lib.raw.syn_b200_gemm_dev(self.handle, x_ptr, tokens, in_stride, y_ptr, out_stride, precision,
                                                        scratch_ptr, scratch_bytes, stream))
+
+
+class GgufFile:
+    """A mapped GGUF file and its tensor table, parsed by the native library (the sibling of ``GgufFile`` /
+    ``GgufHeaderReader``, src/Synapse.Runtime/Features/ModelLoading/Gguf/GgufFile.cs:57-98, GgufHeaderReader.cs:20-154)."""
+
+    def __init__(self, path: str, lib: NativeB200Library | None = None):
+        self._lib = lib or library()
+        self._handle = c_void_p()
+        self._lib.check(self._lib.raw.syn_b200_gguf_open(os.fsencode(path), byref(self._handle)))
+
+    def close(self) -> None:
+        if getattr(self, "_handle", None):
+            self._lib.raw.syn_b200_gguf_close(self._handle)
+            self._handle = c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *_):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def tensors(self) -> list[GgufTensor]:
+        out = []
+        for index in range(int(self._lib.raw.syn_b200_gguf_tensor_count(self._handle))):
+            entry = GgufTensor()
+            self._lib.check(self._lib.raw.syn_b200_gguf_tensor_at(self._handle, index, byref(entry)))
+            out.append(entry)
+        return out
+
+    def find(self, name: str) -> GgufTensor:
+        entry = GgufTensor()
+        self._lib.check(self._lib.raw.syn_b200_gguf_find(self._handle, name.encode(), byref(entry)))
+        return entry
+
+    def data_offset(self) -> int:
+        length, offset = c_uint64(), c_uint64()
+        self._lib.raw.syn_b200_gguf_mapping(self._handle, byref(length), byref(offset))
+        return int(offset.value)
+
+    def load_matrix(self, name: str, repack: bool = True, cache_directory: str | None = None) -> "QuantizedMatrix":
+        """The tensor as a device-resident matrix; with ``cache_directory`` its repacked image is persisted and reused."""
+        entry = self.find(name)
+        handle = c_void_p()
+        self._lib.check(self._lib.raw.syn_b200_gguf_load_matrix(self._handle, name.encode(), REPACK if repack else 0,
+                                                                os.fsencode(cache_directory) if cache_directory else None, byref(handle)))
+        matrix = QuantizedMatrix.__new__(QuantizedMatrix)
+        matrix._lib, matrix._handle = self._lib, handle
+        matrix.ggml_type, matrix.rows, matrix.columns, matrix.repacked = int(entry.ggml_type), int(entry.dimensions[1]), int(entry.dimensions[0]), repack
+        matrix.row_bytes = matrix.columns // BLOCK_VALUES[matrix.ggml_type] * BLOCK_BYTES[matrix.ggml_type]
+        matrix.source_bytes = matrix.rows * matrix.row_bytes
+        return matrix
 
 
 def matmul_q8_segments_device(segments, scratch_ptr: int, tokens: int, y_ptr: int, out_stride: int, accumulate: bool = False, peer_ptrs=(),
