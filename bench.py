@@ -640,7 +640,7 @@ def main():
                    "d2h_bytes_per_step": 4 * shape["vocabulary"], "ms_per_step": decode_seconds / decode_steps * 1e3, "steps": decode_steps,
                    "tokens_per_s": decode_steps / decode_seconds,
                    "api": "syn_b200_decoder_forward (one call per decoded token: host BatchToken in, host logits out, greedy pick on the "
-                          "host); the step runs as one persistent kernel"}
+                          "host); the step is a replayed CUDA graph of one kernel per fused region"}
             e2e["argmax_api_tokens_per_s"] = decode_steps / argmax_seconds
 
     extras = None

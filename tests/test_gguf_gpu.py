@@ -30,8 +30,10 @@ def test_matrices_loaded_from_a_file_equal_matrices_built_from_the_same_bytes(tm
                 with file.load_matrix(name, cache_directory=str(cache)) as loaded:
                     assert (loaded.rows, loaded.columns, loaded.ggml_type) == (rows, columns, ggml_type)
                     assert loaded.matvec(x, sb.MODE_XQ8).tobytes() == want.tobytes()
-            with file.load_matrix(name, repack=False) as natural:
-                assert natural.matvec(x, sb.MODE_XQ8).tobytes() == want.tobytes()
+            # the file layout walks a row in other units than the planar one, so only the values agree, not the bits
+            with file.load_matrix(name, repack=False) as natural, sb.QuantizedMatrix(blocks, ggml_type, rows, columns, repack=False) as reference:
+                assert natural.matvec(x, sb.MODE_XQ8).tobytes() == reference.matvec(x, sb.MODE_XQ8).tobytes()
+                assert np.allclose(natural.matvec(x, sb.MODE_XQ8), want, rtol=1e-3, atol=1e-4)
         entries = sorted(os.listdir(cache))
         assert len(entries) == 3 and all(e.endswith(".synb200") for e in entries)  # Q6_K, Q8_0, Q6_K: Q4_K keeps its file layout
         # a cache entry of another file (same name, other bytes) is not taken: the digest covers the header and the length
