@@ -1037,6 +1037,10 @@ cudaError_t launch_tokens(const MatvecArgs &a, const WeightView *views, bool one
     }
     // Products that also store into peer copies of the output: one pipelined variant (single token, one pass, ready
     // activations); every other shape takes the direct-load kernel below, whose epilogue handles peers at run time.
+    if (gather && a.tokens <= 1 && one_pass && a.act_ready && a.row_count * a.matrix->row_bytes >= kWideBytes &&
+        plan_pipe<F, W, 1, 2 * kWarps>(a, views, 0, pipe)) {
+        return launch_pipe<F, 1, W, UPL, 1, true, false, 2 * kWarps, true>(a, pipe, stream);  // shards of 96 MB and more
+    }
     if (gather && a.tokens <= 1 && one_pass && a.act_ready && plan_pipe<F, W, R>(a, views, 0, pipe)) {
         return launch_pipe<F, 1, W, UPL, R, true, false, kWarps, true>(a, pipe, stream);
     }
