@@ -141,7 +141,8 @@ SYN_B200_API int32_t syn_b200_matmul_q8(const syn_b200_matrix *matrix, uint64_t 
  * projection of the reference GPU step (native/synapse-gpu/.../step/projection.rs:51-72; kernels
  * cuda/kernels/matmul.cu:79-189) and, in XF32 mode, Q8Operators.Multiply / DecodedRowOperators.Multiply
  * (src/Synapse.Runtime/Features/GraphExecution/Q8Operators.cs:46-98, DecodedRowOperators.cs:20-41).
- * Token counts above the matrix-vector limit run on the tensor-core GEMM when mode is XF32. */
+ * Every token count runs on the matrix-vector kernels here (results do not depend on the token count of a call); the
+ * tensor-core product is syn_b200_gemm. */
 SYN_B200_API int32_t syn_b200_matvec(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count, const float *x,
                         uint64_t tokens, uint64_t in_stride, float *y, uint64_t out_stride, uint32_t mode,
                         uint32_t epilogue);
@@ -306,7 +307,10 @@ SYN_B200_API void syn_b200_shared_buffer_destroy(void *device_ptr);
 SYN_B200_API int32_t syn_b200_enable_peer_access(int32_t peer_device);
 
 /* FP32 device activations x matrix rows. XQ8 mode quantises into `scratch` first (required, at least
- * syn_b200_activation_scratch_bytes); XF32 mode ignores scratch. */
+ * syn_b200_activation_scratch_bytes). XF32 mode needs no scratch; a caller that passes one of at least
+ * syn_b200_gemm_scratch_bytes thereby opts into the reference's projection rule (step/projection.rs:14,51-72): whole-matrix
+ * products of more than 4 tokens with a plain store then run on the tensor cores with fp16 operands (SYN_B200_GEMM_F16),
+ * everything else on the FP32-activation matrix-vector kernels. */
 SYN_B200_API int32_t syn_b200_matvec_dev(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
                             const float *x, uint64_t tokens, uint64_t in_stride, float *y, uint64_t out_stride,
                             uint32_t mode, uint32_t epilogue, void *scratch, uint64_t scratch_bytes,

@@ -90,6 +90,25 @@ def test_prompt_runs_above_four_tokens_take_the_tensor_core_path(oracle):
         want = oracle.f32_matmul(sb.Q4_K, weights, rows, columns, x[:4].cpu().numpy())
         assert np.allclose(few.cpu().numpy(), want, rtol=1e-3, atol=1e-4)  # four tokens stay on the FP32 matvec
         assert not torch.equal(few, routed[:4])
+        # which path an entry point takes is a matter of what the caller passes, never of chance: without the tensor-core
+        # scratch every token count stays on the FP32-activation kernels, and so does the host-buffer entry point
+        small = lib.activation_scratch_bytes(tokens, columns)
+        assert small < lib.gemm_scratch_bytes(tokens, columns)
+        plain = torch.zeros(tokens, rows, device="cuda")
+        matrix.matvec_fused_device(x.data_ptr(), tokens, columns, plain.data_ptr(), rows, mode=sb.MODE_XF32, scratch_ptr=scratch_ptr, scratch_bytes=small)
+        torch.cuda.synchronize()
+        assert torch.equal(plain[:4], few) and not torch.equal(plain, routed)
+        host = matrix.matvec(x.cpu().numpy(), sb.MODE_XF32)
+        assert np.array_equal(host, plain.cpu().numpy())
+        many = _device(synth.activations(129, columns, seed=98))
+        need = lib.gemm_scratch_bytes(129, columns)
+        work = torch.empty(need + 256, dtype=torch.uint8, device="cuda")
+        work_ptr = (work.data_ptr() + 255) // 256 * 256
+        a, b = torch.zeros(129, rows, device="cuda"), torch.zeros(129, rows, device="cuda")
+        matrix.matvec_fused_device(many.data_ptr(), 129, columns, a.data_ptr(), rows, mode=sb.MODE_XF32, scratch_ptr=work_ptr, scratch_bytes=need)
+        matrix.gemm_device(many.data_ptr(), 129, columns, b.data_ptr(), rows, work_ptr, need)
+        torch.cuda.synchronize()
+        assert torch.equal(a, b)
 
 
 @pytest.mark.parametrize("ggml_type", [sb.Q8_0, sb.Q4_K, sb.Q6_K])
