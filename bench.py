@@ -559,8 +559,9 @@ def main():
     per_matrix = None
     if not args.no_e2e and world > 1:
         # N > 1: the row-sharded step through the device entry points with the exchange inside: every step copies the
-        # activations from pinned host memory, runs the gathered step, waits until every rank's slices have landed
-        # (a barrier across the ranks) and reads the gathered vocabulary vector back to the host.
+        # activations from pinned host memory, runs the gathered step (whose last kernel waits, bounded, until every
+        # rank's slices of the vocabulary vector have landed), meets the other ranks so that nobody's next step stores
+        # into a vector that is still being copied, and reads the gathered vocabulary vector back to the host.
         host_x = {k: torch.from_numpy(v).pin_memory() for k, v in x_host.items()}
         host_logits = torch.zeros(vocabulary, dtype=torch.float32).pin_memory()
 
@@ -589,7 +590,8 @@ def main():
                "d2h_bytes_per_step": 4 * vocabulary, "ms_per_step": e2e_seconds / e2e_steps * 1e3, "steps": e2e_steps,
                "api": "row-sharded step through the device entry points (" + ("syn_b200_matmul_q8_segments_dev / _swiglu_dev / _gather_dev storing "
                       "into every GPU's copy" if peers is not None else "syn_b200_matmul_q8_dev + NCCL all-gather per product") +
-                      "): pinned host activations in, a barrier across the ranks as the completion of the exchange, gathered vocabulary vector out"}
+                      "): pinned host activations in; the step ends with the bounded device-side wait for every rank's completion word of the vocabulary "
+                      "vector, a barrier across the ranks keeps the next step's stores out of the vector while it is copied, gathered vector out"}
     if not args.no_e2e and world == 1:
         # (a) the per-projection boundary: one host call per matrix, pinned host x in, host y out
         host_x = {k: torch.from_numpy(v).pin_memory() for k, v in x_host.items()}
@@ -715,6 +717,7 @@ def main():
         extras["matvec_xf32_batch1"] = bench_extras.xf32_rates(sb, lib, torch, device, stream, peak)
 
     # config 4 at this N: the 70B-class shapes and the vocabulary projection, row-sharded, at 1 / 8 / 64 columns
+    stored_by_kernel = peers is not None
     if not args.no_e2e:
         if world > 1:
             for entry in matrices:
@@ -749,7 +752,7 @@ def main():
                            "launches": ("one per fused region: q|k (two segments) with v beside it, o, gate|up with SwiGLU in registers, down" if fused_regions
                                         else "one per matrix, q|k|v and gate|up on parallel graph branches"),
                            "projection_launches_per_step": (5 if fused_regions else 7) * args.layers + 1,
-                           "l2": "weights per step exceed L2 35x, no flush", "parallelism": (f"row-shard x{world}, " + ("slices stored into every GPU's copy by the product kernel; every step ends with a bounded wait for all ranks' completion signals" if peers is not None
+                           "l2": "weights per step exceed L2 35x, no flush", "parallelism": (f"row-shard x{world}, " + ("slices stored into every GPU's copy by the product kernel; every step ends with a bounded wait for all ranks' completion signals" if stored_by_kernel
                                                                      else "NCCL all-gather per product")) if world > 1 else "single gpu",
                            "tokens_per_s": 1e3 / ms_per_step},
                 "gather_verified": gather_verified, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_per_matrix_calls": per_matrix, "extras": extras, "clocks": clocks,
