@@ -1,0 +1,492 @@
+// Q4_K and Q6_K x Q8_0-quantised activations for 2..8 tokens per launch on the integer tensor-core path (mma.sync,
+// 8-bit operands, 32-bit accumulators): the batched-decode and short-prompt shape of synapse_q8_matvec_{2,4,8}
+// (native/synapse-gpu/src/Features/GpuKernels/cuda/kernels/matmul.cu:79-145). Included at the end of matvec_xq8.cuh.
+//
+// Why: with dp4a every (row, token) pair costs its own unpack and dot instructions (about 200 warp instructions per
+// row and token), so eight tokens take seven times the one-token time although the weights cross HBM once. One MMA
+// takes the exact integer dots of a group of weights for 16 rows x 8 tokens at once; what is left per (row, token) is
+// the FP32 combination of a unit's groups.
+//
+// Bit-identical to the one-token kernels. Those give lane l of team warp w the units (w * UPL + j) * 32 + l, j < UPL,
+// evaluate F::dot for them one after the other on one accumulator, sum the 32 lanes with the xor butterfly (offsets 16,
+// 8, 4, 2, 1) and then the team's warps in index order. Here a stage of the ring holds the units (w * UPL + j) * 32 ..
+// + 31 of 16 rows; consumer warp i plays lanes i and i + 16: it evaluates their units with the same FP32 expression
+// from the same integers, carries their accumulators from j to j + 1, and adds the two (the butterfly's first level).
+// 128 threads, one per (row, token), then add the sixteen partial sums in the butterfly's tree order
+// ((p0 + p8) + (p4 + p12)) + ... and the team's warps (the chunks w) in index order. Floating-point addition is
+// commutative, so the tree is all that matters.
+#pragma once
+
+namespace syn {
+namespace mv {
+
+constexpr int kMmaWarps = 16;                  // consumer warps
+constexpr uint32_t kMmaRows = 16;              // rows of a tile: M of the MMA
+constexpr uint32_t kMmaShared = 220u * 1024u;  // dynamic shared memory of the kernel
+
+struct MmaArgs {
+    WeightView weights;      // plane bases at the first row of the call
+    uint64_t rows;
+    uint32_t row_bytes;      // Q4_K: bytes of a row
+    uint32_t K;
+    uint32_t units;          // F::units(K)
+    uint32_t upl;            // units per lane of the one-token team
+    uint32_t chunks;         // warps of the one-token team: ceil(units / (32 * upl))
+    uint32_t tokens;
+    uint32_t tp;             // tokens per group (2, 4 or 8): how many tokens' activations shared memory holds
+    uint32_t row_stride;     // bytes between the rows of a stage, chosen so that a warp's loads do not meet in a bank
+    uint32_t code_stride;    // bytes between the tokens' activation codes (the row length plus the same kind of padding)
+    uint32_t scale_stride;   // floats between the tokens' activation scales
+    uint32_t sum_stride;     // elements between the tokens' activation sums
+    uint32_t offset_scales, offset_sums, offset_partial, offset_stages;  // inside the dynamic shared memory
+    uint32_t offset_tail;    // Q6_K: where, inside a stage, the tile's super-block scales (the d plane) start
+    uint32_t stage_bytes, stages;
+};
+
+__device__ __forceinline__ void mma_u8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %11, %12, %13};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+__device__ __forceinline__ void mma_u8s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0)
+{
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%7, %8, %9, %10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+
+// What the consumer side of a codec sees.
+struct MmaContext {
+    const uint8_t *codes;   // activation codes of the group, token t at t * code_stride
+    const float *scales;    // block scales, token t at t * scale_stride
+    const void *sums;       // per-format sums, token t at t * sum_stride elements
+    uint32_t g, tig;        // the MMA's group (lane / 4) and thread-in-group (lane % 4)
+    uint32_t bt;            // the token whose codes this thread feeds to the MMA (column g of B)
+    uint32_t t0, t1;        // the tokens of this thread's accumulator columns (2 tig, 2 tig + 1)
+    uint32_t tail_shift;    // Q6_K: where the tile's part of the d plane starts inside its 16-byte-aligned copy
+};
+
+// ------------------------------------------------------------------------------------------------------
+// Q4_K (file layout). Unit = half a super-block = sub-blocks 4h .. 4h+3; a stage holds 32 units = 16 super-blocks of
+// every row, rows row_stride apart. One m16n8k32 per sub-block; the high nibbles are multiplied in place (sixteen times
+// the dot, as Q4KXq8::dot has it).
+// ------------------------------------------------------------------------------------------------------
+struct Q4KMma {
+    using Format = Q4KXq8;
+    static constexpr uint32_t kUnitValues = 128;
+    static void layout(MmaArgs &m)
+    {
+        const uint32_t piece = (m.units < 32 ? m.units : 32) * 72;
+        m.row_stride = (uint32_t)align_up(piece, 128) + 32;  // 8-byte loads of rows g = 0..3 and tig = 0..3 cover the 32 banks
+        m.offset_tail = 0;
+        m.stage_bytes = kMmaRows * m.row_stride;
+        m.code_stride = m.K + 32;
+        m.scale_stride = m.K / 32 + 4;
+        m.sum_stride = m.K / 32 + 4;  // floats: scale * (sum of the block's codes)
+    }
+    static uint64_t sums_bytes(const MmaArgs &m, uint32_t tp) { return (uint64_t)tp * m.sum_stride * 4; }
+
+    static __device__ __forceinline__ void produce(const MmaArgs &m, uint32_t stage, uint64_t row0, uint32_t n, uint32_t w, uint32_t j, uint32_t lane,
+                                                   uint32_t bar, uint64_t policy)
+    {
+        const uint32_t first = (w * m.upl + j) * 32;                // first unit of the stage
+        const uint32_t piece = min(32u, m.units - first) * 72u;  // a multiple of 144: rows hold whole super-blocks
+        if (lane == 0) {
+            mbar_expect_tx(bar, n * piece);
+        }
+        __syncwarp();
+        if (lane < n) {
+            bulk_copy(stage + lane * m.row_stride, m.weights.p0 + (row0 + lane) * m.row_bytes + (uint64_t)first * 72, piece, bar, policy);
+        }
+    }
+    // scale * (sum of the block's codes) for the min term, as Q4KXq8::load_act computes it
+    static __device__ __forceinline__ void store_sums(const MmaArgs &m, const ActView &act, uint64_t token, bool live, uint32_t t, uint32_t block, float d,
+                                                      void *sums)
+    {
+        float ds = 0.0f;
+        if (live) {
+            const uint32_t pair = __ldg(reinterpret_cast<const uint32_t *>(act.sums + token * (m.K / 16)) + block);
+            ds = d * (float)((int)(short)(pair & 0xffff) + (int)(short)(pair >> 16));
+        }
+        static_cast<float *>(sums)[t * m.sum_stride + block] = ds;
+    }
+
+    // Adds unit `u` (lane `local` of chunk w, step j) to the accumulators of this thread's four (row, token) pairs.
+    static __device__ __forceinline__ void unit(const MmaArgs &m, const MmaContext &c, const uint8_t *stage, uint32_t local, uint32_t u, float (&acc)[4])
+    {
+        const uint8_t *const r0 = stage + c.g * m.row_stride + (local >> 1) * 144, *const r1 = r0 + 8 * m.row_stride;
+        const uint4 h0 = *reinterpret_cast<const uint4 *>(r0), h1 = *reinterpret_cast<const uint4 *>(r1);
+        const uint32_t q = 16 + (local & 1) * 64 + 8 * c.tig;
+        // this thread's eight bytes of each 32-byte nibble run: k positions (tig, byte) of the MMA, and the same eight
+        // positions of the activation codes below
+        const uint2 a00 = *reinterpret_cast<const uint2 *>(r0 + q), a01 = *reinterpret_cast<const uint2 *>(r0 + q + 32);
+        const uint2 a10 = *reinterpret_cast<const uint2 *>(r1 + q), a11 = *reinterpret_cast<const uint2 *>(r1 + q + 32);
+        const uint8_t *const b = c.codes + c.bt * m.code_stride + u * 128 + 8 * c.tig;
+        const uint2 b0 = *reinterpret_cast<const uint2 *>(b), b1 = *reinterpret_cast<const uint2 *>(b + 32);
+        const uint2 b2 = *reinterpret_cast<const uint2 *>(b + 64), b3 = *reinterpret_cast<const uint2 *>(b + 96);
+        int lo0[4], hi0[4], lo1[4], hi1[4];
+        constexpr uint32_t kLow = 0x0F0F0F0Fu, kHigh = 0xF0F0F0F0u;
+        mma_u8s8_k32(lo0, a00.x & kLow, a10.x & kLow, a00.y & kLow, a10.y & kLow, b0.x, b0.y);
+        mma_u8s8_k32(hi0, a00.x & kHigh, a10.x & kHigh, a00.y & kHigh, a10.y & kHigh, b1.x, b1.y);
+        mma_u8s8_k32(lo1, a01.x & kLow, a11.x & kLow, a01.y & kLow, a11.y & kLow, b2.x, b2.y);
+        mma_u8s8_k32(hi1, a01.x & kHigh, a11.x & kHigh, a01.y & kHigh, a11.y & kHigh, b3.x, b3.y);
+        // 6-bit scales and mins of the unit's four sub-blocks, one per byte (as in Q4KXq8::dot)
+        uint32_t sc[2], mn[2];
+        if ((local & 1) == 0) {
+            sc[0] = h0.y & 0x3f3f3f3fu;
+            mn[0] = h0.z & 0x3f3f3f3fu;
+            sc[1] = h1.y & 0x3f3f3f3fu;
+            mn[1] = h1.z & 0x3f3f3f3fu;
+        } else {
+            sc[0] = (h0.w & 0x0f0f0f0fu) | ((h0.y >> 2) & 0x30303030u);
+            mn[0] = ((h0.w >> 4) & 0x0f0f0f0fu) | ((h0.z >> 2) & 0x30303030u);
+            sc[1] = (h1.w & 0x0f0f0f0fu) | ((h1.y >> 2) & 0x30303030u);
+            mn[1] = ((h1.w >> 4) & 0x0f0f0f0fu) | ((h1.z >> 2) & 0x30303030u);
+        }
+        const float d[2] = {half_bits_to_float(h0.x & 0xffff), half_bits_to_float(h1.x & 0xffff)};
+        const float dmin[2] = {half_bits_to_float(h0.x >> 16), half_bits_to_float(h1.x >> 16)};
+        const float *const sums = static_cast<const float *>(c.sums);
+        const float4 ad[2] = {*reinterpret_cast<const float4 *>(c.scales + c.t0 * m.scale_stride + u * 4),
+                              *reinterpret_cast<const float4 *>(c.scales + c.t1 * m.scale_stride + u * 4)};
+        const float4 as[2] = {*reinterpret_cast<const float4 *>(sums + c.t0 * m.sum_stride + u * 4),
+                              *reinterpret_cast<const float4 *>(sums + c.t1 * m.sum_stride + u * 4)};
+        // accumulator [2 * row + token]: row g / g + 8, token 2 tig / 2 tig + 1 -- the MMA's C fragment order
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const int row = p >> 1, token = p & 1;
+            // the expression of Q4KXq8::dot
+            float f_lo = (byte_to_float(sc[row], 0) * small_int_to_float(lo0[p])) * ad[token].x;
+            f_lo = fmaf(byte_to_float(sc[row], 2) * small_int_to_float(lo1[p]), ad[token].z, f_lo);
+            float f_hi = (byte_to_float(sc[row], 1) * small_int_to_float(hi0[p])) * ad[token].y;
+            f_hi = fmaf(byte_to_float(sc[row], 3) * small_int_to_float(hi1[p]), ad[token].w, f_hi);
+            float gm = byte_to_float(mn[row], 0) * as[token].x;
+            gm = fmaf(byte_to_float(mn[row], 1), as[token].y, gm);
+            gm = fmaf(byte_to_float(mn[row], 2), as[token].z, gm);
+            gm = fmaf(byte_to_float(mn[row], 3), as[token].w, gm);
+            acc[p] = fmaf(d[row], fmaf(f_hi, 0.0625f, f_lo), acc[p]);
+            acc[p] = fmaf(-dmin[row], gm, acc[p]);
+        }
+    }
+};
+
+// ------------------------------------------------------------------------------------------------------
+// Q6_K (planes: ql | qh | int8 scales | fp16 super-block scales). Unit = 64 values: bytes l = 16 i .. 16 i + 15 of half h
+// of super-block u / 4, four groups of 16 values with their own scales. A stage holds 32 units = 8 super-blocks of every
+// row (ql 1024, qh 512, scales 128 bytes, rows row_stride apart) and, behind the rows, the tile's part of the d plane.
+// One m16n8k16 per group of 16 values.
+// ------------------------------------------------------------------------------------------------------
+struct Q6KMma {
+    using Format = Q6KPlanarXq8;
+    static constexpr uint32_t kUnitValues = 64;
+    static void layout(MmaArgs &m)
+    {
+        const uint32_t sbs = m.units < 32 ? m.units / 4 : 8;  // super-blocks of a stage
+        // 4-byte loads of rows g = 0..7 and tig = 0..3 cover the 32 banks when the stride is 16 more than a multiple of 128
+        m.row_stride = (uint32_t)align_up(sbs * (128 + 64 + 16), 128) + 16;
+        m.offset_tail = kMmaRows * m.row_stride;
+        // the 16 rows' super-block scales are contiguous in their plane: one copy from the 16-byte boundary below them
+        m.stage_bytes = (uint32_t)align_up(m.offset_tail + kMmaRows * (m.K / 128) + 32, 128);
+        m.code_stride = m.K + 16;
+        m.scale_stride = m.K / 32 + 4;
+        m.sum_stride = m.K / 16 + 8;  // int16: the sums of every 16 codes
+    }
+    static uint64_t sums_bytes(const MmaArgs &m, uint32_t tp) { return (uint64_t)tp * m.sum_stride * 2; }
+
+    static __device__ __forceinline__ void produce(const MmaArgs &m, uint32_t stage, uint64_t row0, uint32_t n, uint32_t w, uint32_t j, uint32_t lane,
+                                                   uint32_t bar, uint64_t policy)
+    {
+        const uint32_t first = (w * m.upl + j) * 32;            // first unit of the stage
+        const uint32_t sb0 = first / 4, sbs = min(32u, m.units - first) / 4;
+        const uint8_t *const tail = m.weights.p3 + row0 * (m.K / 128);
+        const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(tail) & 15);
+        const uint32_t tail_bytes = (shift + n * (m.K / 128) + 15) & ~15u;
+        if (lane == 0) {
+            mbar_expect_tx(bar, n * sbs * (128 + 64 + 16) + tail_bytes);
+            bulk_copy(stage + m.offset_tail, tail - shift, tail_bytes, bar, policy);
+        }
+        __syncwarp();
+        if (lane < n) {
+            const uint64_t row = row0 + lane;
+            const uint32_t base = stage + lane * m.row_stride;
+            bulk_copy(base, m.weights.p0 + row * (m.K / 2) + (uint64_t)sb0 * 128, sbs * 128, bar, policy);
+            bulk_copy(base + sbs * 128, m.weights.p1 + row * (m.K / 4) + (uint64_t)sb0 * 64, sbs * 64, bar, policy);
+            bulk_copy(base + sbs * 192, m.weights.p2 + row * (m.K / 16) + (uint64_t)sb0 * 16, sbs * 16, bar, policy);
+        }
+    }
+    static __device__ __forceinline__ void store_sums(const MmaArgs &m, const ActView &act, uint64_t token, bool live, uint32_t t, uint32_t index, float,
+                                                      void *sums)
+    {
+        // two of the int16 sums per call (index counts pairs)
+        uint32_t pair = 0;
+        if (live) {
+            pair = __ldg(reinterpret_cast<const uint32_t *>(act.sums + token * (m.K / 16)) + index);
+        }
+        reinterpret_cast<uint32_t *>(static_cast<int16_t *>(sums) + t * m.sum_stride)[index] = pair;
+    }
+
+    static __device__ __forceinline__ void unit(const MmaArgs &m, const MmaContext &c, const uint8_t *stage, uint32_t local, uint32_t u, float (&acc)[4])
+    {
+        const uint32_t first = u - local;                       // first unit of the stage
+        const uint32_t sbs = min(32u, m.units - first) / 4;     // super-blocks the stage holds
+        const uint32_t sb = local >> 2, h = (local >> 1) & 1, i = local & 1;
+        const uint8_t *const r0 = stage + c.g * m.row_stride, *const r1 = r0 + 8 * m.row_stride;
+        const uint32_t ql = sb * 128 + h * 64 + i * 16 + 4 * c.tig, qh = sbs * 128 + sb * 64 + h * 32 + i * 16 + 4 * c.tig;
+        const uint32_t a0 = *reinterpret_cast<const uint32_t *>(r0 + ql), b0 = *reinterpret_cast<const uint32_t *>(r0 + ql + 32);
+        const uint32_t h0 = *reinterpret_cast<const uint32_t *>(r0 + qh);
+        const uint32_t a1 = *reinterpret_cast<const uint32_t *>(r1 + ql), b1 = *reinterpret_cast<const uint32_t *>(r1 + ql + 32);
+        const uint32_t h1 = *reinterpret_cast<const uint32_t *>(r1 + qh);
+        uint32_t v0[4], v1[4];
+        q6k_codes(a0, b0, h0, v0[0], v0[1], v0[2], v0[3]);
+        q6k_codes(a1, b1, h1, v1[0], v1[1], v1[2], v1[3]);
+        // activation codes of group q: 16 codes at sb * 256 + h * 128 + i * 16 + 32 q of the row; this thread's four
+        const uint8_t *const b = c.codes + c.bt * m.code_stride + (u >> 2) * 256 + h * 128 + i * 16 + 4 * c.tig;
+        int dots[4][4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            mma_u8s8_k16(dots[q], v0[q], v1[q], *reinterpret_cast<const uint32_t *>(b + 32 * q));
+        }
+        // the eight int8 scales of the half, and the super-block scale
+        const uint32_t sc = sbs * 192 + sb * 16 + h * 8;
+        const uint2 s0 = *reinterpret_cast<const uint2 *>(r0 + sc), s1 = *reinterpret_cast<const uint2 *>(r1 + sc);
+        const uint8_t *const tail = stage + m.offset_tail + c.tail_shift;
+        const float d[2] = {half_bits_to_float(*reinterpret_cast<const unsigned short *>(tail + (c.g * (m.K / 256) + (u >> 2)) * 2)),
+                            half_bits_to_float(*reinterpret_cast<const unsigned short *>(tail + ((c.g + 8) * (m.K / 256) + (u >> 2)) * 2))};
+        const int16_t *const sums = static_cast<const int16_t *>(c.sums);
+        const float4 ad[2] = {*reinterpret_cast<const float4 *>(c.scales + c.t0 * m.scale_stride + (u >> 1) * 4),
+                              *reinterpret_cast<const float4 *>(c.scales + c.t1 * m.scale_stride + (u >> 1) * 4)};
+        const int16_t *const as[2] = {sums + c.t0 * m.sum_stride + (u >> 1) * 8 + i, sums + c.t1 * m.sum_stride + (u >> 1) * 8 + i};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint32_t word0 = q < 2 ? s0.x : s0.y, word1 = q < 2 ? s1.x : s1.y;
+            const int scale[2] = {(int)(signed char)((word0 >> (8 * (2 * (q & 1) + i))) & 0xff), (int)(signed char)((word1 >> (8 * (2 * (q & 1) + i))) & 0xff)};
+            const float adq[2] = {q == 0 ? ad[0].x : q == 1 ? ad[0].y : q == 2 ? ad[0].z : ad[0].w, q == 0 ? ad[1].x : q == 1 ? ad[1].y : q == 2 ? ad[1].z : ad[1].w};
+            const int asq[2] = {(int)as[0][2 * q], (int)as[1][2 * q]};
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const int row = p >> 1, token = p & 1;
+                // the expression of q6k_dot
+                const int dot = dots[q][p] - 32 * asq[token];
+                acc[p] = fmaf((d[row] * small_int_to_float(scale[row])) * adq[token], small_int_to_float(dot), acc[p]);
+            }
+        }
+    }
+};
+
+template <class Codec, bool GATHER>
+__global__ void __launch_bounds__(kMmaWarps * 32 + 32, 1)
+matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_stride, Epilogue epilogue, uint32_t *fault)
+{
+    extern __shared__ __align__(128) uint8_t mma_memory[];
+    __shared__ __align__(8) uint64_t barriers[2 * kMaxStages];  // full[s] then empty[s]
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint64_t tiles = (m.rows + kMmaRows - 1) / kMmaRows;
+    const uint32_t my_tiles = tiles > blockIdx.x ? (uint32_t)((tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+    const uint32_t full0 = smem_u32(&barriers[0]), empty0 = smem_u32(&barriers[kMaxStages]);
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < m.stages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, kMmaWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == kMmaWarps) {
+        // ---- producer: one stage per (tile, team warp w, step j), one bulk copy per row and plane ----
+        const uint64_t policy = l2_evict_first_policy();
+        const uint32_t stage0 = smem_u32(mma_memory) + m.offset_stages;
+        uint32_t s = 0, round = 0;
+        for (uint32_t it = 0; it < my_tiles; ++it) {
+            const uint64_t row0 = ((uint64_t)blockIdx.x + (uint64_t)it * gridDim.x) * kMmaRows;
+            const uint32_t n = (uint32_t)min((uint64_t)kMmaRows, m.rows - row0);
+            for (uint32_t w = 0; w < m.chunks; ++w) {
+                for (uint32_t j = 0; j < m.upl; ++j) {
+                    if ((w * m.upl + j) * 32 >= m.units) {
+                        break;  // the last team warp's lanes have no unit at this step
+                    }
+                    if (round > 0 && !mbar_wait(empty0 + 8 * s, (round - 1) & 1) && fault && lane == 0) {
+                        atomicAdd(fault, 1u);
+                    }
+                    Codec::produce(m, stage0 + s * m.stage_bytes, row0, n, w, j, lane, full0 + 8 * s, policy);
+                    if (++s == m.stages) {
+                        s = 0;
+                        ++round;
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // ---- consumers ---------------------------------------------------------------------------------------
+    constexpr uint32_t kThreads = kMmaWarps * 32;
+    const uint64_t token0 = (uint64_t)blockIdx.y * m.tp;
+    const uint32_t live = min(m.tp, m.tokens - (uint32_t)token0);
+    float *const scales = reinterpret_cast<float *>(mma_memory + m.offset_scales);
+    void *const sums = mma_memory + m.offset_sums;
+    float *const partial = reinterpret_cast<float *>(mma_memory + m.offset_partial);  // [2][kMmaWarps][128]
+
+    pdl_wait();
+    {
+        // the group's quantised activations: codes, block scales, and the sums the format's offset term needs
+        const uint32_t pieces = m.K / 16, blocks = m.K / 32;
+        for (uint32_t i = threadIdx.x; i < m.tp * pieces; i += kThreads) {
+            const uint32_t t = i / pieces, piece = i % pieces;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (t < live) {
+                v = __ldg(reinterpret_cast<const uint4 *>(act.codes + (token0 + t) * m.K) + piece);
+            }
+            *reinterpret_cast<uint4 *>(mma_memory + t * m.code_stride + piece * 16) = v;
+        }
+        for (uint32_t i = threadIdx.x; i < m.tp * blocks; i += kThreads) {
+            const uint32_t t = i / blocks, block = i % blocks;
+            const float d = t < live ? __ldg(act.scales + (token0 + t) * blocks + block) : 0.0f;
+            scales[t * m.scale_stride + block] = d;
+            Codec::store_sums(m, act, token0 + t, t < live, t, block, d, sums);
+        }
+    }
+    consumer_barrier<kThreads>();
+
+    MmaContext c;
+    c.codes = mma_memory;
+    c.scales = scales;
+    c.sums = sums;
+    c.g = lane >> 2;
+    c.tig = lane & 3;
+    c.bt = min(c.g, m.tp - 1);
+    c.t0 = min(2 * c.tig, m.tp - 1);
+    c.t1 = min(2 * c.tig + 1, m.tp - 1);
+    const uint32_t out_row = threadIdx.x >> 3, out_token = threadIdx.x & 7;  // the pair a combining thread owns
+    float running = 0.0f;
+    uint32_t s = 0, phase = 0, buffer = 0;
+    for (uint32_t it = 0; it < my_tiles; ++it) {
+        const uint64_t row0 = ((uint64_t)blockIdx.x + (uint64_t)it * gridDim.x) * kMmaRows;
+        c.tail_shift = (uint32_t)(reinterpret_cast<uintptr_t>(m.weights.p3 + row0 * (m.K / 128)) & 15);
+        for (uint32_t w = 0; w < m.chunks; ++w) {
+            float acc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};  // lanes warp and warp + 16 of team warp w
+            for (uint32_t j = 0; j < m.upl; ++j) {
+                const uint32_t first = (w * m.upl + j) * 32;
+                if (first >= m.units) {
+                    break;
+                }
+                if (!mbar_wait(full0 + 8 * s, phase) && fault && lane == 0) {
+                    atomicAdd(fault, 1u);
+                }
+                const uint8_t *const stage = mma_memory + m.offset_stages + s * m.stage_bytes;
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const uint32_t local = warp + 16 * k;
+                    if (first + local < m.units) {
+                        Codec::unit(m, c, stage, local, first + local, acc[k]);
+                    }
+                }
+                // Give the stage back: the shared-memory reads above have retired (their values were used), the fence
+                // orders them before the producer's next bulk copy into the stage.
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(empty0 + 8 * s);
+                }
+                if (++s == m.stages) {
+                    s = 0;
+                    phase ^= 1;
+                }
+            }
+            // first level of the butterfly: lane i + lane i + 16
+            float *const mine = partial + (buffer * kMmaWarps + warp) * 128;
+            *reinterpret_cast<float2 *>(mine + c.g * 8 + 2 * c.tig) = make_float2(acc[0][0] + acc[1][0], acc[0][1] + acc[1][1]);
+            *reinterpret_cast<float2 *>(mine + (c.g + 8) * 8 + 2 * c.tig) = make_float2(acc[0][2] + acc[1][2], acc[0][3] + acc[1][3]);
+            consumer_barrier<kThreads>();
+            if (threadIdx.x < 128) {
+                const float *const p = partial + buffer * kMmaWarps * 128 + threadIdx.x;
+                float level[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    level[i] = p[i * 128] + p[(i + 8) * 128];  // offset 8
+                }
+                const float c0 = level[0] + level[4], c1 = level[1] + level[5], c2 = level[2] + level[6], c3 = level[3] + level[7];  // offset 4
+                const float e = (c0 + c2) + (c1 + c3);  // offsets 2 and 1
+                running = w == 0 ? e : running + e;      // the team's warps in index order
+                if (w + 1 == m.chunks && row0 + out_row < m.rows && out_token < live) {
+                    store_result<GATHER>(epilogue, y, token0 + out_token, out_stride, row0 + out_row, running);
+                }
+            }
+            buffer ^= 1;
+        }
+    }
+    if (GATHER) {
+        consumer_barrier<kThreads>();
+        if (threadIdx.x == 0) {
+            signal_completion(epilogue);
+        }
+    }
+}
+
+// Lays the shared memory out for `a` and launches; cudaErrorNotSupported when not even two tokens' activations and two
+// stages fit (very long rows), so that the caller falls back to the dp4a kernels.
+template <class Codec, bool GATHER>
+cudaError_t launch_mma(const MatvecArgs &a, const WeightView &view, uint32_t upl, cudaStream_t stream)
+{
+    MmaArgs m{};
+    m.weights = view;
+    m.rows = a.row_count;
+    m.row_bytes = (uint32_t)a.matrix->row_bytes;
+    m.K = (uint32_t)a.matrix->columns;
+    m.units = m.K / Codec::kUnitValues;  // (F::units is device code)
+    m.upl = upl;
+    m.chunks = (m.units + 32 * upl - 1) / (32 * upl);
+    m.tokens = (uint32_t)a.tokens;
+    Codec::layout(m);
+    const uint32_t fixed = 2 * kMmaWarps * 128 * 4;  // the partial sums, double-buffered
+    m.tp = 0;
+    for (uint32_t tp = 8; tp >= 2; tp /= 2) {
+        const uint64_t codes = align_up((uint64_t)tp * m.code_stride, 128), scales = align_up((uint64_t)tp * m.scale_stride * 4, 128);
+        const uint64_t sums = align_up(Codec::sums_bytes(m, tp), 128);
+        if (codes + scales + sums + fixed + 2ull * m.stage_bytes <= kMmaShared && (tp == 2 || tp / 2 < a.tokens)) {
+            m.tp = tp;
+            m.offset_scales = (uint32_t)codes;
+            m.offset_sums = (uint32_t)(codes + scales);
+            m.offset_partial = (uint32_t)(codes + scales + sums);
+            m.offset_stages = m.offset_partial + fixed;
+            const uint64_t stages = (kMmaShared - m.offset_stages) / m.stage_bytes;
+            m.stages = (uint32_t)(stages > kMaxStages ? kMaxStages : stages);
+            break;
+        }
+    }
+    if (m.tp == 0) {
+        return cudaErrorNotSupported;
+    }
+    auto kernel = matvec_mma_kernel<Codec, GATHER>;
+    static PerDevice configured;
+    if (configured.first_use(a.matrix->device)) {
+        cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaShared);
+        if (error != cudaSuccess) {
+            configured.forget(a.matrix->device);
+            return error;
+        }
+    }
+    uint64_t ctas = (a.row_count + kMmaRows - 1) / kMmaRows;
+    const uint64_t cap = (uint64_t)sm_count(a.matrix->device);
+    if (ctas > cap) {
+        ctas = cap;
+    }
+    const dim3 grid((unsigned)ctas, (unsigned)((a.tokens + m.tp - 1) / m.tp));
+    return launch_kernel(kernel, grid, dim3(kMmaWarps * 32 + 32), (size_t)kMmaShared, stream, m, a.act, a.y, a.out_stride, a.fused, fault_word_device());
+}
+
+template <class F, bool GATHER>
+cudaError_t launch_tensor_core_tokens(const MatvecArgs &a, const WeightView &view, uint32_t upl, cudaStream_t stream)
+{
+    if constexpr (std::is_same<F, Q4KXq8>::value) {
+        return launch_mma<Q4KMma, GATHER>(a, view, upl, stream);
+    } else if constexpr (std::is_same<F, Q6KPlanarXq8>::value) {
+        return launch_mma<Q6KMma, GATHER>(a, view, upl, stream);
+    } else {
+        return cudaErrorNotSupported;
+    }
+}
+
+}  // namespace mv
+}  // namespace syn

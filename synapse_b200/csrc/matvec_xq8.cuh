@@ -981,6 +981,11 @@ cudaError_t launch_token_teams(const MatvecArgs &a, const WeightView &view, cuda
                          (uint32_t)a.tokens, tp, a.y, a.out_stride, a.fused, fault_word_device());
 }
 
+// Q4_K and planar Q6_K with 2..8 tokens on the integer tensor cores (matvec_mma.cuh); cudaErrorNotSupported for the
+// other formats and when the row is too long for two tokens' activations and two stages to fit shared memory.
+template <class F, bool GATHER>
+cudaError_t launch_tensor_core_tokens(const MatvecArgs &a, const WeightView &view, uint32_t upl, cudaStream_t stream);
+
 template <class F, int W, int UPL>
 cudaError_t launch_tokens(const MatvecArgs &a, const WeightView *views, bool one_pass, uint64_t dump_groups, cudaStream_t stream)
 {
@@ -1056,6 +1061,13 @@ cudaError_t launch_tokens(const MatvecArgs &a, const WeightView *views, bool one
             return error;
         }
     }
+    if (a.tokens >= 2 && one_pass) {
+        // Several tokens of a K-quant: exact integer dots of 16 rows x 8 tokens per tensor-core instruction.
+        const cudaError_t error = gather ? launch_tensor_core_tokens<F, true>(a, view, UPL, stream) : launch_tensor_core_tokens<F, false>(a, view, UPL, stream);
+        if (error != cudaErrorNotSupported) {
+            return error;
+        }
+    }
     // (rows so long that the sixteen warps form fewer teams than there are tokens would need several passes over the
     // weights: those keep the direct-load kernels, which loop over the tokens inside a warp)
     if (F::kTokenTeams && a.tokens >= 2 && one_pass && (uint64_t)(kTokenWarps / W) >= (a.tokens < 8 ? a.tokens : 8)) {
@@ -1113,3 +1125,5 @@ cudaError_t launch_format(const MatvecArgs &a, const WeightView *views, uint64_t
 
 }  // namespace mv
 }  // namespace syn
+
+#include "matvec_mma.cuh"

@@ -131,6 +131,46 @@ def test_tokens_are_batch_invariant(oracle):
             assert matrix.matvec(x[t:t + 1], sb.MODE_XQ8).tobytes() == together[t:t + 1].tobytes()
 
 
+# type, rows, columns. Q4_K: one-warp teams (28 units), ragged rows, two / five / seven team warps (the last ones partly
+# filled), the shortest row there is, and row lengths whose activations fit shared memory only for four or two tokens at
+# a time. Q6_K: one and two units per lane, second steps that are partly filled (3584: 24 of 32 lanes; 2304: 4; 18944:
+# five team warps, the last with 32 + 8 units).
+TENSOR_CORE_SHAPES = [(sb.Q4_K, 3584, 3584), (sb.Q4_K, 45, 3584), (sb.Q4_K, 130, 8192), (sb.Q4_K, 77, 18944), (sb.Q4_K, 33, 28672),
+                      (sb.Q4_K, 20, 256), (sb.Q4_K, 19, 4096), (sb.Q4_K, 64, 4352),
+                      (sb.Q6_K, 512, 3584), (sb.Q6_K, 45, 3584), (sb.Q6_K, 3584, 18944), (sb.Q6_K, 21, 256), (sb.Q6_K, 50, 2048),
+                      (sb.Q6_K, 18, 2304), (sb.Q6_K, 130, 8192), (sb.Q6_K, 33, 28672)]
+
+
+@pytest.mark.parametrize("ggml_type,rows,columns", TENSOR_CORE_SHAPES)
+@pytest.mark.parametrize("tokens", [2, 3, 5, 8, 9, 17])
+def test_kquant_token_groups_on_tensor_cores_equal_single_token_products(oracle, ggml_type, rows, columns, tokens):
+    """Q4_K and (planar) Q6_K with several tokens run on the integer tensor cores. Every token's row must carry the bits
+    of a launch of its own (OptimizedQwen2Tests.cs:41-54: a token's result does not depend on what shares its weight
+    pass), for every team shape, with accumulation, row ranges and strides, and the values must be the oracle's."""
+    if rows * columns > 20_000_000 and tokens not in (2, 8):
+        pytest.skip("the large shapes run at two and eight tokens")
+    weights = synth.matrix(ggml_type, rows, columns, seed=61 + rows)
+    x = synth.activations(tokens, columns, seed=62)
+    with sb.QuantizedMatrix(weights, ggml_type, rows, columns) as matrix:
+        together = matrix.matvec(x, sb.MODE_XQ8)
+        alone = np.concatenate([matrix.matvec(x[t:t + 1], sb.MODE_XQ8) for t in range(tokens)])
+        assert together.tobytes() == alone.tobytes()
+        first, count = rows // 3, rows - rows // 3 - 1
+        strided = np.full((tokens, count + 5), SENTINEL, np.float32)
+        matrix.matvec(x, sb.MODE_XQ8, row_start=first, row_count=count, output=strided, output_stride=count + 5)
+        assert strided[:, :count].tobytes() == np.ascontiguousarray(together[:, first:first + count]).tobytes()
+        assert np.all(strided[:, count:] == SENTINEL)
+        residual = synth.activations(tokens, rows, seed=64).copy()
+        accumulated = residual.copy()
+        matrix.matvec(x, sb.MODE_XQ8, epilogue=sb.EPILOGUE_ACCUMULATE, output=accumulated)
+        assert np.array_equal(accumulated, residual + together)
+        assert sb.library().device_faults() == 0
+    if rows * columns <= 20_000_000:
+        codes, scales = oracle.quantize(x)
+        exact, magnitude = oracle.kq_q8_exact(ggml_type, weights, rows, columns, codes, scales)
+        assert_parity(together, oracle.kq_q8_matmul(ggml_type, weights, rows, columns, codes, scales), exact, magnitude, "tensor-core token groups")
+
+
 def test_invalid_calls_fail_with_a_status_and_leave_outputs_untouched():
     weights = synth.matrix(sb.Q8_0, 4, 64, seed=41)
     with sb.QuantizedMatrix(weights, sb.Q8_0, 4, 64) as matrix:
