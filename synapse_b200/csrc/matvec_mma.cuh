@@ -22,23 +22,31 @@ namespace mv {
 
 constexpr int kMmaWarps = 16;                  // consumer warps
 constexpr uint32_t kMmaRows = 16;              // rows of a tile: M of the MMA
+constexpr uint32_t kMmaTokens = 8;             // tokens of a group: N of the MMA
+constexpr uint32_t kMmaChunkValues = 4096;     // the values one warp of a one-token team covers (32 lanes x UPL units)
 constexpr uint32_t kMmaShared = 220u * 1024u;  // dynamic shared memory of the kernel
 
+// Shared memory: [activation buffer 0][activation buffer 1 (rows longer than a chunk)][partial sums][running sums][stages].
+// An activation buffer holds, for the eight tokens of the group, the part of the quantised activations that goes with
+// one team warp's units (a chunk of at most 4096 values): codes | block scales | block sums. The CTA walks the chunks in
+// the outer loop and its row tiles in the inner one, so a chunk's activations are fetched once per CTA and the next
+// chunk's arrive (cp.async) while the current one is multiplied; the sums of a tile's finished chunks wait in the
+// running area.
 struct MmaArgs {
     WeightView weights;      // plane bases at the first row of the call
     uint64_t rows;
     uint32_t row_bytes;      // Q4_K: bytes of a row
     uint32_t K;
-    uint32_t units;          // F::units(K)
+    uint32_t units;          // values / Codec::kUnitValues
     uint32_t upl;            // units per lane of the one-token team
     uint32_t chunks;         // warps of the one-token team: ceil(units / (32 * upl))
     uint32_t tokens;
-    uint32_t tp;             // tokens per group (2, 4 or 8): how many tokens' activations shared memory holds
     uint32_t row_stride;     // bytes between the rows of a stage, chosen so that a warp's loads do not meet in a bank
-    uint32_t code_stride;    // bytes between the tokens' activation codes (the row length plus the same kind of padding)
-    uint32_t scale_stride;   // floats between the tokens' activation scales
-    uint32_t sum_stride;     // elements between the tokens' activation sums
-    uint32_t offset_scales, offset_sums, offset_partial, offset_stages;  // inside the dynamic shared memory
+    uint32_t code_stride;    // bytes between the tokens' activation codes in a buffer (chunk length plus the same kind of padding)
+    uint32_t scale_stride;   // 32-bit words between the tokens' block scales, and between their block sums
+    uint32_t buffer_bytes;   // one activation buffer
+    uint32_t offset_scales, offset_sums;  // inside an activation buffer
+    uint32_t offset_partial, offset_running, offset_stages;  // inside the dynamic shared memory
     uint32_t offset_tail;    // Q6_K: where, inside a stage, the tile's super-block scales (the d plane) start
     uint32_t stage_bytes, stages;
 };
@@ -58,12 +66,11 @@ __device__ __forceinline__ void mma_u8s8_k16(int (&c)[4], uint32_t a0, uint32_t 
 
 // What the consumer side of a codec sees.
 struct MmaContext {
-    const uint8_t *codes;   // activation codes of the group, token t at t * code_stride
-    const float *scales;    // block scales, token t at t * scale_stride
-    const void *sums;       // per-format sums, token t at t * sum_stride elements
-    uint32_t g, tig;        // the MMA's group (lane / 4) and thread-in-group (lane % 4)
-    uint32_t bt;            // the token whose codes this thread feeds to the MMA (column g of B)
-    uint32_t t0, t1;        // the tokens of this thread's accumulator columns (2 tig, 2 tig + 1)
+    const uint8_t *codes;   // the chunk's activation codes, token t at t * code_stride
+    const float *scales;    // its block scales, token t at t * scale_stride
+    const void *sums;       // its block sums (per format), token t at t * scale_stride words
+    uint32_t g, tig;        // the MMA's group (lane / 4) and thread-in-group (lane % 4): B column g, C columns 2 tig, 2 tig + 1
+    uint32_t chunk_unit;    // first unit of the chunk
     uint32_t tail_shift;    // Q6_K: where the tile's part of the d plane starts inside its 16-byte-aligned copy
 };
 
@@ -81,11 +88,8 @@ struct Q4KMma {
         m.row_stride = (uint32_t)align_up(piece, 128) + 32;  // 8-byte loads of rows g = 0..3 and tig = 0..3 cover the 32 banks
         m.offset_tail = 0;
         m.stage_bytes = kMmaRows * m.row_stride;
-        m.code_stride = m.K + 32;
-        m.scale_stride = m.K / 32 + 4;
-        m.sum_stride = m.K / 32 + 4;  // floats: scale * (sum of the block's codes)
+        m.code_stride = (m.K < kMmaChunkValues ? m.K : kMmaChunkValues) + 32;
     }
-    static uint64_t sums_bytes(const MmaArgs &m, uint32_t tp) { return (uint64_t)tp * m.sum_stride * 4; }
 
     static __device__ __forceinline__ void produce(const MmaArgs &m, uint32_t stage, uint64_t row0, uint32_t n, uint32_t w, uint32_t j, uint32_t lane,
                                                    uint32_t bar, uint64_t policy)
@@ -100,16 +104,17 @@ struct Q4KMma {
             bulk_copy(stage + lane * m.row_stride, m.weights.p0 + (row0 + lane) * m.row_bytes + (uint64_t)first * 72, piece, bar, policy);
         }
     }
-    // scale * (sum of the block's codes) for the min term, as Q4KXq8::load_act computes it
-    static __device__ __forceinline__ void store_sums(const MmaArgs &m, const ActView &act, uint64_t token, bool live, uint32_t t, uint32_t block, float d,
-                                                      void *sums)
+    // The block sums arrive as the quantiser's pairs of 16-code sums; the min term wants scale * (sum of the block's
+    // codes), computed as Q4KXq8::load_act computes it, in place.
+    static __device__ __forceinline__ void finish_sums(const MmaArgs &m, uint8_t *buffer, uint32_t blocks, uint32_t thread, uint32_t threads)
     {
-        float ds = 0.0f;
-        if (live) {
-            const uint32_t pair = __ldg(reinterpret_cast<const uint32_t *>(act.sums + token * (m.K / 16)) + block);
-            ds = d * (float)((int)(short)(pair & 0xffff) + (int)(short)(pair >> 16));
+        const float *const scales = reinterpret_cast<const float *>(buffer + m.offset_scales);
+        uint32_t *const sums = reinterpret_cast<uint32_t *>(buffer + m.offset_sums);
+        for (uint32_t i = thread; i < kMmaTokens * blocks; i += threads) {
+            const uint32_t index = (i / blocks) * m.scale_stride + i % blocks;
+            const uint32_t pair = sums[index];
+            sums[index] = __float_as_uint(scales[index] * (float)((int)(short)(pair & 0xffff) + (int)(short)(pair >> 16)));
         }
-        static_cast<float *>(sums)[t * m.sum_stride + block] = ds;
     }
 
     // Adds unit `u` (lane `local` of chunk w, step j) to the accumulators of this thread's four (row, token) pairs.
@@ -122,7 +127,8 @@ struct Q4KMma {
         // positions of the activation codes below
         const uint2 a00 = *reinterpret_cast<const uint2 *>(r0 + q), a01 = *reinterpret_cast<const uint2 *>(r0 + q + 32);
         const uint2 a10 = *reinterpret_cast<const uint2 *>(r1 + q), a11 = *reinterpret_cast<const uint2 *>(r1 + q + 32);
-        const uint8_t *const b = c.codes + c.bt * m.code_stride + u * 128 + 8 * c.tig;
+        const uint32_t ur = u - c.chunk_unit;  // the unit's place in the chunk
+        const uint8_t *const b = c.codes + c.g * m.code_stride + ur * 128 + 8 * c.tig;
         const uint2 b0 = *reinterpret_cast<const uint2 *>(b), b1 = *reinterpret_cast<const uint2 *>(b + 32);
         const uint2 b2 = *reinterpret_cast<const uint2 *>(b + 64), b3 = *reinterpret_cast<const uint2 *>(b + 96);
         int lo0[4], hi0[4], lo1[4], hi1[4];
@@ -147,10 +153,9 @@ struct Q4KMma {
         const float d[2] = {half_bits_to_float(h0.x & 0xffff), half_bits_to_float(h1.x & 0xffff)};
         const float dmin[2] = {half_bits_to_float(h0.x >> 16), half_bits_to_float(h1.x >> 16)};
         const float *const sums = static_cast<const float *>(c.sums);
-        const float4 ad[2] = {*reinterpret_cast<const float4 *>(c.scales + c.t0 * m.scale_stride + u * 4),
-                              *reinterpret_cast<const float4 *>(c.scales + c.t1 * m.scale_stride + u * 4)};
-        const float4 as[2] = {*reinterpret_cast<const float4 *>(sums + c.t0 * m.sum_stride + u * 4),
-                              *reinterpret_cast<const float4 *>(sums + c.t1 * m.sum_stride + u * 4)};
+        const uint32_t first = 2 * c.tig * m.scale_stride + ur * 4;  // token 2 tig; token 2 tig + 1 is scale_stride further
+        const float4 ad[2] = {*reinterpret_cast<const float4 *>(c.scales + first), *reinterpret_cast<const float4 *>(c.scales + first + m.scale_stride)};
+        const float4 as[2] = {*reinterpret_cast<const float4 *>(sums + first), *reinterpret_cast<const float4 *>(sums + first + m.scale_stride)};
         // accumulator [2 * row + token]: row g / g + 8, token 2 tig / 2 tig + 1 -- the MMA's C fragment order
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
@@ -187,11 +192,8 @@ struct Q6KMma {
         m.offset_tail = kMmaRows * m.row_stride;
         // the 16 rows' super-block scales are contiguous in their plane: one copy from the 16-byte boundary below them
         m.stage_bytes = (uint32_t)align_up(m.offset_tail + kMmaRows * (m.K / 128) + 32, 128);
-        m.code_stride = m.K + 16;
-        m.scale_stride = m.K / 32 + 4;
-        m.sum_stride = m.K / 16 + 8;  // int16: the sums of every 16 codes
+        m.code_stride = (m.K < kMmaChunkValues ? m.K : kMmaChunkValues) + 16;
     }
-    static uint64_t sums_bytes(const MmaArgs &m, uint32_t tp) { return (uint64_t)tp * m.sum_stride * 2; }
 
     static __device__ __forceinline__ void produce(const MmaArgs &m, uint32_t stage, uint64_t row0, uint32_t n, uint32_t w, uint32_t j, uint32_t lane,
                                                    uint32_t bar, uint64_t policy)
@@ -214,16 +216,8 @@ struct Q6KMma {
             bulk_copy(base + sbs * 192, m.weights.p2 + row * (m.K / 16) + (uint64_t)sb0 * 16, sbs * 16, bar, policy);
         }
     }
-    static __device__ __forceinline__ void store_sums(const MmaArgs &m, const ActView &act, uint64_t token, bool live, uint32_t t, uint32_t index, float,
-                                                      void *sums)
-    {
-        // two of the int16 sums per call (index counts pairs)
-        uint32_t pair = 0;
-        if (live) {
-            pair = __ldg(reinterpret_cast<const uint32_t *>(act.sums + token * (m.K / 16)) + index);
-        }
-        reinterpret_cast<uint32_t *>(static_cast<int16_t *>(sums) + t * m.sum_stride)[index] = pair;
-    }
+    // the quantiser's sums of every 16 codes are used as they are
+    static __device__ __forceinline__ void finish_sums(const MmaArgs &, uint8_t *, uint32_t, uint32_t, uint32_t) {}
 
     static __device__ __forceinline__ void unit(const MmaArgs &m, const MmaContext &c, const uint8_t *stage, uint32_t local, uint32_t u, float (&acc)[4])
     {
@@ -240,7 +234,8 @@ struct Q6KMma {
         q6k_codes(a0, b0, h0, v0[0], v0[1], v0[2], v0[3]);
         q6k_codes(a1, b1, h1, v1[0], v1[1], v1[2], v1[3]);
         // activation codes of group q: 16 codes at sb * 256 + h * 128 + i * 16 + 32 q of the row; this thread's four
-        const uint8_t *const b = c.codes + c.bt * m.code_stride + (u >> 2) * 256 + h * 128 + i * 16 + 4 * c.tig;
+        const uint32_t ur = u - c.chunk_unit;  // the unit's place in the chunk
+        const uint8_t *const b = c.codes + c.g * m.code_stride + (ur >> 2) * 256 + h * 128 + i * 16 + 4 * c.tig;
         int dots[4][4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -253,9 +248,9 @@ struct Q6KMma {
         const float d[2] = {half_bits_to_float(*reinterpret_cast<const unsigned short *>(tail + (c.g * (m.K / 256) + (u >> 2)) * 2)),
                             half_bits_to_float(*reinterpret_cast<const unsigned short *>(tail + ((c.g + 8) * (m.K / 256) + (u >> 2)) * 2))};
         const int16_t *const sums = static_cast<const int16_t *>(c.sums);
-        const float4 ad[2] = {*reinterpret_cast<const float4 *>(c.scales + c.t0 * m.scale_stride + (u >> 1) * 4),
-                              *reinterpret_cast<const float4 *>(c.scales + c.t1 * m.scale_stride + (u >> 1) * 4)};
-        const int16_t *const as[2] = {sums + c.t0 * m.sum_stride + (u >> 1) * 8 + i, sums + c.t1 * m.sum_stride + (u >> 1) * 8 + i};
+        const uint32_t block = 2 * c.tig * m.scale_stride + (ur >> 1) * 4;  // token 2 tig; token 2 tig + 1 is scale_stride further
+        const float4 ad[2] = {*reinterpret_cast<const float4 *>(c.scales + block), *reinterpret_cast<const float4 *>(c.scales + block + m.scale_stride)};
+        const int16_t *const as[2] = {sums + 2 * block + i, sums + 2 * (block + m.scale_stride) + i};
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const uint32_t word0 = q < 2 ? s0.x : s0.y, word1 = q < 2 ? s1.x : s1.y;
@@ -272,6 +267,42 @@ struct Q6KMma {
         }
     }
 };
+
+__device__ __forceinline__ void copy16_async(void *shared, const void *global)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(shared)), "l"(global) : "memory");
+}
+__device__ __forceinline__ void copies_async_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// Starts the copy of chunk w's activations (the group's tokens token0 .. token0 + live - 1; the others read as zero)
+// into `buffer`: 16-byte pieces, asynchronous where they come from memory.
+__device__ __forceinline__ void fetch_chunk(const MmaArgs &m, const ActView &act, uint64_t token0, uint32_t live, uint32_t w, uint8_t *buffer, uint32_t thread,
+                                            uint32_t threads)
+{
+    const uint32_t value0 = w * kMmaChunkValues, values = min(kMmaChunkValues, m.K - value0);
+    const uint32_t code_pieces = values / 16, word_pieces = values / 128;  // 16-byte pieces per token: codes; scales and sums (4 bytes per 32 values)
+    const uint32_t per_token = code_pieces + 2 * word_pieces;
+    for (uint32_t i = thread; i < kMmaTokens * per_token; i += threads) {
+        const uint32_t t = i / per_token, piece = i % per_token;
+        uint8_t *destination;
+        const uint8_t *source;
+        if (piece < code_pieces) {
+            destination = buffer + t * m.code_stride + piece * 16;
+            source = reinterpret_cast<const uint8_t *>(act.codes) + (token0 + t) * m.K + value0 + piece * 16;
+        } else if (piece < code_pieces + word_pieces) {
+            destination = buffer + m.offset_scales + t * m.scale_stride * 4 + (piece - code_pieces) * 16;
+            source = reinterpret_cast<const uint8_t *>(act.scales) + ((token0 + t) * (m.K / 32) + value0 / 32) * 4 + (piece - code_pieces) * 16;
+        } else {
+            destination = buffer + m.offset_sums + t * m.scale_stride * 4 + (piece - code_pieces - word_pieces) * 16;
+            source = reinterpret_cast<const uint8_t *>(act.sums) + ((token0 + t) * (m.K / 16) + value0 / 16) * 2 + (piece - code_pieces - word_pieces) * 16;
+        }
+        if (t < live) {
+            copy16_async(destination, source);
+        } else {
+            *reinterpret_cast<uint4 *>(destination) = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
 
 template <class Codec, bool GATHER>
 __global__ void __launch_bounds__(kMmaWarps * 32 + 32, 1)
@@ -294,14 +325,14 @@ matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_st
     pdl_launch_dependents();
 
     if (warp == kMmaWarps) {
-        // ---- producer: one stage per (tile, team warp w, step j), one bulk copy per row and plane ----
+        // ---- producer: one stage per (team warp w, tile, step j), one bulk copy per row and plane ----
         const uint64_t policy = l2_evict_first_policy();
         const uint32_t stage0 = smem_u32(mma_memory) + m.offset_stages;
         uint32_t s = 0, round = 0;
-        for (uint32_t it = 0; it < my_tiles; ++it) {
-            const uint64_t row0 = ((uint64_t)blockIdx.x + (uint64_t)it * gridDim.x) * kMmaRows;
-            const uint32_t n = (uint32_t)min((uint64_t)kMmaRows, m.rows - row0);
-            for (uint32_t w = 0; w < m.chunks; ++w) {
+        for (uint32_t w = 0; w < m.chunks; ++w) {
+            for (uint32_t it = 0; it < my_tiles; ++it) {
+                const uint64_t row0 = ((uint64_t)blockIdx.x + (uint64_t)it * gridDim.x) * kMmaRows;
+                const uint32_t n = (uint32_t)min((uint64_t)kMmaRows, m.rows - row0);
                 for (uint32_t j = 0; j < m.upl; ++j) {
                     if ((w * m.upl + j) * 32 >= m.units) {
                         break;  // the last team warp's lanes have no unit at this step
@@ -322,49 +353,36 @@ matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_st
 
     // ---- consumers ---------------------------------------------------------------------------------------
     constexpr uint32_t kThreads = kMmaWarps * 32;
-    const uint64_t token0 = (uint64_t)blockIdx.y * m.tp;
-    const uint32_t live = min(m.tp, m.tokens - (uint32_t)token0);
-    float *const scales = reinterpret_cast<float *>(mma_memory + m.offset_scales);
-    void *const sums = mma_memory + m.offset_sums;
+    const uint64_t token0 = (uint64_t)blockIdx.y * kMmaTokens;
+    const uint32_t live = min(kMmaTokens, m.tokens - (uint32_t)token0);
     float *const partial = reinterpret_cast<float *>(mma_memory + m.offset_partial);  // [2][kMmaWarps][128]
+    float *const running = reinterpret_cast<float *>(mma_memory + m.offset_running);  // [my_tiles][128] when the team has several warps
 
     pdl_wait();
-    {
-        // the group's quantised activations: codes, block scales, and the sums the format's offset term needs
-        const uint32_t pieces = m.K / 16, blocks = m.K / 32;
-        for (uint32_t i = threadIdx.x; i < m.tp * pieces; i += kThreads) {
-            const uint32_t t = i / pieces, piece = i % pieces;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (t < live) {
-                v = __ldg(reinterpret_cast<const uint4 *>(act.codes + (token0 + t) * m.K) + piece);
-            }
-            *reinterpret_cast<uint4 *>(mma_memory + t * m.code_stride + piece * 16) = v;
-        }
-        for (uint32_t i = threadIdx.x; i < m.tp * blocks; i += kThreads) {
-            const uint32_t t = i / blocks, block = i % blocks;
-            const float d = t < live ? __ldg(act.scales + (token0 + t) * blocks + block) : 0.0f;
-            scales[t * m.scale_stride + block] = d;
-            Codec::store_sums(m, act, token0 + t, t < live, t, block, d, sums);
-        }
-    }
+    fetch_chunk(m, act, token0, live, 0, mma_memory, threadIdx.x, kThreads);
+    copies_async_wait();
+    consumer_barrier<kThreads>();
+    Codec::finish_sums(m, mma_memory, min(kMmaChunkValues, m.K) / 32, threadIdx.x, kThreads);
     consumer_barrier<kThreads>();
 
     MmaContext c;
-    c.codes = mma_memory;
-    c.scales = scales;
-    c.sums = sums;
     c.g = lane >> 2;
     c.tig = lane & 3;
-    c.bt = min(c.g, m.tp - 1);
-    c.t0 = min(2 * c.tig, m.tp - 1);
-    c.t1 = min(2 * c.tig + 1, m.tp - 1);
     const uint32_t out_row = threadIdx.x >> 3, out_token = threadIdx.x & 7;  // the pair a combining thread owns
-    float running = 0.0f;
     uint32_t s = 0, phase = 0, buffer = 0;
-    for (uint32_t it = 0; it < my_tiles; ++it) {
-        const uint64_t row0 = ((uint64_t)blockIdx.x + (uint64_t)it * gridDim.x) * kMmaRows;
-        c.tail_shift = (uint32_t)(reinterpret_cast<uintptr_t>(m.weights.p3 + row0 * (m.K / 128)) & 15);
-        for (uint32_t w = 0; w < m.chunks; ++w) {
+    for (uint32_t w = 0; w < m.chunks; ++w) {
+        uint8_t *const acts = mma_memory + (w & 1) * m.buffer_bytes;
+        if (w + 1 < m.chunks) {
+            // the other buffer was last read in chunk w - 1, which every warp has left (the barrier that ended it)
+            fetch_chunk(m, act, token0, live, w + 1, mma_memory + ((w + 1) & 1) * m.buffer_bytes, threadIdx.x, kThreads);
+        }
+        c.codes = acts;
+        c.scales = reinterpret_cast<const float *>(acts + m.offset_scales);
+        c.sums = acts + m.offset_sums;
+        c.chunk_unit = w * m.upl * 32;
+        for (uint32_t it = 0; it < my_tiles; ++it) {
+            const uint64_t row0 = ((uint64_t)blockIdx.x + (uint64_t)it * gridDim.x) * kMmaRows;
+            c.tail_shift = (uint32_t)(reinterpret_cast<uintptr_t>(m.weights.p3 + row0 * (m.K / 128)) & 15);
             float acc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};  // lanes warp and warp + 16 of team warp w
             for (uint32_t j = 0; j < m.upl; ++j) {
                 const uint32_t first = (w * m.upl + j) * 32;
@@ -408,12 +426,21 @@ matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_st
                 }
                 const float c0 = level[0] + level[4], c1 = level[1] + level[5], c2 = level[2] + level[6], c3 = level[3] + level[7];  // offset 4
                 const float e = (c0 + c2) + (c1 + c3);  // offsets 2 and 1
-                running = w == 0 ? e : running + e;      // the team's warps in index order
-                if (w + 1 == m.chunks && row0 + out_row < m.rows && out_token < live) {
-                    store_result<GATHER>(epilogue, y, token0 + out_token, out_stride, row0 + out_row, running);
+                // the team's warps in index order
+                const float total = w == 0 ? e : running[it * 128 + threadIdx.x] + e;
+                if (w + 1 < m.chunks) {
+                    running[it * 128 + threadIdx.x] = total;
+                } else if (row0 + out_row < m.rows && out_token < live) {
+                    store_result<GATHER>(epilogue, y, token0 + out_token, out_stride, row0 + out_row, total);
                 }
             }
             buffer ^= 1;
+        }
+        if (w + 1 < m.chunks) {
+            copies_async_wait();
+            consumer_barrier<kThreads>();
+            Codec::finish_sums(m, mma_memory + ((w + 1) & 1) * m.buffer_bytes, min(kMmaChunkValues, m.K - (w + 1) * kMmaChunkValues) / 32, threadIdx.x, kThreads);
+            consumer_barrier<kThreads>();
         }
     }
     if (GATHER) {
@@ -424,8 +451,8 @@ matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_st
     }
 }
 
-// Lays the shared memory out for `a` and launches; cudaErrorNotSupported when not even two tokens' activations and two
-// stages fit (very long rows), so that the caller falls back to the dp4a kernels.
+// Lays the shared memory out for `a` and launches; cudaErrorNotSupported when two stages and the running sums of the
+// CTA's tiles do not fit beside the activation buffers, so that the caller falls back to the dp4a kernels.
 template <class Codec, bool GATHER>
 cudaError_t launch_mma(const MatvecArgs &a, const WeightView &view, uint32_t upl, cudaStream_t stream)
 {
@@ -438,26 +465,29 @@ cudaError_t launch_mma(const MatvecArgs &a, const WeightView &view, uint32_t upl
     m.upl = upl;
     m.chunks = (m.units + 32 * upl - 1) / (32 * upl);
     m.tokens = (uint32_t)a.tokens;
-    Codec::layout(m);
-    const uint32_t fixed = 2 * kMmaWarps * 128 * 4;  // the partial sums, double-buffered
-    m.tp = 0;
-    for (uint32_t tp = 8; tp >= 2; tp /= 2) {
-        const uint64_t codes = align_up((uint64_t)tp * m.code_stride, 128), scales = align_up((uint64_t)tp * m.scale_stride * 4, 128);
-        const uint64_t sums = align_up(Codec::sums_bytes(m, tp), 128);
-        if (codes + scales + sums + fixed + 2ull * m.stage_bytes <= kMmaShared && (tp == 2 || tp / 2 < a.tokens)) {
-            m.tp = tp;
-            m.offset_scales = (uint32_t)codes;
-            m.offset_sums = (uint32_t)(codes + scales);
-            m.offset_partial = (uint32_t)(codes + scales + sums);
-            m.offset_stages = m.offset_partial + fixed;
-            const uint64_t stages = (kMmaShared - m.offset_stages) / m.stage_bytes;
-            m.stages = (uint32_t)(stages > kMaxStages ? kMaxStages : stages);
-            break;
-        }
+    if (m.chunks > 1 && upl * 32 * Codec::kUnitValues != kMmaChunkValues) {
+        return cudaErrorNotSupported;  // a team warp always covers 4096 values when the team has several
     }
-    if (m.tp == 0) {
+    Codec::layout(m);
+    const uint32_t chunk_values = m.K < kMmaChunkValues ? m.K : kMmaChunkValues;
+    m.scale_stride = chunk_values / 32 + 4;
+    m.offset_scales = (uint32_t)align_up((uint64_t)kMmaTokens * m.code_stride, 128);
+    m.offset_sums = m.offset_scales + (uint32_t)align_up((uint64_t)kMmaTokens * m.scale_stride * 4, 128);
+    m.buffer_bytes = m.offset_sums + (uint32_t)align_up((uint64_t)kMmaTokens * m.scale_stride * 4, 128);
+    uint64_t ctas = (a.row_count + kMmaRows - 1) / kMmaRows;
+    const uint64_t cap = (uint64_t)sm_count(a.matrix->device);
+    const uint64_t tiles_per_cta = ctas > cap ? (ctas + cap - 1) / cap : 1;
+    if (ctas > cap) {
+        ctas = cap;
+    }
+    m.offset_partial = (m.chunks > 1 ? 2 : 1) * m.buffer_bytes;
+    m.offset_running = m.offset_partial + 2 * kMmaWarps * 128 * 4;  // the partial sums, double-buffered
+    m.offset_stages = m.offset_running + (m.chunks > 1 ? (uint32_t)tiles_per_cta * 128 * 4 : 0);
+    if (m.offset_stages + 2ull * m.stage_bytes > kMmaShared) {
         return cudaErrorNotSupported;
     }
+    const uint64_t stages = (kMmaShared - m.offset_stages) / m.stage_bytes;
+    m.stages = (uint32_t)(stages > kMaxStages ? kMaxStages : stages);
     auto kernel = matvec_mma_kernel<Codec, GATHER>;
     static PerDevice configured;
     if (configured.first_use(a.matrix->device)) {
@@ -467,12 +497,7 @@ cudaError_t launch_mma(const MatvecArgs &a, const WeightView &view, uint32_t upl
             return error;
         }
     }
-    uint64_t ctas = (a.row_count + kMmaRows - 1) / kMmaRows;
-    const uint64_t cap = (uint64_t)sm_count(a.matrix->device);
-    if (ctas > cap) {
-        ctas = cap;
-    }
-    const dim3 grid((unsigned)ctas, (unsigned)((a.tokens + m.tp - 1) / m.tp));
+    const dim3 grid((unsigned)ctas, (unsigned)((a.tokens + kMmaTokens - 1) / kMmaTokens));
     return launch_kernel(kernel, grid, dim3(kMmaWarps * 32 + 32), (size_t)kMmaShared, stream, m, a.act, a.y, a.out_stride, a.fused, fault_word_device());
 }
 
