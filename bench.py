@@ -648,6 +648,8 @@ def main():
     extras = None
     if world == 1 and not args.no_e2e:
         extras = {}
+        # the same model through the decoder with several tokens per step (projections on the integer tensor cores)
+        extras["qwen2.5-7b_q4_k_m_batched_decode"] = bench_extras.batched_decode(dec, image)
         # config 3: the tensor-core product over the token counts and matrices the baseline names
         extras["prefill"] = bench_extras.prefill_sweep(sb, lib, torch, device, stream, ROOT)
         # config 1: the Qwen2.5-0.5B-shaped all-Q8_0 decode step through the decoder, greedy pick on the device
@@ -713,6 +715,7 @@ def main():
         }
         # several tokens per launch (batched decode, speculative verification): every weight is read once per launch
         extras["matvec_q4_k_18944x3584_tokens"] = {str(t): kernel_rate(synth.Q4_K, 18944, 3584, 4, tokens=t) for t in (2, 4, 8)}
+        extras["matvec_q6_k_3584x18944_tokens"] = {str(t): kernel_rate(synth.Q6_K, 3584, 18944, 3, tokens=t) for t in (2, 4, 8)}
         # the FP32-activation contract of the reference backend on the two big layer shapes
         extras["matvec_xf32_batch1"] = bench_extras.xf32_rates(sb, lib, torch, device, stream, peak)
 

@@ -209,6 +209,37 @@ def config4_sweep(sb, lib, torch, dist, device, stream, world, rank, peak, use_p
     return out
 
 
+def batched_decode(dec, image):
+    """The decoder on several tokens per step: 2 / 4 / 8 sessions decoding together (one token each per step, greedy pick
+    on the device) and a 64-token prompt run of one session (``syn_b200_decoder_forward_argmax``, host tokens in, token
+    ids out). Same model image as the single-session `e2e`; only the slot and step sizes of the descriptor differ."""
+    import copy
+
+    wide = copy.copy(image)
+    wide.shape = dict(image.shape, session_slots=8, step_tokens=64, logits_rows=8)
+    out = {}
+    with dec.Decoder(wide) as model:
+        for sessions in (2, 4, 8):
+            tokens = [11 + s for s in range(sessions)]
+            for position in range(3):
+                tokens = model.forward_argmax([(s, tokens[s], position, s) for s in range(sessions)])
+            steps = 10
+            start = time.perf_counter()
+            for position in range(3, 3 + steps):
+                tokens = model.forward_argmax([(s, tokens[s], position, s) for s in range(sessions)])
+            seconds = time.perf_counter() - start
+            out[f"{sessions} sessions"] = {"ms_per_step": seconds / steps * 1e3, "tokens_per_s": sessions * steps / seconds}
+        prompt = [(0, 100 + p, p, 0 if p == 63 else -1) for p in range(64)]
+        model.forward_argmax(prompt)
+        runs = 3
+        start = time.perf_counter()
+        for _ in range(runs):
+            model.forward_argmax(prompt)
+        seconds = time.perf_counter() - start
+        out["64-token prompt run"] = {"ms_per_run": seconds / runs * 1e3, "tokens_per_s": 64 * runs / seconds}
+    return out
+
+
 def parity_summary(sb, torch):
     """Counts for the record (the assertions live in tests/): how many outputs of the benchmark's dominant shape pass on
     the summation-order gate instead of the 1e-3 relative one, and which share of tensor-core outputs is inside 1e-3."""
