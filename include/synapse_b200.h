@@ -310,7 +310,10 @@ SYN_B200_API int32_t syn_b200_enable_peer_access(int32_t peer_device);
  * syn_b200_activation_scratch_bytes). XF32 mode needs no scratch; a caller that passes one of at least
  * syn_b200_gemm_scratch_bytes thereby opts into the reference's projection rule (step/projection.rs:14,51-72): whole-matrix
  * products of more than 4 tokens with a plain store then run on the tensor cores with fp16 operands (SYN_B200_GEMM_F16),
- * everything else on the FP32-activation matrix-vector kernels. */
+ * everything else on the FP32-activation matrix-vector kernels.
+ * XQ8 mode with several tokens (the reference's matvec_{2,4,8}, cuda/kernels/matmul.cu:79-145): Q4_K and repacked Q6_K
+ * take the exact integer block dots on the tensor cores (mma.sync, u8 x s8), eight tokens per weight pass; a token's
+ * result carries the bits of a single-token call whatever shares its pass. */
 SYN_B200_API int32_t syn_b200_matvec_dev(const syn_b200_matrix *matrix, uint64_t row_start, uint64_t row_count,
                             const float *x, uint64_t tokens, uint64_t in_stride, float *y, uint64_t out_stride,
                             uint32_t mode, uint32_t epilogue, void *scratch, uint64_t scratch_bytes,

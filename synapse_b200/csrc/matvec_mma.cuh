@@ -20,13 +20,15 @@
 namespace syn {
 namespace mv {
 
-constexpr int kMmaWarps = 16;                  // consumer warps
+constexpr int kMmaWarps = 16;                  // multiplying warps
+constexpr int kMmaCombineWarps = 4;            // 128 threads, one per (row, token) of a tile, that add the warps' partial sums
+constexpr uint32_t kMmaSlots = 4;              // sets of partial sums in flight between the two, at most
 constexpr uint32_t kMmaRows = 16;              // rows of a tile: M of the MMA
 constexpr uint32_t kMmaTokens = 8;             // tokens of a group: N of the MMA
 constexpr uint32_t kMmaChunkValues = 4096;     // the values one warp of a one-token team covers (32 lanes x UPL units)
 constexpr uint32_t kMmaShared = 220u * 1024u;  // dynamic shared memory of the kernel
 
-// Shared memory: [activation buffer 0][activation buffer 1 (rows longer than a chunk)][partial sums][running sums][stages].
+// Shared memory: [activation buffer 0][activation buffer 1 (rows longer than a chunk)][ring of partial sums][running sums][stages].
 // An activation buffer holds, for the eight tokens of the group, the part of the quantised activations that goes with
 // one team warp's units (a chunk of at most 4096 values): codes | block scales | block sums. The CTA walks the chunks in
 // the outer loop and its row tiles in the inner one, so a chunk's activations are fetched once per CTA and the next
@@ -49,6 +51,7 @@ struct MmaArgs {
     uint32_t offset_partial, offset_running, offset_stages;  // inside the dynamic shared memory
     uint32_t offset_tail;    // Q6_K: where, inside a stage, the tile's super-block scales (the d plane) start
     uint32_t stage_bytes, stages;
+    uint32_t slots;          // sets of partial sums in the ring (kMmaSlots, or two when that buys a third stage)
 };
 
 __device__ __forceinline__ void mma_u8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
@@ -64,14 +67,52 @@ __device__ __forceinline__ void mma_u8s8_k16(int (&c)[4], uint32_t a0, uint32_t 
         : "r"(a0), "r"(a1), "r"(b0), "r"(0), "r"(0), "r"(0), "r"(0));
 }
 
-// What the consumer side of a codec sees.
+// Shared-memory loads by 32-bit shared address with a constant byte offset. (Plain C++ loads through pointers kept in a
+// struct cost 64-bit address arithmetic per access: a third of this kernel's instructions before these were used.)
+// volatile: they must stay behind the wait for the stage and ahead of its hand-back.
+template <int OFFSET = 0>
+__device__ __forceinline__ uint4 lds128(uint32_t a)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a), "n"(OFFSET));
+    return v;
+}
+template <int OFFSET = 0>
+__device__ __forceinline__ float4 lds128f(uint32_t a)
+{
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a), "n"(OFFSET));
+    return v;
+}
+template <int OFFSET = 0>
+__device__ __forceinline__ uint2 lds64(uint32_t a)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(a), "n"(OFFSET));
+    return v;
+}
+template <int OFFSET = 0>
+__device__ __forceinline__ uint32_t lds32(uint32_t a)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFFSET));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a)
+{
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+
+// What a multiplying thread knows about its place: byte offsets and 32-bit shared addresses, set once per chunk.
 struct MmaContext {
-    const uint8_t *codes;   // the chunk's activation codes, token t at t * code_stride
-    const float *scales;    // its block scales, token t at t * scale_stride
-    const void *sums;       // its block sums (per format), token t at t * scale_stride words
     uint32_t g, tig;        // the MMA's group (lane / 4) and thread-in-group (lane % 4): B column g, C columns 2 tig, 2 tig + 1
-    uint32_t chunk_unit;    // first unit of the chunk
-    uint32_t tail_shift;    // Q6_K: where the tile's part of the d plane starts inside its 16-byte-aligned copy
+    uint32_t row0, row8;    // offset of row g inside a stage, and the distance to row g + 8
+    uint32_t codes;         // the chunk's activation codes of token g, at this thread's k positions
+    uint32_t scales, sums;  // the chunk's block scales and block sums of token 2 tig
+    uint32_t token_step;    // distance to token 2 tig + 1 in both
+    uint32_t tail;          // Q6_K: offset of row g's super-block scales inside a stage (the tile's shift included)
 };
 
 // ------------------------------------------------------------------------------------------------------
@@ -117,20 +158,29 @@ struct Q4KMma {
         }
     }
 
-    // Adds unit `u` (lane `local` of chunk w, step j) to the accumulators of this thread's four (row, token) pairs.
-    static __device__ __forceinline__ void unit(const MmaArgs &m, const MmaContext &c, const uint8_t *stage, uint32_t local, uint32_t u, float (&acc)[4])
+    static __device__ __forceinline__ void place(const MmaArgs &m, MmaContext &c, uint32_t buffer)
     {
-        const uint8_t *const r0 = stage + c.g * m.row_stride + (local >> 1) * 144, *const r1 = r0 + 8 * m.row_stride;
-        const uint4 h0 = *reinterpret_cast<const uint4 *>(r0), h1 = *reinterpret_cast<const uint4 *>(r1);
-        const uint32_t q = 16 + (local & 1) * 64 + 8 * c.tig;
+        c.row0 = c.g * m.row_stride;
+        c.row8 = 8 * m.row_stride;
+        c.codes = buffer + c.g * m.code_stride + 8 * c.tig;
+        c.scales = buffer + m.offset_scales + 2 * c.tig * m.scale_stride * 4;
+        c.sums = buffer + m.offset_sums + 2 * c.tig * m.scale_stride * 4;
+        c.token_step = m.scale_stride * 4;
+    }
+    static __device__ __forceinline__ void place_tile(const MmaArgs &, MmaContext &, uint64_t) {}
+
+    // Adds unit `u` (lane `local` of team warp w at step j; unit `ur` of the chunk) to the accumulators of this thread's
+    // four (row, token) pairs. `stage` is the stage's shared address.
+    static __device__ __forceinline__ void unit(const MmaArgs &, const MmaContext &c, uint32_t stage, uint32_t local, uint32_t ur, uint32_t, float (&acc)[4])
+    {
+        const uint32_t block = stage + c.row0 + (local >> 1) * 144;
+        const uint4 h0 = lds128(block), h1 = lds128(block + c.row8);
         // this thread's eight bytes of each 32-byte nibble run: k positions (tig, byte) of the MMA, and the same eight
         // positions of the activation codes below
-        const uint2 a00 = *reinterpret_cast<const uint2 *>(r0 + q), a01 = *reinterpret_cast<const uint2 *>(r0 + q + 32);
-        const uint2 a10 = *reinterpret_cast<const uint2 *>(r1 + q), a11 = *reinterpret_cast<const uint2 *>(r1 + q + 32);
-        const uint32_t ur = u - c.chunk_unit;  // the unit's place in the chunk
-        const uint8_t *const b = c.codes + c.g * m.code_stride + ur * 128 + 8 * c.tig;
-        const uint2 b0 = *reinterpret_cast<const uint2 *>(b), b1 = *reinterpret_cast<const uint2 *>(b + 32);
-        const uint2 b2 = *reinterpret_cast<const uint2 *>(b + 64), b3 = *reinterpret_cast<const uint2 *>(b + 96);
+        const uint32_t q = block + 16 + (local & 1) * 64 + 8 * c.tig;
+        const uint2 a00 = lds64<0>(q), a01 = lds64<32>(q), a10 = lds64<0>(q + c.row8), a11 = lds64<32>(q + c.row8);
+        const uint32_t b = c.codes + ur * 128;
+        const uint2 b0 = lds64<0>(b), b1 = lds64<32>(b), b2 = lds64<64>(b), b3 = lds64<96>(b);
         int lo0[4], hi0[4], lo1[4], hi1[4];
         constexpr uint32_t kLow = 0x0F0F0F0Fu, kHigh = 0xF0F0F0F0u;
         mma_u8s8_k32(lo0, a00.x & kLow, a10.x & kLow, a00.y & kLow, a10.y & kLow, b0.x, b0.y);
@@ -152,10 +202,8 @@ struct Q4KMma {
         }
         const float d[2] = {half_bits_to_float(h0.x & 0xffff), half_bits_to_float(h1.x & 0xffff)};
         const float dmin[2] = {half_bits_to_float(h0.x >> 16), half_bits_to_float(h1.x >> 16)};
-        const float *const sums = static_cast<const float *>(c.sums);
-        const uint32_t first = 2 * c.tig * m.scale_stride + ur * 4;  // token 2 tig; token 2 tig + 1 is scale_stride further
-        const float4 ad[2] = {*reinterpret_cast<const float4 *>(c.scales + first), *reinterpret_cast<const float4 *>(c.scales + first + m.scale_stride)};
-        const float4 as[2] = {*reinterpret_cast<const float4 *>(sums + first), *reinterpret_cast<const float4 *>(sums + first + m.scale_stride)};
+        const float4 ad[2] = {lds128f(c.scales + ur * 16), lds128f(c.scales + c.token_step + ur * 16)};
+        const float4 as[2] = {lds128f(c.sums + ur * 16), lds128f(c.sums + c.token_step + ur * 16)};
         // accumulator [2 * row + token]: row g / g + 8, token 2 tig / 2 tig + 1 -- the MMA's C fragment order
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
@@ -219,50 +267,62 @@ struct Q6KMma {
     // the quantiser's sums of every 16 codes are used as they are
     static __device__ __forceinline__ void finish_sums(const MmaArgs &, uint8_t *, uint32_t, uint32_t, uint32_t) {}
 
-    static __device__ __forceinline__ void unit(const MmaArgs &m, const MmaContext &c, const uint8_t *stage, uint32_t local, uint32_t u, float (&acc)[4])
+    static __device__ __forceinline__ void place(const MmaArgs &m, MmaContext &c, uint32_t buffer)
     {
-        const uint32_t first = u - local;                       // first unit of the stage
-        const uint32_t sbs = min(32u, m.units - first) / 4;     // super-blocks the stage holds
+        c.row0 = c.g * m.row_stride;
+        c.row8 = 8 * m.row_stride;
+        c.codes = buffer + c.g * m.code_stride + 4 * c.tig;
+        c.scales = buffer + m.offset_scales + 2 * c.tig * m.scale_stride * 4;
+        c.sums = buffer + m.offset_sums + 2 * c.tig * m.scale_stride * 4;
+        c.token_step = m.scale_stride * 4;
+    }
+    // the tile's part of the d plane was copied from the 16-byte boundary below its first byte
+    static __device__ __forceinline__ void place_tile(const MmaArgs &m, MmaContext &c, uint64_t row0)
+    {
+        c.tail = m.offset_tail + (uint32_t)(reinterpret_cast<uintptr_t>(m.weights.p3 + row0 * (m.K / 128)) & 15) + c.g * (m.K / 128);
+    }
+
+    static __device__ __forceinline__ void unit(const MmaArgs &m, const MmaContext &c, uint32_t stage, uint32_t local, uint32_t ur, uint32_t u, float (&acc)[4])
+    {
+        const uint32_t sbs = min(32u, m.units - (u - local)) / 4;  // super-blocks the stage holds
         const uint32_t sb = local >> 2, h = (local >> 1) & 1, i = local & 1;
-        const uint8_t *const r0 = stage + c.g * m.row_stride, *const r1 = r0 + 8 * m.row_stride;
-        const uint32_t ql = sb * 128 + h * 64 + i * 16 + 4 * c.tig, qh = sbs * 128 + sb * 64 + h * 32 + i * 16 + 4 * c.tig;
-        const uint32_t a0 = *reinterpret_cast<const uint32_t *>(r0 + ql), b0 = *reinterpret_cast<const uint32_t *>(r0 + ql + 32);
-        const uint32_t h0 = *reinterpret_cast<const uint32_t *>(r0 + qh);
-        const uint32_t a1 = *reinterpret_cast<const uint32_t *>(r1 + ql), b1 = *reinterpret_cast<const uint32_t *>(r1 + ql + 32);
-        const uint32_t h1 = *reinterpret_cast<const uint32_t *>(r1 + qh);
+        const uint32_t row = stage + c.row0;
+        const uint32_t ql = row + sb * 128 + h * 64 + i * 16 + 4 * c.tig, qh = row + sbs * 128 + sb * 64 + h * 32 + i * 16 + 4 * c.tig;
+        const uint32_t a0 = lds32<0>(ql), b0 = lds32<32>(ql), h0 = lds32<0>(qh);
+        const uint32_t a1 = lds32<0>(ql + c.row8), b1 = lds32<32>(ql + c.row8), h1 = lds32<0>(qh + c.row8);
         uint32_t v0[4], v1[4];
         q6k_codes(a0, b0, h0, v0[0], v0[1], v0[2], v0[3]);
         q6k_codes(a1, b1, h1, v1[0], v1[1], v1[2], v1[3]);
-        // activation codes of group q: 16 codes at sb * 256 + h * 128 + i * 16 + 32 q of the row; this thread's four
-        const uint32_t ur = u - c.chunk_unit;  // the unit's place in the chunk
-        const uint8_t *const b = c.codes + c.g * m.code_stride + (ur >> 2) * 256 + h * 128 + i * 16 + 4 * c.tig;
+        // activation codes of group q: 16 codes at sb * 256 + h * 128 + i * 16 + 32 q of the chunk; this thread's four
+        const uint32_t b = c.codes + (ur >> 2) * 256 + h * 128 + i * 16;
+        const uint32_t codes[4] = {lds32<0>(b), lds32<32>(b), lds32<64>(b), lds32<96>(b)};
         int dots[4][4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            mma_u8s8_k16(dots[q], v0[q], v1[q], *reinterpret_cast<const uint32_t *>(b + 32 * q));
+            mma_u8s8_k16(dots[q], v0[q], v1[q], codes[q]);
         }
         // the eight int8 scales of the half, and the super-block scale
-        const uint32_t sc = sbs * 192 + sb * 16 + h * 8;
-        const uint2 s0 = *reinterpret_cast<const uint2 *>(r0 + sc), s1 = *reinterpret_cast<const uint2 *>(r1 + sc);
-        const uint8_t *const tail = stage + m.offset_tail + c.tail_shift;
-        const float d[2] = {half_bits_to_float(*reinterpret_cast<const unsigned short *>(tail + (c.g * (m.K / 256) + (u >> 2)) * 2)),
-                            half_bits_to_float(*reinterpret_cast<const unsigned short *>(tail + ((c.g + 8) * (m.K / 256) + (u >> 2)) * 2))};
-        const int16_t *const sums = static_cast<const int16_t *>(c.sums);
-        const uint32_t block = 2 * c.tig * m.scale_stride + (ur >> 1) * 4;  // token 2 tig; token 2 tig + 1 is scale_stride further
-        const float4 ad[2] = {*reinterpret_cast<const float4 *>(c.scales + block), *reinterpret_cast<const float4 *>(c.scales + block + m.scale_stride)};
-        const int16_t *const as[2] = {sums + 2 * block + i, sums + 2 * (block + m.scale_stride) + i};
+        const uint32_t sc = row + sbs * 192 + sb * 16 + h * 8;
+        const uint2 s0 = lds64<0>(sc), s1 = lds64<0>(sc + c.row8);
+        const uint32_t tail = stage + c.tail + (u >> 2) * 2;
+        const float d[2] = {half_bits_to_float(lds16(tail)), half_bits_to_float(lds16(tail + 8 * (m.K / 128)))};
+        const float4 ad[2] = {lds128f(c.scales + (ur >> 1) * 16), lds128f(c.scales + c.token_step + (ur >> 1) * 16)};
+        // the sums of the eight 16-code groups of the half, two per word: group q of this unit is half i of word q
+        const uint4 as[2] = {lds128(c.sums + (ur >> 1) * 16), lds128(c.sums + c.token_step + (ur >> 1) * 16)};
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const uint32_t word0 = q < 2 ? s0.x : s0.y, word1 = q < 2 ? s1.x : s1.y;
             const int scale[2] = {(int)(signed char)((word0 >> (8 * (2 * (q & 1) + i))) & 0xff), (int)(signed char)((word1 >> (8 * (2 * (q & 1) + i))) & 0xff)};
             const float adq[2] = {q == 0 ? ad[0].x : q == 1 ? ad[0].y : q == 2 ? ad[0].z : ad[0].w, q == 0 ? ad[1].x : q == 1 ? ad[1].y : q == 2 ? ad[1].z : ad[1].w};
-            const int asq[2] = {(int)as[0][2 * q], (int)as[1][2 * q]};
+            const uint32_t pair0 = q == 0 ? as[0].x : q == 1 ? as[0].y : q == 2 ? as[0].z : as[0].w;
+            const uint32_t pair1 = q == 0 ? as[1].x : q == 1 ? as[1].y : q == 2 ? as[1].z : as[1].w;
+            const int asq[2] = {(int)(short)(i ? pair0 >> 16 : pair0 & 0xffff), (int)(short)(i ? pair1 >> 16 : pair1 & 0xffff)};
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
-                const int row = p >> 1, token = p & 1;
+                const int row_index = p >> 1, token = p & 1;
                 // the expression of q6k_dot
                 const int dot = dots[q][p] - 32 * asq[token];
-                acc[p] = fmaf((d[row] * small_int_to_float(scale[row])) * adq[token], small_int_to_float(dot), acc[p]);
+                acc[p] = fmaf((d[row_index] * small_int_to_float(scale[row_index])) * adq[token], small_int_to_float(dot), acc[p]);
             }
         }
     }
@@ -305,19 +365,24 @@ __device__ __forceinline__ void fetch_chunk(const MmaArgs &m, const ActView &act
 }
 
 template <class Codec, bool GATHER>
-__global__ void __launch_bounds__(kMmaWarps * 32 + 32, 1)
+__global__ void __launch_bounds__((kMmaWarps + 1 + kMmaCombineWarps) * 32, 1)
 matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_stride, Epilogue epilogue, uint32_t *fault)
 {
     extern __shared__ __align__(128) uint8_t mma_memory[];
-    __shared__ __align__(8) uint64_t barriers[2 * kMaxStages];  // full[s] then empty[s]
+    __shared__ __align__(8) uint64_t barriers[2 * kMaxStages + 2 * kMmaSlots];  // full[s], empty[s]; sums_full[k], sums_empty[k]
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint64_t tiles = (m.rows + kMmaRows - 1) / kMmaRows;
     const uint32_t my_tiles = tiles > blockIdx.x ? (uint32_t)((tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
     const uint32_t full0 = smem_u32(&barriers[0]), empty0 = smem_u32(&barriers[kMaxStages]);
+    const uint32_t sums_full0 = smem_u32(&barriers[2 * kMaxStages]), sums_empty0 = smem_u32(&barriers[2 * kMaxStages + kMmaSlots]);
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < m.stages; ++s) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, kMmaWarps);
+        }
+        for (uint32_t k = 0; k < m.slots; ++k) {
+            mbar_init(sums_full0 + 8 * k, kMmaWarps);
+            mbar_init(sums_empty0 + 8 * k, kMmaCombineWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -351,13 +416,61 @@ matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_st
         return;
     }
 
-    // ---- consumers ---------------------------------------------------------------------------------------
     constexpr uint32_t kThreads = kMmaWarps * 32;
     const uint64_t token0 = (uint64_t)blockIdx.y * kMmaTokens;
     const uint32_t live = min(kMmaTokens, m.tokens - (uint32_t)token0);
-    float *const partial = reinterpret_cast<float *>(mma_memory + m.offset_partial);  // [2][kMmaWarps][128]
+    float *const partial = reinterpret_cast<float *>(mma_memory + m.offset_partial);  // [kMmaSlots][kMmaWarps][128]
     float *const running = reinterpret_cast<float *>(mma_memory + m.offset_running);  // [my_tiles][128] when the team has several warps
 
+    if (warp > kMmaWarps) {
+        // ---- combining warps: thread p owns (row p / 8, token p % 8) of every tile. They take the multiplying warps'
+        // partial sums through a ring of kMmaSlots sets (mbarriers, no CTA-wide barrier), so the multiplying warps
+        // never wait for the additions and drift apart instead of running every stage in lockstep.
+        const uint32_t pair = threadIdx.x - (kMmaWarps + 1) * 32;
+        const uint32_t out_row = pair >> 3, out_token = pair & 7;
+        pdl_wait();
+        uint32_t slot = 0, slot_phase = 0;
+        for (uint32_t w = 0; w < m.chunks; ++w) {
+            for (uint32_t it = 0; it < my_tiles; ++it) {
+                const uint64_t row0 = ((uint64_t)blockIdx.x + (uint64_t)it * gridDim.x) * kMmaRows;
+                if (!mbar_wait(sums_full0 + 8 * slot, slot_phase) && fault && lane == 0) {
+                    atomicAdd(fault, 1u);
+                }
+                const float *const p = partial + slot * kMmaWarps * 128 + pair;
+                float level[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    level[i] = p[i * 128] + p[(i + 8) * 128];  // offset 8
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(sums_empty0 + 8 * slot);  // the values are in registers
+                }
+                if (++slot == m.slots) {
+                    slot = 0;
+                    slot_phase ^= 1;
+                }
+                const float c0 = level[0] + level[4], c1 = level[1] + level[5], c2 = level[2] + level[6], c3 = level[3] + level[7];  // offset 4
+                const float e = (c0 + c2) + (c1 + c3);  // offsets 2 and 1
+                // the team's warps in index order
+                const float total = w == 0 ? e : running[it * 128 + pair] + e;
+                if (w + 1 < m.chunks) {
+                    running[it * 128 + pair] = total;
+                } else if (row0 + out_row < m.rows && out_token < live) {
+                    store_result<GATHER>(epilogue, y, token0 + out_token, out_stride, row0 + out_row, total);
+                }
+            }
+        }
+        if (GATHER) {
+            asm volatile("bar.sync 2, %0;" ::"n"(kMmaCombineWarps * 32) : "memory");
+            if (pair == 0) {
+                signal_completion(epilogue);
+            }
+        }
+        return;
+    }
+
+    // ---- multiplying warps ------------------------------------------------------------------------------
     pdl_wait();
     fetch_chunk(m, act, token0, live, 0, mma_memory, threadIdx.x, kThreads);
     copies_async_wait();
@@ -365,24 +478,21 @@ matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_st
     Codec::finish_sums(m, mma_memory, min(kMmaChunkValues, m.K) / 32, threadIdx.x, kThreads);
     consumer_barrier<kThreads>();
 
-    MmaContext c;
+    MmaContext c{};
     c.g = lane >> 2;
     c.tig = lane & 3;
-    const uint32_t out_row = threadIdx.x >> 3, out_token = threadIdx.x & 7;  // the pair a combining thread owns
-    uint32_t s = 0, phase = 0, buffer = 0;
+    uint32_t s = 0, phase = 0, slot = 0, slot_round = 0;
     for (uint32_t w = 0; w < m.chunks; ++w) {
         uint8_t *const acts = mma_memory + (w & 1) * m.buffer_bytes;
         if (w + 1 < m.chunks) {
             // the other buffer was last read in chunk w - 1, which every warp has left (the barrier that ended it)
             fetch_chunk(m, act, token0, live, w + 1, mma_memory + ((w + 1) & 1) * m.buffer_bytes, threadIdx.x, kThreads);
         }
-        c.codes = acts;
-        c.scales = reinterpret_cast<const float *>(acts + m.offset_scales);
-        c.sums = acts + m.offset_sums;
-        c.chunk_unit = w * m.upl * 32;
+        Codec::place(m, c, smem_u32(acts));
+        const uint32_t chunk_unit = w * m.upl * 32;
         for (uint32_t it = 0; it < my_tiles; ++it) {
             const uint64_t row0 = ((uint64_t)blockIdx.x + (uint64_t)it * gridDim.x) * kMmaRows;
-            c.tail_shift = (uint32_t)(reinterpret_cast<uintptr_t>(m.weights.p3 + row0 * (m.K / 128)) & 15);
+            Codec::place_tile(m, c, row0);
             float acc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};  // lanes warp and warp + 16 of team warp w
             for (uint32_t j = 0; j < m.upl; ++j) {
                 const uint32_t first = (w * m.upl + j) * 32;
@@ -392,13 +502,15 @@ matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_st
                 if (!mbar_wait(full0 + 8 * s, phase) && fault && lane == 0) {
                     atomicAdd(fault, 1u);
                 }
-                const uint8_t *const stage = mma_memory + m.offset_stages + s * m.stage_bytes;
-#pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                    const uint32_t local = warp + 16 * k;
-                    if (first + local < m.units) {
-                        Codec::unit(m, c, stage, local, first + local, acc[k]);
-                    }
+                const uint32_t stage = smem_u32(mma_memory) + m.offset_stages + s * m.stage_bytes;
+                const uint32_t ur = first - chunk_unit + warp;  // place in the chunk of the unit of lane `warp`
+                if (first + warp + 16 < m.units) {
+                    // both lanes have a unit (the usual case): one straight run of code, so that the two independent
+                    // chains of loads, MMAs and FP32 operations can be interleaved
+                    Codec::unit(m, c, stage, warp, ur, first + warp, acc[0]);
+                    Codec::unit(m, c, stage, warp + 16, ur + 16, first + warp + 16, acc[1]);
+                } else if (first + warp < m.units) {
+                    Codec::unit(m, c, stage, warp, ur, first + warp, acc[0]);
                 }
                 // Give the stage back: the shared-memory reads above have retired (their values were used), the fence
                 // orders them before the producer's next bulk copy into the stage.
@@ -412,41 +524,27 @@ matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_st
                     phase ^= 1;
                 }
             }
-            // first level of the butterfly: lane i + lane i + 16
-            float *const mine = partial + (buffer * kMmaWarps + warp) * 128;
+            // first level of the butterfly: lane i + lane i + 16; the set goes to the combining warps
+            if (slot_round > 0 && !mbar_wait(sums_empty0 + 8 * slot, (slot_round - 1) & 1) && fault && lane == 0) {
+                atomicAdd(fault, 1u);
+            }
+            float *const mine = partial + (slot * kMmaWarps + warp) * 128;
             *reinterpret_cast<float2 *>(mine + c.g * 8 + 2 * c.tig) = make_float2(acc[0][0] + acc[1][0], acc[0][1] + acc[1][1]);
             *reinterpret_cast<float2 *>(mine + (c.g + 8) * 8 + 2 * c.tig) = make_float2(acc[0][2] + acc[1][2], acc[0][3] + acc[1][3]);
-            consumer_barrier<kThreads>();
-            if (threadIdx.x < 128) {
-                const float *const p = partial + buffer * kMmaWarps * 128 + threadIdx.x;
-                float level[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    level[i] = p[i * 128] + p[(i + 8) * 128];  // offset 8
-                }
-                const float c0 = level[0] + level[4], c1 = level[1] + level[5], c2 = level[2] + level[6], c3 = level[3] + level[7];  // offset 4
-                const float e = (c0 + c2) + (c1 + c3);  // offsets 2 and 1
-                // the team's warps in index order
-                const float total = w == 0 ? e : running[it * 128 + threadIdx.x] + e;
-                if (w + 1 < m.chunks) {
-                    running[it * 128 + threadIdx.x] = total;
-                } else if (row0 + out_row < m.rows && out_token < live) {
-                    store_result<GATHER>(epilogue, y, token0 + out_token, out_stride, row0 + out_row, total);
-                }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(sums_full0 + 8 * slot);  // release: the warp's stores above are visible to who sees the phase complete
             }
-            buffer ^= 1;
+            if (++slot == m.slots) {
+                slot = 0;
+                ++slot_round;
+            }
         }
         if (w + 1 < m.chunks) {
             copies_async_wait();
             consumer_barrier<kThreads>();
             Codec::finish_sums(m, mma_memory + ((w + 1) & 1) * m.buffer_bytes, min(kMmaChunkValues, m.K - (w + 1) * kMmaChunkValues) / 32, threadIdx.x, kThreads);
             consumer_barrier<kThreads>();
-        }
-    }
-    if (GATHER) {
-        consumer_barrier<kThreads>();
-        if (threadIdx.x == 0) {
-            signal_completion(epilogue);
         }
     }
 }
@@ -481,13 +579,20 @@ cudaError_t launch_mma(const MatvecArgs &a, const WeightView &view, uint32_t upl
         ctas = cap;
     }
     m.offset_partial = (m.chunks > 1 ? 2 : 1) * m.buffer_bytes;
-    m.offset_running = m.offset_partial + 2 * kMmaWarps * 128 * 4;  // the partial sums, double-buffered
-    m.offset_stages = m.offset_running + (m.chunks > 1 ? (uint32_t)tiles_per_cta * 128 * 4 : 0);
-    if (m.offset_stages + 2ull * m.stage_bytes > kMmaShared) {
+    for (m.slots = kMmaSlots; m.slots >= 2; m.slots /= 2) {
+        m.offset_running = m.offset_partial + m.slots * kMmaWarps * 128 * 4;  // the ring of partial sums
+        m.offset_stages = m.offset_running + (m.chunks > 1 ? (uint32_t)tiles_per_cta * 128 * 4 : 0);
+        m.stages = m.offset_stages < kMmaShared ? (kMmaShared - m.offset_stages) / m.stage_bytes : 0;
+        if (m.stages >= 3 || m.slots == 2) {
+            break;
+        }
+    }
+    if (m.stages < 2) {
         return cudaErrorNotSupported;
     }
-    const uint64_t stages = (kMmaShared - m.offset_stages) / m.stage_bytes;
-    m.stages = (uint32_t)(stages > kMaxStages ? kMaxStages : stages);
+    if (m.stages > (uint32_t)kMaxStages) {
+        m.stages = kMaxStages;
+    }
     auto kernel = matvec_mma_kernel<Codec, GATHER>;
     static PerDevice configured;
     if (configured.first_use(a.matrix->device)) {
@@ -498,7 +603,7 @@ cudaError_t launch_mma(const MatvecArgs &a, const WeightView &view, uint32_t upl
         }
     }
     const dim3 grid((unsigned)ctas, (unsigned)((a.tokens + kMmaTokens - 1) / kMmaTokens));
-    return launch_kernel(kernel, grid, dim3(kMmaWarps * 32 + 32), (size_t)kMmaShared, stream, m, a.act, a.y, a.out_stride, a.fused, fault_word_device());
+    return launch_kernel(kernel, grid, dim3((kMmaWarps + 1 + kMmaCombineWarps) * 32), (size_t)kMmaShared, stream, m, a.act, a.y, a.out_stride, a.fused, fault_word_device());
 }
 
 template <class F, bool GATHER>
