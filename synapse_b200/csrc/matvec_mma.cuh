@@ -26,7 +26,7 @@ constexpr uint32_t kMmaSlots = 4;              // sets of partial sums in flight
 constexpr uint32_t kMmaRows = 16;              // rows of a tile: M of the MMA
 constexpr uint32_t kMmaTokens = 8;             // tokens of a group: N of the MMA
 constexpr uint32_t kMmaChunkValues = 4096;     // the values one warp of a one-token team covers (32 lanes x UPL units)
-constexpr uint32_t kMmaShared = 220u * 1024u;  // dynamic shared memory of the kernel
+constexpr uint32_t kMmaShared = 226u * 1024u;  // dynamic shared memory of the kernel (the CTA has the SM to itself)
 
 // Shared memory: [activation buffer 0][activation buffer 1 (rows longer than a chunk)][ring of partial sums][running sums][stages].
 // An activation buffer holds, for the eight tokens of the group, the part of the quantised activations that goes with
@@ -579,19 +579,22 @@ cudaError_t launch_mma(const MatvecArgs &a, const WeightView &view, uint32_t upl
         ctas = cap;
     }
     m.offset_partial = (m.chunks > 1 ? 2 : 1) * m.buffer_bytes;
-    for (m.slots = kMmaSlots; m.slots >= 2; m.slots /= 2) {
-        m.offset_running = m.offset_partial + m.slots * kMmaWarps * 128 * 4;  // the ring of partial sums
+    // stages matter more than sets of partial sums: four sets only where they do not cost a stage
+    auto lay = [&](uint32_t slots) {
+        m.slots = slots;
+        m.offset_running = m.offset_partial + slots * kMmaWarps * 128 * 4;  // behind the ring of partial sums
         m.offset_stages = m.offset_running + (m.chunks > 1 ? (uint32_t)tiles_per_cta * 128 * 4 : 0);
-        m.stages = m.offset_stages < kMmaShared ? (kMmaShared - m.offset_stages) / m.stage_bytes : 0;
-        if (m.stages >= 3 || m.slots == 2) {
-            break;
-        }
+        const uint32_t stages = m.offset_stages < kMmaShared ? (kMmaShared - m.offset_stages) / m.stage_bytes : 0;
+        m.stages = stages > (uint32_t)kMaxStages ? (uint32_t)kMaxStages : stages;
+    };
+    lay(2);
+    const uint32_t with_two = m.stages;
+    lay(kMmaSlots);
+    if (m.stages < with_two) {
+        lay(2);
     }
     if (m.stages < 2) {
         return cudaErrorNotSupported;
-    }
-    if (m.stages > (uint32_t)kMaxStages) {
-        m.stages = kMaxStages;
     }
     auto kernel = matvec_mma_kernel<Codec, GATHER>;
     static PerDevice configured;
