@@ -264,7 +264,7 @@ def main():
     from synapse_b200 import decoder as dec
 
     shape = dict(dec.QWEN25_7B, layers=args.layers)
-    image = dec.ModelImage(**shape, context=64, matrix_types=dec.Q4KM_TYPES, embedding_type=synth.Q4_K, output_type=synth.Q4_K, seed=100,
+    image = dec.ModelImage(**shape, context=512, matrix_types=dec.Q4KM_TYPES, embedding_type=synth.Q4_K, output_type=synth.Q4_K, seed=100,
                            bias=True)
     leaf_fields = {"attn_q": "query", "attn_k": "key", "attn_v": "value", "attn_o": "attention_output", "ffn_gate": "gate", "ffn_up": "up",
                    "ffn_down": "down"}

@@ -211,8 +211,8 @@ def config4_sweep(sb, lib, torch, dist, device, stream, world, rank, peak, use_p
 
 def batched_decode(dec, image):
     """The decoder on several tokens per step: 2 / 4 / 8 sessions decoding together (one token each per step, greedy pick
-    on the device) and a 64-token prompt run of one session (``syn_b200_decoder_forward_argmax``, host tokens in, token
-    ids out). Same model image as the single-session `e2e`; only the slot and step sizes of the descriptor differ."""
+    on the device) and prompt runs of 64 and 512 tokens of one session in chunks of 64 (``syn_b200_decoder_forward_argmax``,
+    host tokens in, token ids out). Same model image as the single-session `e2e`; only the slot and step sizes of the descriptor differ."""
     import copy
 
     wide = copy.copy(image)
@@ -229,14 +229,22 @@ def batched_decode(dec, image):
                 tokens = model.forward_argmax([(s, tokens[s], position, s) for s in range(sessions)])
             seconds = time.perf_counter() - start
             out[f"{sessions} sessions"] = {"ms_per_step": seconds / steps * 1e3, "tokens_per_s": sessions * steps / seconds}
-        prompt = [(0, 100 + p, p, 0 if p == 63 else -1) for p in range(64)]
-        model.forward_argmax(prompt)
-        runs = 3
-        start = time.perf_counter()
-        for _ in range(runs):
-            model.forward_argmax(prompt)
-        seconds = time.perf_counter() - start
-        out["64-token prompt run"] = {"ms_per_run": seconds / runs * 1e3, "tokens_per_s": 64 * runs / seconds}
+
+        def prompt(length):
+            # chunks of 64 tokens (the reference's prefill chunk); only the last token asks for logits
+            for first in range(0, length, 64):
+                chunk = [(0, 100 + p, p, 0 if p == length - 1 else -1) for p in range(first, min(first + 64, length))]
+                last = model.forward_argmax(chunk)
+            return last
+
+        for length in (64, min(512, image.shape["context"])):
+            prompt(length)
+            runs = 3 if length == 64 else 2
+            start = time.perf_counter()
+            for _ in range(runs):
+                prompt(length)
+            seconds = time.perf_counter() - start
+            out[f"{length}-token prompt run"] = {"ms_per_run": seconds / runs * 1e3, "tokens_per_s": length * runs / seconds}
     return out
 
 
