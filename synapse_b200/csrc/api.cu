@@ -9,6 +9,8 @@
 #include <new>
 #include <string>
 
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace syn {
@@ -76,6 +78,50 @@ uint32_t fault_word_read(bool reset)
         *word = 0;
     }
     return value;
+}
+
+// Tensor maps for tiled bulk copies (cp.async.bulk.tensor) of 16-row boxes out of the ql, qh and scale planes of a planar
+// Q6_K matrix. A plane [rows][row_bytes] is described as bytes [segment][row][128] (strides 128 and row_bytes), so that a
+// box of S segments x 16 rows x 128 bytes lands in shared memory segment by segment with the 128-byte swizzle keyed by
+// the row: the eight rows a warp reads at one column then sit in different banks. The encoder is a driver entry point
+// taken through the runtime (the library does not link libcuda). A last segment may reach past the row's end into the
+// next row or, for the last row, into the plane behind it, which is inside the allocation; nothing reads those bytes.
+const unsigned char (*q6k_tensor_maps(const syn_b200_matrix *matrix))[128]
+{
+    static std::mutex guard;
+    std::lock_guard<std::mutex> lock(guard);
+    syn_b200_matrix *m = const_cast<syn_b200_matrix *>(matrix);
+    if (m->tensor_maps_state == 0) {
+        m->tensor_maps_state = -1;
+        using Encode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                    const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+        void *entry = nullptr;
+        cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+        if (m->type == kQ6_K && m->layout == Layout::Planar && m->rows > 0 &&
+            cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &found) == cudaSuccess && entry &&
+            found == cudaDriverEntryPointSuccess) {
+            const uint64_t row_bytes[3] = {m->columns / 2, m->columns / 4, m->columns / 16};
+            const uint64_t offsets[3] = {m->planes.p0, m->planes.p1, m->planes.p2};
+            const uint32_t segments[3] = {8, 4, 1};  // of a box: eight super-blocks of a row
+            bool ok = true;
+            for (int k = 0; k < 3 && ok; ++k) {
+                const cuuint64_t dims[3] = {128, m->rows, (row_bytes[k] + 127) / 128};
+                const cuuint64_t strides[2] = {row_bytes[k], 128};
+                const cuuint32_t box[3] = {128, 16, segments[k]};
+                const cuuint32_t steps[3] = {1, 1, 1};
+                ok = row_bytes[k] % 16 == 0 &&
+                     reinterpret_cast<Encode>(entry)(reinterpret_cast<CUtensorMap *>(m->tensor_maps[k]), CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, m->data + offsets[k],
+                                                     dims, strides, box, steps, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+            }
+            if (ok) {
+                m->tensor_maps_state = 1;
+            }
+        } else {
+            cudaGetLastError();
+        }
+    }
+    return m->tensor_maps_state == 1 ? m->tensor_maps : nullptr;
 }
 
 int sm_count(int device)

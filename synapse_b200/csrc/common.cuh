@@ -52,6 +52,10 @@ struct syn_b200_matrix {
     // Staging for the host-pointer entry points, grown on demand, owned by the handle.
     void *stage = nullptr;
     uint64_t stage_bytes = 0;
+    // Tensor maps of the three big planes of a planar Q6_K matrix (ql, qh, scales), for tiled bulk copies of 16-row
+    // boxes; built on first use (syn::q6k_tensor_maps). State: 0 not built yet, 1 ready, -1 cannot be built.
+    alignas(64) unsigned char tensor_maps[3][128] = {};
+    int tensor_maps_state = 0;
 };
 
 namespace syn {
@@ -114,6 +118,8 @@ int32_t guarded(Body body)
 }
 void count_launch();
 int sm_count(int device);
+// The three tensor maps of a planar Q6_K matrix (3 x 128 bytes, 64-byte aligned), or null when they cannot be had.
+const unsigned char (*q6k_tensor_maps(const syn_b200_matrix *matrix))[128];
 
 // Launches `kernel` on `stream` with programmatic stream serialization: its prologue and first weight copies overlap
 // the tail of the kernel before it. Every kernel launched this way executes griddepcontrol.wait before it reads

@@ -37,6 +37,7 @@ constexpr uint32_t kMmaShared = 226u * 1024u;  // dynamic shared memory of the k
 struct MmaArgs {
     WeightView weights;      // plane bases at the first row of the call
     uint64_t rows;
+    uint64_t row_first;      // the call's first row inside the matrix (tensor maps describe whole planes)
     uint32_t row_bytes;      // Q4_K: bytes of a row
     uint32_t K;
     uint32_t units;          // values / Codec::kUnitValues
@@ -53,6 +54,20 @@ struct MmaArgs {
     uint32_t stage_bytes, stages;
     uint32_t slots;          // sets of partial sums in the ring (kMmaSlots, or two when that buys a third stage)
 };
+
+// The tensor maps of a planar Q6_K matrix, passed to the kernel by value (the tiled bulk copy wants them in parameter,
+// constant or global memory).
+struct alignas(64) MmaMaps {
+    unsigned char bytes[3][128];
+};
+
+// Tiled bulk copy of one box of a 3-D tensor map into shared memory; completion on an mbarrier, like bulk_copy.
+__device__ __forceinline__ void tensor_copy(uint32_t dst, const void *map, int x, int y, int z, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+                 : "memory");
+}
 
 __device__ __forceinline__ void mma_u8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
 {
@@ -132,8 +147,8 @@ struct Q4KMma {
         m.code_stride = (m.K < kMmaChunkValues ? m.K : kMmaChunkValues) + 32;
     }
 
-    static __device__ __forceinline__ void produce(const MmaArgs &m, uint32_t stage, uint64_t row0, uint32_t n, uint32_t w, uint32_t j, uint32_t lane,
-                                                   uint32_t bar, uint64_t policy)
+    static __device__ __forceinline__ void produce(const MmaArgs &m, const MmaMaps &, uint32_t stage, uint64_t row0, uint32_t n, uint32_t w, uint32_t j,
+                                                   uint32_t lane, uint32_t bar, uint64_t policy)
     {
         const uint32_t first = (w * m.upl + j) * 32;                // first unit of the stage
         const uint32_t piece = min(32u, m.units - first) * 72u;  // a multiple of 144: rows hold whole super-blocks
@@ -226,31 +241,56 @@ struct Q4KMma {
 // ------------------------------------------------------------------------------------------------------
 // Q6_K (planes: ql | qh | int8 scales | fp16 super-block scales). Unit = 64 values: bytes l = 16 i .. 16 i + 15 of half h
 // of super-block u / 4, four groups of 16 values with their own scales. A stage holds 32 units = 8 super-blocks of every
-// row (ql 1024, qh 512, scales 128 bytes, rows row_stride apart) and, behind the rows, the tile's part of the d plane.
-// One m16n8k16 per group of 16 values.
+// row and, behind them, the tile's part of the d plane. One m16n8k16 per group of 16 values.
+// TILED: the three big planes arrive as one tiled bulk copy each (a box of 16 rows), laid out [segment of 128 bytes][row]
+// with the 128-byte swizzle, whose key is the row: 16-byte piece p of a row's segment sits at piece p ^ (row % 8), so the
+// eight rows a warp reads at one column are in different banks. A stage is ql 8 x 16 x 128 | qh 4 x 16 x 128 | scales
+// 1 x 16 x 128 | d. Otherwise (no tensor maps to be had): one plain bulk copy per row and plane (49 per stage, which is
+// what the multiplying warps then wait for a third of the time), rows row_stride apart (ql 1024, qh 512, scales 128 bytes).
 // ------------------------------------------------------------------------------------------------------
-struct Q6KMma {
+template <bool TILED>
+struct Q6KMmaT {
     using Format = Q6KPlanarXq8;
     static constexpr uint32_t kUnitValues = 64;
+    static constexpr uint32_t kQh = 8 * 16 * 128, kScales = kQh + 4 * 16 * 128, kBoxBytes = kScales + 16 * 128;  // inside a tiled stage
     static void layout(MmaArgs &m)
     {
         const uint32_t sbs = m.units < 32 ? m.units / 4 : 8;  // super-blocks of a stage
-        // 4-byte loads of rows g = 0..7 and tig = 0..3 cover the 32 banks when the stride is 16 more than a multiple of 128
-        m.row_stride = (uint32_t)align_up(sbs * (128 + 64 + 16), 128) + 16;
-        m.offset_tail = kMmaRows * m.row_stride;
+        if (TILED) {
+            m.row_stride = 128;
+            m.offset_tail = kBoxBytes;
+        } else {
+            // 4-byte loads of rows g = 0..7 and tig = 0..3 cover the 32 banks when the stride is 16 more than a multiple of 128
+            m.row_stride = (uint32_t)align_up(sbs * (128 + 64 + 16), 128) + 16;
+            m.offset_tail = kMmaRows * m.row_stride;
+        }
         // the 16 rows' super-block scales are contiguous in their plane: one copy from the 16-byte boundary below them
-        m.stage_bytes = (uint32_t)align_up(m.offset_tail + kMmaRows * (m.K / 128) + 32, 128);
+        // (stages are multiples of 1024 bytes: the swizzle's period)
+        m.stage_bytes = (uint32_t)align_up(m.offset_tail + kMmaRows * (m.K / 128) + 32, 1024);
         m.code_stride = (m.K < kMmaChunkValues ? m.K : kMmaChunkValues) + 16;
     }
 
-    static __device__ __forceinline__ void produce(const MmaArgs &m, uint32_t stage, uint64_t row0, uint32_t n, uint32_t w, uint32_t j, uint32_t lane,
-                                                   uint32_t bar, uint64_t policy)
+    static __device__ __forceinline__ void produce(const MmaArgs &m, const MmaMaps &maps, uint32_t stage, uint64_t row0, uint32_t n, uint32_t w, uint32_t j,
+                                                   uint32_t lane, uint32_t bar, uint64_t policy)
     {
         const uint32_t first = (w * m.upl + j) * 32;            // first unit of the stage
         const uint32_t sb0 = first / 4, sbs = min(32u, m.units - first) / 4;
         const uint8_t *const tail = m.weights.p3 + row0 * (m.K / 128);
         const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(tail) & 15);
         const uint32_t tail_bytes = (shift + n * (m.K / 128) + 15) & ~15u;
+        if (TILED) {
+            // Boxes are always whole: rows past the matrix read as zero, segments past the row's end are never looked at.
+            // Coordinates: byte 0 of the segment (a multiple of 16, as a tiled copy needs), the row, the segment.
+            if (lane == 0) {
+                const int row = (int)(m.row_first + row0);
+                mbar_expect_tx(bar, kBoxBytes + tail_bytes);
+                tensor_copy(stage, maps.bytes[0], 0, row, (int)sb0, bar);
+                tensor_copy(stage + kQh, maps.bytes[1], 0, row, (int)(sb0 / 2), bar);
+                tensor_copy(stage + kScales, maps.bytes[2], 0, row, (int)(sb0 / 8), bar);
+                bulk_copy(stage + m.offset_tail, tail - shift, tail_bytes, bar, policy);
+            }
+            return;
+        }
         if (lane == 0) {
             mbar_expect_tx(bar, n * sbs * (128 + 64 + 16) + tail_bytes);
             bulk_copy(stage + m.offset_tail, tail - shift, tail_bytes, bar, policy);
@@ -287,9 +327,19 @@ struct Q6KMma {
         const uint32_t sbs = min(32u, m.units - (u - local)) / 4;  // super-blocks the stage holds
         const uint32_t sb = local >> 2, h = (local >> 1) & 1, i = local & 1;
         const uint32_t row = stage + c.row0;
-        const uint32_t ql = row + sb * 128 + h * 64 + i * 16 + 4 * c.tig, qh = row + sbs * 128 + sb * 64 + h * 32 + i * 16 + 4 * c.tig;
-        const uint32_t a0 = lds32<0>(ql), b0 = lds32<32>(ql), h0 = lds32<0>(qh);
-        const uint32_t a1 = lds32<0>(ql + c.row8), b1 = lds32<32>(ql + c.row8), h1 = lds32<0>(qh + c.row8);
+        uint32_t a0, b0, h0, a1, b1, h1;
+        if (TILED) {
+            // segment of ql = the super-block; of qh = a pair of them; 16-byte piece p of the row's segment is at p ^ g
+            // (rows g and g + 8 have the same key)
+            const uint32_t ql = row + sb * 2048 + 4 * c.tig, qh = row + kQh + (sb >> 1) * 2048 + 4 * c.tig;
+            const uint32_t pa = ((h * 4 + i) ^ c.g) << 4, pb = ((h * 4 + i + 2) ^ c.g) << 4, ph = (((sb & 1) * 4 + h * 2 + i) ^ c.g) << 4;
+            a0 = lds32<0>(ql + pa), b0 = lds32<0>(ql + pb), h0 = lds32<0>(qh + ph);
+            a1 = lds32<1024>(ql + pa), b1 = lds32<1024>(ql + pb), h1 = lds32<1024>(qh + ph);
+        } else {
+            const uint32_t ql = row + sb * 128 + h * 64 + i * 16 + 4 * c.tig, qh = row + sbs * 128 + sb * 64 + h * 32 + i * 16 + 4 * c.tig;
+            a0 = lds32<0>(ql), b0 = lds32<32>(ql), h0 = lds32<0>(qh);
+            a1 = lds32<0>(ql + c.row8), b1 = lds32<32>(ql + c.row8), h1 = lds32<0>(qh + c.row8);
+        }
         uint32_t v0[4], v1[4];
         q6k_codes(a0, b0, h0, v0[0], v0[1], v0[2], v0[3]);
         q6k_codes(a1, b1, h1, v1[0], v1[1], v1[2], v1[3]);
@@ -302,7 +352,7 @@ struct Q6KMma {
             mma_u8s8_k16(dots[q], v0[q], v1[q], codes[q]);
         }
         // the eight int8 scales of the half, and the super-block scale
-        const uint32_t sc = row + sbs * 192 + sb * 16 + h * 8;
+        const uint32_t sc = TILED ? row + kScales + ((sb ^ c.g) << 4) + h * 8 : row + sbs * 192 + sb * 16 + h * 8;
         const uint2 s0 = lds64<0>(sc), s1 = lds64<0>(sc + c.row8);
         const uint32_t tail = stage + c.tail + (u >> 2) * 2;
         const float d[2] = {half_bits_to_float(lds16(tail)), half_bits_to_float(lds16(tail + 8 * (m.K / 128)))};
@@ -327,6 +377,8 @@ struct Q6KMma {
         }
     }
 };
+using Q6KMma = Q6KMmaT<false>;
+using Q6KTiledMma = Q6KMmaT<true>;
 
 __device__ __forceinline__ void copy16_async(void *shared, const void *global)
 {
@@ -366,7 +418,8 @@ __device__ __forceinline__ void fetch_chunk(const MmaArgs &m, const ActView &act
 
 template <class Codec, bool GATHER>
 __global__ void __launch_bounds__((kMmaWarps + 1 + kMmaCombineWarps) * 32, 1)
-matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_stride, Epilogue epilogue, uint32_t *fault)
+matvec_mma_kernel(MmaArgs m, const __grid_constant__ MmaMaps maps, ActView act, float *__restrict__ y, uint64_t out_stride, Epilogue epilogue,
+                  uint32_t *fault)
 {
     extern __shared__ __align__(128) uint8_t mma_memory[];
     __shared__ __align__(8) uint64_t barriers[2 * kMaxStages + 2 * kMmaSlots];  // full[s], empty[s]; sums_full[k], sums_empty[k]
@@ -392,7 +445,7 @@ matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_st
     if (warp == kMmaWarps) {
         // ---- producer: one stage per (team warp w, tile, step j), one bulk copy per row and plane ----
         const uint64_t policy = l2_evict_first_policy();
-        const uint32_t stage0 = smem_u32(mma_memory) + m.offset_stages;
+        const uint32_t stage0 = (smem_u32(mma_memory) + m.offset_stages + 1023) & ~1023u;  // the swizzle's period
         uint32_t s = 0, round = 0;
         for (uint32_t w = 0; w < m.chunks; ++w) {
             for (uint32_t it = 0; it < my_tiles; ++it) {
@@ -405,7 +458,7 @@ matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_st
                     if (round > 0 && !mbar_wait(empty0 + 8 * s, (round - 1) & 1) && fault && lane == 0) {
                         atomicAdd(fault, 1u);
                     }
-                    Codec::produce(m, stage0 + s * m.stage_bytes, row0, n, w, j, lane, full0 + 8 * s, policy);
+                    Codec::produce(m, maps, stage0 + s * m.stage_bytes, row0, n, w, j, lane, full0 + 8 * s, policy);
                     if (++s == m.stages) {
                         s = 0;
                         ++round;
@@ -502,7 +555,7 @@ matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_st
                 if (!mbar_wait(full0 + 8 * s, phase) && fault && lane == 0) {
                     atomicAdd(fault, 1u);
                 }
-                const uint32_t stage = smem_u32(mma_memory) + m.offset_stages + s * m.stage_bytes;
+                const uint32_t stage = ((smem_u32(mma_memory) + m.offset_stages + 1023) & ~1023u) + s * m.stage_bytes;
                 const uint32_t ur = first - chunk_unit + warp;  // place in the chunk of the unit of lane `warp`
                 if (first + warp + 16 < m.units) {
                     // both lanes have a unit (the usual case): one straight run of code, so that the two independent
@@ -552,11 +605,12 @@ matvec_mma_kernel(MmaArgs m, ActView act, float *__restrict__ y, uint64_t out_st
 // Lays the shared memory out for `a` and launches; cudaErrorNotSupported when two stages and the running sums of the
 // CTA's tiles do not fit beside the activation buffers, so that the caller falls back to the dp4a kernels.
 template <class Codec, bool GATHER>
-cudaError_t launch_mma(const MatvecArgs &a, const WeightView &view, uint32_t upl, cudaStream_t stream)
+cudaError_t launch_mma(const MatvecArgs &a, const WeightView &view, uint32_t upl, const unsigned char (*tensor_maps)[128], cudaStream_t stream)
 {
     MmaArgs m{};
     m.weights = view;
     m.rows = a.row_count;
+    m.row_first = a.row_start;
     m.row_bytes = (uint32_t)a.matrix->row_bytes;
     m.K = (uint32_t)a.matrix->columns;
     m.units = m.K / Codec::kUnitValues;  // (F::units is device code)
@@ -584,7 +638,8 @@ cudaError_t launch_mma(const MatvecArgs &a, const WeightView &view, uint32_t upl
         m.slots = slots;
         m.offset_running = m.offset_partial + slots * kMmaWarps * 128 * 4;  // behind the ring of partial sums
         m.offset_stages = m.offset_running + (m.chunks > 1 ? (uint32_t)tiles_per_cta * 128 * 4 : 0);
-        const uint32_t stages = m.offset_stages < kMmaShared ? (kMmaShared - m.offset_stages) / m.stage_bytes : 0;
+        // (up to 1023 bytes go into starting the stages on a multiple of 1024)
+        const uint32_t stages = m.offset_stages + 1024 < kMmaShared ? (kMmaShared - 1024 - m.offset_stages) / m.stage_bytes : 0;
         m.stages = stages > (uint32_t)kMaxStages ? (uint32_t)kMaxStages : stages;
     };
     lay(2);
@@ -606,16 +661,22 @@ cudaError_t launch_mma(const MatvecArgs &a, const WeightView &view, uint32_t upl
         }
     }
     const dim3 grid((unsigned)ctas, (unsigned)((a.tokens + kMmaTokens - 1) / kMmaTokens));
-    return launch_kernel(kernel, grid, dim3((kMmaWarps + 1 + kMmaCombineWarps) * 32), (size_t)kMmaShared, stream, m, a.act, a.y, a.out_stride, a.fused, fault_word_device());
+    MmaMaps maps{};
+    if (tensor_maps) {
+        memcpy(maps.bytes, tensor_maps, sizeof(maps.bytes));
+    }
+    return launch_kernel(kernel, grid, dim3((kMmaWarps + 1 + kMmaCombineWarps) * 32), (size_t)kMmaShared, stream, m, maps, a.act, a.y, a.out_stride, a.fused,
+                         fault_word_device());
 }
 
 template <class F, bool GATHER>
 cudaError_t launch_tensor_core_tokens(const MatvecArgs &a, const WeightView &view, uint32_t upl, cudaStream_t stream)
 {
     if constexpr (std::is_same<F, Q4KXq8>::value) {
-        return launch_mma<Q4KMma, GATHER>(a, view, upl, stream);
+        return launch_mma<Q4KMma, GATHER>(a, view, upl, nullptr, stream);
     } else if constexpr (std::is_same<F, Q6KPlanarXq8>::value) {
-        return launch_mma<Q6KMma, GATHER>(a, view, upl, stream);
+        const unsigned char(*tensor_maps)[128] = q6k_tensor_maps(a.matrix);
+        return tensor_maps ? launch_mma<Q6KTiledMma, GATHER>(a, view, upl, tensor_maps, stream) : launch_mma<Q6KMma, GATHER>(a, view, upl, nullptr, stream);
     } else {
         return cudaErrorNotSupported;
     }
