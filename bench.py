@@ -462,9 +462,9 @@ def main():
             if not torch.equal(out_full[name], expected[name]):
                 mismatches += 1
                 sys.stderr.write(f"rank {rank}: gathered vector {name} differs from the whole-matrix product\n")
-        verdict = torch.tensor([mismatches], device=device)
-        dist.all_reduce(verdict)
-        gather_verified = {"ok": int(verdict.item()) == 0, "vectors_per_rank": checks, "ranks": world,
+        mismatch_total = torch.tensor([mismatches], device=device)
+        dist.all_reduce(mismatch_total)
+        gather_verified = {"ok": int(mismatch_total.item()) == 0, "vectors_per_rank": checks, "ranks": world,
                            "how": "bitwise equal to the whole-matrix products computed on every rank"}
         del expected
 
