@@ -112,35 +112,39 @@ def test_prompt_runs_above_four_tokens_take_the_tensor_core_path(oracle):
 
 
 @pytest.mark.parametrize("ggml_type", [sb.Q8_0, sb.Q4_K, sb.Q6_K])
-def test_gather_entry_stores_every_result_into_all_copies(ggml_type):
+@pytest.mark.parametrize("tokens", [1, 8, 11])
+def test_gather_entry_stores_every_result_into_all_copies(ggml_type, tokens):
     """syn_b200_matmul_q8_gather_dev on one GPU, the "peers" being further buffers of the same device: every copy ends up
-    holding what the plain product writes, shard by shard, and nothing outside the shard's rows is touched."""
+    holding what the plain product writes, shard by shard, and nothing outside the shard's rows is touched. One token takes
+    the pipelined kernel's storing variant, several tokens the tensor-core token groups' (Q4_K, Q6_K) or the direct-load
+    kernels' (Q8_0)."""
     import torch
 
     rows, columns, world = 768, 1024, 3
     weights = synth.matrix(ggml_type, rows, columns, seed=21)
-    x = torch.from_numpy(synth.activations(1, columns, seed=22)).cuda()
+    x = torch.from_numpy(synth.activations(tokens, columns, seed=22)).cuda()
     lib = sb.library()
-    need = lib.activation_scratch_bytes(1, columns)
+    need = lib.activation_scratch_bytes(tokens, columns)
     scratch = torch.empty(need + 256, dtype=torch.uint8, device="cuda")
     scratch_ptr = (scratch.data_ptr() + 255) // 256 * 256
-    sb.quantize_device(x.data_ptr(), 1, columns, columns, scratch_ptr, need, 0)
+    sb.quantize_device(x.data_ptr(), tokens, columns, columns, scratch_ptr, need, 0)
     with sb.QuantizedMatrix(weights, ggml_type, rows, columns) as matrix:
-        want = torch.zeros(rows, device="cuda")
-        matrix.matmul_q8_device(scratch_ptr, 1, want.data_ptr(), rows)
-        copies = [torch.full((rows,), -7.0, device="cuda") for _ in range(world)]
+        want = torch.zeros(tokens, rows, device="cuda")
+        matrix.matmul_q8_device(scratch_ptr, tokens, want.data_ptr(), rows)
+        copies = [torch.full((tokens, rows), -7.0, device="cuda") for _ in range(world)]
         share = rows // world
         for rank in (1,):  # only the middle shard is computed: the others must keep their sentinel
             first = rank * share
             own = copies[rank].data_ptr() + 4 * first
             others = [copies[r].data_ptr() + 4 * first for r in range(world) if r != rank]
-            matrix.matmul_q8_gather_device(scratch_ptr, 1, own, share, others, row_start=first, row_count=share)
+            matrix.matmul_q8_gather_device(scratch_ptr, tokens, own, rows, others, row_start=first, row_count=share)
         torch.cuda.synchronize()
         for copy in copies:
-            assert torch.equal(copy[share:2 * share], want[share:2 * share])
-            assert bool((copy[:share] == -7.0).all()) and bool((copy[2 * share:] == -7.0).all())
+            assert torch.equal(copy[:, share:2 * share], want[:, share:2 * share])
+            assert bool((copy[:, :share] == -7.0).all()) and bool((copy[:, 2 * share:] == -7.0).all())
         with pytest.raises(sb.KernelError):
-            matrix.matmul_q8_gather_device(scratch_ptr, 1, copies[0].data_ptr(), share, [copies[1].data_ptr()] * 8)
+            matrix.matmul_q8_gather_device(scratch_ptr, tokens, copies[0].data_ptr(), rows, [copies[1].data_ptr()] * 8)
+    assert lib.device_faults() == 0
 
 
 def test_shared_buffer_and_peer_access_entry_points():
