@@ -280,36 +280,38 @@ def test_gate_up_pair_in_one_launch_equals_the_two_launch_form(oracle, ggml_type
     assert lib.device_faults() == 0
 
 
-def test_completion_signal_and_bounded_wait_on_one_gpu():
+@pytest.mark.parametrize("tokens", [1, 8])
+def test_completion_signal_and_bounded_wait_on_one_gpu(tokens):
     """The exchange step's completion signal, with the "ranks" emulated on one GPU (three buffers of the same device):
     each rank's product writes its slice into all three copies and then its sequence number into its word of every copy's
     signal array; a wait on a copy succeeds once all three words show the sequence number. With one rank's product
     withheld the wait's limit runs out: the kernel returns, the fault count goes up by one, nothing is left waiting and
-    the device stays usable. The ranks run one after the other on one stream, so no kernel ever waits for a later one."""
+    the device stays usable. The ranks run one after the other on one stream, so no kernel ever waits for a later one.
+    One token signals from the pipelined kernel, eight from the tensor-core token groups."""
     import torch
 
     lib = sb.library()
     rows, columns, world = 768, 1024, 3
     share = rows // world
     weights = synth.matrix(sb.Q4_K, rows, columns, seed=451)
-    x = torch.from_numpy(synth.activations(1, columns, seed=452)).cuda()
-    need = lib.activation_scratch_bytes(1, columns)
+    x = torch.from_numpy(synth.activations(tokens, columns, seed=452)).cuda()
+    need = lib.activation_scratch_bytes(tokens, columns)
     scratch = torch.empty(need + 256, dtype=torch.uint8, device="cuda")
     scratch_ptr = (scratch.data_ptr() + 255) // 256 * 256
-    sb.quantize_device(x.data_ptr(), 1, columns, columns, scratch_ptr, need, 0)
-    copies = [torch.full((rows,), -7.0, device="cuda") for _ in range(world)]
+    sb.quantize_device(x.data_ptr(), tokens, columns, columns, scratch_ptr, need, 0)
+    copies = [torch.full((tokens, rows), -7.0, device="cuda") for _ in range(world)]
     control = [torch.zeros(32, dtype=torch.int32, device="cuda") for _ in range(world)]  # per "GPU": signal words 0..2, arrivals 16/17, epoch 24
     assert lib.device_faults(reset=True) == 0
     with sb.QuantizedMatrix(weights, sb.Q4_K, rows, columns) as matrix:
-        want = torch.zeros(rows, device="cuda")
-        matrix.matmul_q8_device(scratch_ptr, 1, want.data_ptr(), rows)
+        want = torch.zeros(tokens, rows, device="cuda")
+        matrix.matmul_q8_device(scratch_ptr, tokens, want.data_ptr(), rows)
 
         def product(rank):
             first = rank * share
             own = copies[rank].data_ptr() + 4 * first
             others = [copies[r].data_ptr() + 4 * first for r in range(world) if r != rank]
             words = [control[rank].data_ptr() + 4 * rank] + [control[r].data_ptr() + 4 * rank for r in range(world) if r != rank]
-            matrix.matmul_q8_gather_device(scratch_ptr, 1, own, share, others, row_start=first, row_count=share, signal_ptrs=words,
+            matrix.matmul_q8_gather_device(scratch_ptr, tokens, own, rows, others, row_start=first, row_count=share, signal_ptrs=words,
                                            arrivals_ptr=control[rank].data_ptr() + 4 * 16)
 
         def wait(rank, limit_us):
