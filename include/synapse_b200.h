@@ -393,8 +393,9 @@ typedef struct syn_b200_batch_token {
 typedef struct syn_b200_decoder syn_b200_decoder;
 
 /* Replaces synapse_gpu_decoder_create (ffi.rs:113-172). Up to 64 tokens per step (decode tokens of several sessions and
- * prompt runs: tokens of one slot at consecutive positions, the reference's prefill chunks); FP32 KV cache of `context`
- * positions per slot; NeoX rotary layout; SwiGLU. A token's logits do not depend on what else shares its step. */
+ * prompt runs: tokens of one slot at consecutive positions, the reference's prefill chunks); KV cache of `context`
+ * positions per slot, FP32 (kv_precision 0) or FP16 (1: KvPrecision::F16, decoder.rs:43-58 -- keys and values are rounded
+ * to the nearest fp16 number on their way in; any other value is status 2); NeoX rotary layout; SwiGLU. A token's logits do not depend on what else shares its step. */
 SYN_B200_API int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_decoder **out);
 
 /* Replaces synapse_gpu_decoder_forward (ffi.rs:181-203): one batched step; writes k * vocabulary logits for its k

@@ -1098,6 +1098,15 @@ int orc_decoder_forward(orc_decoder *d, int32_t slot, int32_t token, int32_t pos
             float *x = head < s->heads ? q + (size_t)head * s->head_dim : k + (size_t)(head - s->heads) * s->head_dim;
             orc_rotate_neox(x, s->head_dim, cosines, sines);
         }
+        if (s->kv_precision == 1) {
+            /* KvPrecision::F16 (native/synapse-gpu/src/Features/GpuKernels/decoder.rs:43-58): the cache holds the nearest
+             * fp16 number of every rotated key and value, and attention -- the current position included -- reads the
+             * cache. The CPU executor has no such mode: this branch is this backend's statement of it, not a restatement. */
+            for (size_t i = 0; i < kvw; ++i) {
+                k[i] = orc_fp16_to_f32(orc_f32_to_fp16(k[i]));
+                v[i] = orc_fp16_to_f32(orc_f32_to_fp16(v[i]));
+            }
+        }
         for (uint32_t kh = 0; kh < s->kv_heads; ++kh) {
             memcpy(d->keys + kv_index(s, (uint32_t)slot, l, kh, (uint32_t)position), k + (size_t)kh * s->head_dim, sizeof(float) * s->head_dim);
             memcpy(d->values + kv_index(s, (uint32_t)slot, l, kh, (uint32_t)position), v + (size_t)kh * s->head_dim, sizeof(float) * s->head_dim);

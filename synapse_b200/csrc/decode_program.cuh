@@ -595,9 +595,14 @@ __device__ __noinline__ void quantize_local(const Op *op, Shared &sh, uint32_t a
 // order (Qwen2CpuAttention.cs:82-173). BATCH positions are loaded at a time so that their latencies overlap (a warp far
 // into the context otherwise spends a load latency per position); the arithmetic and its order are exactly those of a
 // position-at-a-time loop, whatever BATCH is. `current_key/value` (may be null) replace the cache entry of `position`.
-template <int PER, int BATCH>
+// KV is the cache's element type: float, or __half (DecoderDesc.kv_precision = 1, KvPrecision::F16 of the reference,
+// native/synapse-gpu/src/Features/GpuKernels/decoder.rs:43-58), whose values widen exactly.
+__device__ __forceinline__ float cache_value(const float *p, uint32_t i) { return p[i]; }
+__device__ __forceinline__ float cache_value(const __half *p, uint32_t i) { return __half2float(p[i]); }
+
+template <int PER, int BATCH, class KV>
 __device__ __forceinline__ void attend_positions(const float *qv, uint32_t per_lane, uint32_t lane, int first, int position, uint32_t head_dim,
-                                                 float scale, const float *keys, const float *values, const float *current_key,
+                                                 float scale, const KV *keys, const KV *values, const float *current_key,
                                                  const float *current_value, float *acc, float &running_max, float &running_sum)
 {
     for (int p0 = first; p0 <= position; p0 += kAttentionWarps * BATCH) {
@@ -607,12 +612,17 @@ __device__ __forceinline__ void attend_positions(const float *qv, uint32_t per_l
             const int p = p0 + kAttentionWarps * b;
             const bool live = p <= position;
             const bool current = current_key && p == position;
-            const float *key = current ? current_key : keys + (uint64_t)(live ? p : position) * head_dim;
-            const float *value = current ? current_value : values + (uint64_t)(live ? p : position) * head_dim;
+            const KV *key = keys + (uint64_t)(live ? p : position) * head_dim;
+            const KV *value = values + (uint64_t)(live ? p : position) * head_dim;
 #pragma unroll
             for (int j = 0; j < PER; ++j) {
-                k[b][j] = (uint32_t)j < per_lane ? key[lane + 32 * j] : 0.0f;
-                v[b][j] = (uint32_t)j < per_lane ? value[lane + 32 * j] : 0.0f;
+                if (current) {
+                    k[b][j] = (uint32_t)j < per_lane ? current_key[lane + 32 * j] : 0.0f;
+                    v[b][j] = (uint32_t)j < per_lane ? current_value[lane + 32 * j] : 0.0f;
+                } else {
+                    k[b][j] = (uint32_t)j < per_lane ? cache_value(key, lane + 32 * j) : 0.0f;
+                    v[b][j] = (uint32_t)j < per_lane ? cache_value(value, lane + 32 * j) : 0.0f;
+                }
             }
         }
         float dots[BATCH];
@@ -649,8 +659,9 @@ __device__ __forceinline__ void attend_positions(const float *qv, uint32_t per_l
     }
 }
 // Heads of up to 128 values take four positions at a time, larger heads two (the loaded keys and values live in registers).
+template <class KV>
 __device__ __forceinline__ void attend_head(const float *qv, uint32_t per_lane, uint32_t lane, int first, int position, uint32_t head_dim,
-                                            float scale, const float *keys, const float *values, const float *current_key,
+                                            float scale, const KV *keys, const KV *values, const float *current_key,
                                             const float *current_value, float *acc, float &running_max, float &running_sum)
 {
     if (per_lane <= 4) {

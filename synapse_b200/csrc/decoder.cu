@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 #include <vector>
 
 #include "common.cuh"
@@ -129,9 +130,17 @@ rmsnorm_quantize_kernel(const BatchToken *__restrict__ tokens, const float *__re
 
 // NeoX rotation of every query and key head (first half against second half, Qwen2CpuState.cs:85-105) and the
 // append of the rotated key and the value to the slot's cache. Grid (heads + kv_heads, tokens), head_dim/2 threads.
+// What a value becomes in the cache: itself, or the nearest fp16 number (KvPrecision::F16,
+// native/synapse-gpu/src/Features/GpuKernels/decoder.rs:43-58).
+__device__ __forceinline__ void cache_store(float *p, float v) { *p = v; }
+__device__ __forceinline__ void cache_store(__half *p, float v) { *p = __float2half_rn(v); }
+__device__ __forceinline__ float cache_rounded(const float *, float v) { return v; }
+__device__ __forceinline__ float cache_rounded(const __half *, float v) { return __half2float(__float2half_rn(v)); }
+
+template <class KV>
 __global__ void rope_store_kernel(const BatchToken *__restrict__ tokens, float *__restrict__ q, float *__restrict__ k,
                                   const float *__restrict__ v, const float *__restrict__ cosines, const float *__restrict__ sines,
-                                  float *__restrict__ keys, float *__restrict__ values, uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
+                                  KV *__restrict__ keys, KV *__restrict__ values, uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
                                   uint32_t layer, uint32_t layers, uint32_t context)
 {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -147,11 +156,11 @@ __global__ void rope_store_kernel(const BatchToken *__restrict__ tokens, float *
     if (head >= heads) {
         const uint32_t kh = head - heads;
         const uint64_t at = ((((uint64_t)token.slot * layers + layer) * kv_heads + kh) * context + token.position) * head_dim;
-        keys[at + i] = first;
-        keys[at + i + half] = second;
+        cache_store(keys + at + i, first);
+        cache_store(keys + at + i + half, second);
         const float *vs = v + ((uint64_t)t * kv_heads + kh) * head_dim;
-        values[at + i] = vs[i];
-        values[at + i + half] = vs[i + half];
+        cache_store(values + at + i, vs[i]);
+        cache_store(values + at + i + half, vs[i + half]);
     }
 }
 
@@ -162,10 +171,12 @@ __global__ void rope_store_kernel(const BatchToken *__restrict__ tokens, float *
 // head and the key head it reads, the first query head of every key head appends key and value to the cache -- and
 // attends to the current position out of shared memory. Same arithmetic, one launch less per layer. Steps with several
 // tokens keep the separate rotation kernel: a prompt run's later tokens read the cache entries of its earlier ones.
-template <bool ROTATE>
+// KV: the cache's element type. With fp16 the current position is attended to with the values the cache holds for it
+// (rounded), as every later step will see them.
+template <bool ROTATE, class KV>
 __global__ void __launch_bounds__(32 * prog::kAttentionWarps)
 attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
-                 const float *__restrict__ cosines, const float *__restrict__ sines, float *__restrict__ keys, float *__restrict__ values,
+                 const float *__restrict__ cosines, const float *__restrict__ sines, KV *__restrict__ keys, KV *__restrict__ values,
                  uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t layer, uint32_t layers, uint32_t context, float scale,
                  int8_t *__restrict__ codes, float *__restrict__ scales, int16_t *__restrict__ sums)
 {
@@ -193,16 +204,16 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
             const float first = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)), second = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
             const float *vs = v + ((uint64_t)t * kv_heads + kh) * head_dim;
             const float v0 = vs[i], v1 = vs[i + half];
-            current_key[i] = first;
-            current_key[i + half] = second;
-            current_value[i] = v0;
-            current_value[i + half] = v1;
+            current_key[i] = cache_rounded(keys, first);
+            current_key[i + half] = cache_rounded(keys, second);
+            current_value[i] = cache_rounded(values, v0);
+            current_value[i + half] = cache_rounded(values, v1);
             if (head % group == 0) {
                 const uint64_t at = base + (uint64_t)token.position * head_dim;
-                keys[at + i] = first;
-                keys[at + i + half] = second;
-                values[at + i] = v0;
-                values[at + i + half] = v1;
+                cache_store(keys + at + i, first);
+                cache_store(keys + at + i + half, second);
+                cache_store(values + at + i, v0);
+                cache_store(values + at + i + half, v1);
             }
         }
         __syncthreads();
@@ -215,7 +226,7 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
         acc[j] = 0.0f;
     }
     float running_max = -INFINITY, running_sum = 0.0f;
-    prog::attend_head(qv, per_lane, lane, (int)warp, token.position, head_dim, scale, keys + base, values + base, ROTATE ? current_key : nullptr,
+    prog::attend_head(qv, per_lane, lane, (int)warp, token.position, head_dim, scale, (const KV *)keys + base, (const KV *)values + base, ROTATE ? current_key : nullptr,
                       ROTATE ? current_value : nullptr, acc, running_max, running_sum);
 #pragma unroll
     for (int j = 0; j < kPerLane; ++j) {
@@ -558,21 +569,29 @@ cudaError_t enqueue_step(syn_b200_decoder *d, uint32_t count, uint32_t logits_ro
             const ActLayout layout = act_layout(count, hidden);
             uint8_t *base = static_cast<uint8_t *>(d->act_hidden);
             const float scale = 1.0f / sqrtf((float)s.head_dim);
-            if (count == 1) {
-                SYN_TRY(launch_kernel(attention_kernel<true>, dim3(s.heads, count), dim3(32 * prog::kAttentionWarps), 0, d->stream,
-                                      (const BatchToken *)d->device_tokens, (const float *)d->q, (const float *)d->k, (const float *)d->v,
-                                      (const float *)d->cosines, (const float *)d->sines, d->keys, d->values, s.heads, s.kv_heads, s.head_dim, l,
-                                      s.layer_count, s.context, scale, reinterpret_cast<int8_t *>(base + layout.codes),
-                                      reinterpret_cast<float *>(base + layout.scales), reinterpret_cast<int16_t *>(base + layout.sums)));
-            } else {
-                SYN_TRY(launch_kernel(rope_store_kernel, dim3(s.heads + s.kv_heads, count), dim3(s.head_dim / 2), 0, d->stream,
+            auto attend = [&](auto *cache_keys, auto *cache_values) -> cudaError_t {
+                using KV = std::remove_pointer_t<decltype(cache_keys)>;
+                int8_t *const codes = reinterpret_cast<int8_t *>(base + layout.codes);
+                float *const scales = reinterpret_cast<float *>(base + layout.scales);
+                int16_t *const sums = reinterpret_cast<int16_t *>(base + layout.sums);
+                if (count == 1) {
+                    return launch_kernel(attention_kernel<true, KV>, dim3(s.heads, count), dim3(32 * prog::kAttentionWarps), 0, d->stream,
+                                         (const BatchToken *)d->device_tokens, (const float *)d->q, (const float *)d->k, (const float *)d->v,
+                                         (const float *)d->cosines, (const float *)d->sines, cache_keys, cache_values, s.heads, s.kv_heads, s.head_dim, l,
+                                         s.layer_count, s.context, scale, codes, scales, sums);
+                }
+                SYN_TRY(launch_kernel(rope_store_kernel<KV>, dim3(s.heads + s.kv_heads, count), dim3(s.head_dim / 2), 0, d->stream,
                                       (const BatchToken *)d->device_tokens, d->q, d->k, (const float *)d->v, (const float *)d->cosines,
-                                      (const float *)d->sines, d->keys, d->values, s.heads, s.kv_heads, s.head_dim, l, s.layer_count, s.context));
-                SYN_TRY(launch_kernel(attention_kernel<false>, dim3(s.heads, count), dim3(32 * prog::kAttentionWarps), 0, d->stream,
-                                      (const BatchToken *)d->device_tokens, (const float *)d->q, (const float *)d->k, (const float *)d->v,
-                                      (const float *)d->cosines, (const float *)d->sines, d->keys, d->values, s.heads, s.kv_heads, s.head_dim, l,
-                                      s.layer_count, s.context, scale, reinterpret_cast<int8_t *>(base + layout.codes),
-                                      reinterpret_cast<float *>(base + layout.scales), reinterpret_cast<int16_t *>(base + layout.sums)));
+                                      (const float *)d->sines, cache_keys, cache_values, s.heads, s.kv_heads, s.head_dim, l, s.layer_count, s.context));
+                return launch_kernel(attention_kernel<false, KV>, dim3(s.heads, count), dim3(32 * prog::kAttentionWarps), 0, d->stream,
+                                     (const BatchToken *)d->device_tokens, (const float *)d->q, (const float *)d->k, (const float *)d->v,
+                                     (const float *)d->cosines, (const float *)d->sines, cache_keys, cache_values, s.heads, s.kv_heads, s.head_dim, l,
+                                     s.layer_count, s.context, scale, codes, scales, sums);
+            };
+            if (s.kv_precision == 1) {
+                SYN_TRY(attend(reinterpret_cast<__half *>(d->keys), reinterpret_cast<__half *>(d->values)));
+            } else {
+                SYN_TRY(attend(d->keys, d->values));
             }
         }
         Epilogue residual;
@@ -711,8 +730,8 @@ cudaError_t build_program(syn_b200_decoder *d)
     // of them is the faster form on every shape measured (7B Q4_K_M: 1.6 ms per token against 1.8 ms; 0.5B Q8_0: 0.65
     // against 1.0 ms). The program stays as the reference point for that comparison and is kept bit-identical by the tests.
     const char *choice = getenv("SYN_B200_DECODE_PROGRAM");
-    if (!choice || choice[0] != '1') {
-        return cudaSuccess;
+    if (!choice || choice[0] != '1' || s.kv_precision != 0) {
+        return cudaSuccess;  // (the program reads an FP32 cache)
     }
     int cooperative = 0;
     cudaDeviceGetAttribute(&cooperative, cudaDevAttrCooperativeLaunch, d->device);
@@ -1104,8 +1123,12 @@ int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_deco
         if (s.step_tokens > kMaxStepTokens || s.logits_rows > s.step_tokens) {
             return fail(SYN_B200_UNAVAILABLE, "a step holds at most " + std::to_string(kMaxStepTokens) + " tokens on this backend");
         }
-        if (s.kv_precision != 0 || s.rope_layout != 0 || s.activation != 0) {
-            return fail(SYN_B200_UNAVAILABLE, "only FP32 KV, the NeoX rotary layout and SwiGLU are implemented");
+        if (s.kv_precision > 1) {
+            // decoder_tests.rs:211-230: an unknown precision is an invalid argument, not a missing feature
+            return fail(SYN_B200_INVALID_ARGUMENT, "unknown KV precision " + std::to_string(s.kv_precision) + " (0 = FP32, 1 = FP16)");
+        }
+        if (s.rope_layout != 0 || s.activation != 0) {
+            return fail(SYN_B200_UNAVAILABLE, "only the NeoX rotary layout and SwiGLU are implemented");
         }
         int device = 0;
         if (cudaGetDevice(&device) != cudaSuccess) {
@@ -1169,8 +1192,10 @@ int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_deco
         if (status == SYN_B200_OK) status = device_alloc(d, &d->logits, (uint64_t)s.logits_rows * s.vocabulary);
         if (status == SYN_B200_OK) status = device_alloc(d, &act_hidden, act_layout(T, s.hidden).total);
         if (status == SYN_B200_OK) status = device_alloc(d, &act_ffn, act_layout(T, s.feed_forward).total);
-        if (status == SYN_B200_OK) status = device_alloc(d, &d->keys, cache);
-        if (status == SYN_B200_OK) status = device_alloc(d, &d->values, cache);
+        // the cache: `cache` elements each of keys and values, 4 or 2 bytes wide (held through float pointers either way)
+        const uint64_t cache_floats = s.kv_precision == 1 ? (cache + 1) / 2 : cache;
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->keys, cache_floats);
+        if (status == SYN_B200_OK) status = device_alloc(d, &d->values, cache_floats);
         if (status == SYN_B200_OK) status = device_alloc(d, &d->device_tokens, T);
         if (status == SYN_B200_OK) status = device_alloc(d, &d->device_argmax, T);
         if (status == SYN_B200_OK) status = device_alloc(d, &d->argmax_value, T * kArgmaxSlices);
@@ -1182,8 +1207,8 @@ int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_deco
         cudaError_t error = cudaMemcpy(d->cosines, s.rope_cosines, (uint64_t)s.context * half * 4, cudaMemcpyHostToDevice);
         if (error == cudaSuccess) error = cudaMemcpy(d->sines, s.rope_sines, (uint64_t)s.context * half * 4, cudaMemcpyHostToDevice);
         if (error == cudaSuccess) error = cudaMemset(d->argmax_arrivals, 0, T * sizeof(uint32_t));
-        if (error == cudaSuccess) error = cudaMemset(d->keys, 0, cache * 4);
-        if (error == cudaSuccess) error = cudaMemset(d->values, 0, cache * 4);
+        if (error == cudaSuccess) error = cudaMemset(d->keys, 0, cache_floats * 4);
+        if (error == cudaSuccess) error = cudaMemset(d->values, 0, cache_floats * 4);
         if (error == cudaSuccess) error = cudaHostAlloc(reinterpret_cast<void **>(&d->host_tokens), T * sizeof(syn::BatchToken), cudaHostAllocDefault);
         if (error == cudaSuccess) error = cudaHostAlloc(reinterpret_cast<void **>(&d->host_argmax), T * sizeof(int32_t), cudaHostAllocDefault);
         if (error == cudaSuccess) {
@@ -1317,7 +1342,7 @@ uint64_t syn_b200_decoder_kv_bytes(const syn_b200_decoder *d)
         return 0;
     }
     const syn_b200_decoder_desc &s = d->shape;
-    return 2ull * s.session_slots * s.layer_count * s.kv_heads * s.context * s.head_dim * 4;
+    return 2ull * s.session_slots * s.layer_count * s.kv_heads * s.context * s.head_dim * (s.kv_precision == 1 ? 2 : 4);
 }
 
 }  // extern "C"

@@ -117,7 +117,8 @@ class ModelImage:
         for key, value in self.shape.items():
             setattr(d, key, value)
         d.embedding_encoding, d.output_encoding = self.embedding_type, self.output_type
-        d.rope_layout = d.activation = d.kv_precision = 0
+        d.rope_layout = d.activation = 0
+        d.kv_precision = getattr(self, "kv_precision", 0)  # 0 = FP32 cache, 1 = FP16 (KvPrecision of the reference)
         d.kv_growth_positions = 1024
         return d
 

@@ -54,6 +54,39 @@ def test_tiny_models_decode_like_the_cpu_executor(oracle, types, embedding, outp
     assert sb.library().device_faults() == 0
 
 
+@pytest.mark.parametrize("types,embedding,output", [(dec.Q8_TYPES, synth.Q8_0, synth.Q8_0), (dec.Q4KM_TYPES, synth.Q4_K, synth.Q6_K)])
+def test_fp16_kv_cache(oracle, types, embedding, output):
+    """DecoderDesc.kv_precision = 1 (KvPrecision::F16, native/synapse-gpu/src/Features/GpuKernels/decoder.rs:43-58; the
+    reference tests the plan only: decoder_tests.rs:211-230): the cache holds the nearest fp16 number of every rotated key
+    and value and takes half the bytes; an unknown precision is an invalid argument. The logits follow the oracle's step
+    with the same rounding at the same gate as the FP32 cache, differ from the FP32-cache logits (how far is the model's
+    business: random weights amplify the 2^-11 rounding), and a prompt run in chunks gives the bits of token-by-token steps (single-token steps rotate and store inside the
+    attention kernel, prompt runs through the separate kernel: both must round the same way)."""
+    image = dec.ModelImage(**TINY, matrix_types=types, embedding_type=embedding, output_type=output, seed=5, bias=True, step_tokens=8)
+    full = dec.ModelImage(**TINY, matrix_types=types, embedding_type=embedding, output_type=output, seed=5, bias=True, step_tokens=8)
+    image.kv_precision = 1
+    with dec.Decoder(full) as wide, dec.Decoder(image) as narrow:
+        assert narrow.kv_bytes() * 2 == wide.kv_bytes()
+    records = _greedy(image, 12, oracle)
+    for r in records:
+        assert r["error"] <= 2e-3, r
+        assert r["gpu"] == r["cpu"], r
+    tokens = [11, 5, 900, 33, 7, 450, 2, 81]
+    with dec.Decoder(full) as wide, dec.Decoder(image) as narrow, dec.Decoder(image) as chunked:
+        singles = []
+        for position, token in enumerate(tokens):
+            wide.decode(token, position)
+            singles.append(narrow.decode(token, position))
+        assert not np.array_equal(wide.decode(3, len(tokens)), narrow.decode(3, len(tokens))), "the cache is not rounded"
+        run = chunked.forward([(0, token, position, position) for position, token in enumerate(tokens)])
+        for position in range(len(tokens)):
+            assert run[position].tobytes() == singles[position].tobytes(), position
+    image.kv_precision = 2
+    with pytest.raises(sb.KernelError, match="KV precision"):
+        dec.Decoder(image)
+    assert sb.library().device_faults() == 0
+
+
 def test_batched_steps_match_single_token_steps(oracle):
     """Tokens of two sessions sharing a step get the logits they would get alone (batch invariance,
     OptimizedQwen2Tests.cs:41-54)."""
