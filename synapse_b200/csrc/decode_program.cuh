@@ -597,8 +597,14 @@ __device__ __noinline__ void quantize_local(const Op *op, Shared &sh, uint32_t a
 // position-at-a-time loop, whatever BATCH is. `current_key/value` (may be null) replace the cache entry of `position`.
 // KV is the cache's element type: float, or __half (DecoderDesc.kv_precision = 1, KvPrecision::F16 of the reference,
 // native/synapse-gpu/src/Features/GpuKernels/decoder.rs:43-58), whose values widen exactly.
-__device__ __forceinline__ float cache_value(const float *p, uint32_t i) { return p[i]; }
-__device__ __forceinline__ float cache_value(const __half *p, uint32_t i) { return __half2float(p[i]); }
+// Which element of a head lane `lane` holds in its j-th register. FP32 cache: lane + 32 j (a warp's load covers 128
+// consecutive bytes). FP16 cache: the lane takes PAIRS of consecutive values, (j / 2) * 64 + 2 * lane + j % 2, so that
+// one 4-byte load brings two of its values and a warp's load again covers 128 consecutive bytes (head_dim a multiple of 64).
+template <class KV>
+__device__ __forceinline__ uint32_t head_element(uint32_t lane, uint32_t j)
+{
+    return sizeof(KV) == 2 ? (j >> 1) * 64 + 2 * lane + (j & 1) : lane + 32 * j;
+}
 
 template <int PER, int BATCH, class KV>
 __device__ __forceinline__ void attend_positions(const float *qv, uint32_t per_lane, uint32_t lane, int first, int position, uint32_t head_dim,
@@ -607,6 +613,9 @@ __device__ __forceinline__ void attend_positions(const float *qv, uint32_t per_l
 {
     for (int p0 = first; p0 <= position; p0 += kAttentionWarps * BATCH) {
         float k[BATCH][PER], v[BATCH][PER];
+        // FP16 cache: the loaded pairs stay as they are until every load of the batch has been issued (a conversion right
+        // behind its load would hold the warp, and with it the next load, for the load's whole latency)
+        __half2 k_pairs[sizeof(KV) == 2 ? BATCH : 1][sizeof(KV) == 2 ? PER / 2 : 1], v_pairs[sizeof(KV) == 2 ? BATCH : 1][sizeof(KV) == 2 ? PER / 2 : 1];
 #pragma unroll
         for (int b = 0; b < BATCH; ++b) {
             const int p = p0 + kAttentionWarps * b;
@@ -614,14 +623,45 @@ __device__ __forceinline__ void attend_positions(const float *qv, uint32_t per_l
             const bool current = current_key && p == position;
             const KV *key = keys + (uint64_t)(live ? p : position) * head_dim;
             const KV *value = values + (uint64_t)(live ? p : position) * head_dim;
+            if constexpr (sizeof(KV) == 2) {
 #pragma unroll
-            for (int j = 0; j < PER; ++j) {
-                if (current) {
+                for (int j = 0; j < PER; j += 2) {
+                    // unconditional loads (registers past the head's width re-read its first pair and are zeroed later)
+                    const uint32_t element = head_element<KV>(lane, (uint32_t)j < per_lane ? j : 0);
+                    if (current) {
+                        // the current position's values were rounded to fp16 when they were put into shared memory
+                        k_pairs[b][j / 2] = __floats2half2_rn(current_key[element], current_key[element + 1]);
+                        v_pairs[b][j / 2] = __floats2half2_rn(current_value[element], current_value[element + 1]);
+                    } else {
+                        k_pairs[b][j / 2] = *reinterpret_cast<const __half2 *>(key + element);
+                        v_pairs[b][j / 2] = *reinterpret_cast<const __half2 *>(value + element);
+                    }
+                }
+            } else if (current) {
+#pragma unroll
+                for (int j = 0; j < PER; ++j) {
                     k[b][j] = (uint32_t)j < per_lane ? current_key[lane + 32 * j] : 0.0f;
                     v[b][j] = (uint32_t)j < per_lane ? current_value[lane + 32 * j] : 0.0f;
-                } else {
-                    k[b][j] = (uint32_t)j < per_lane ? cache_value(key, lane + 32 * j) : 0.0f;
-                    v[b][j] = (uint32_t)j < per_lane ? cache_value(value, lane + 32 * j) : 0.0f;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < PER; ++j) {
+                    k[b][j] = (uint32_t)j < per_lane ? key[lane + 32 * j] : 0.0f;
+                    v[b][j] = (uint32_t)j < per_lane ? value[lane + 32 * j] : 0.0f;
+                }
+            }
+        }
+        if constexpr (sizeof(KV) == 2) {
+#pragma unroll
+            for (int b = 0; b < BATCH; ++b) {
+#pragma unroll
+                for (int j = 0; j < PER; j += 2) {
+                    const bool used = (uint32_t)j < per_lane;
+                    const float2 kk = __half22float2(k_pairs[b][j / 2]), vv = __half22float2(v_pairs[b][j / 2]);
+                    k[b][j] = used ? kk.x : 0.0f;
+                    k[b][j + 1] = used ? kk.y : 0.0f;
+                    v[b][j] = used ? vv.x : 0.0f;
+                    v[b][j + 1] = used ? vv.y : 0.0f;
                 }
             }
         }
@@ -664,12 +704,14 @@ __device__ __forceinline__ void attend_head(const float *qv, uint32_t per_lane, 
                                             float scale, const KV *keys, const KV *values, const float *current_key,
                                             const float *current_value, float *acc, float &running_max, float &running_sum)
 {
+    // (an FP16 cache's loads are half as wide: twice the positions in flight)
+    constexpr int kDeeper = sizeof(KV) == 2 ? 2 : 1;
     if (per_lane <= 4) {
-        attend_positions<4, 4>(qv, per_lane, lane, first, position, head_dim, scale, keys, values, current_key, current_value, acc, running_max,
-                               running_sum);
+        attend_positions<4, 4 * kDeeper>(qv, per_lane, lane, first, position, head_dim, scale, keys, values, current_key, current_value, acc, running_max,
+                                         running_sum);
     } else {
-        attend_positions<8, 2>(qv, per_lane, lane, first, position, head_dim, scale, keys, values, current_key, current_value, acc, running_max,
-                               running_sum);
+        attend_positions<8, 2 * kDeeper>(qv, per_lane, lane, first, position, head_dim, scale, keys, values, current_key, current_value, acc, running_max,
+                                         running_sum);
     }
 }
 

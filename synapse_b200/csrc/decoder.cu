@@ -222,7 +222,7 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
     float qv[kPerLane], acc[kPerLane];
 #pragma unroll
     for (int j = 0; j < kPerLane; ++j) {
-        qv[j] = (uint32_t)j < per_lane ? query[lane + 32 * j] : 0.0f;
+        qv[j] = (uint32_t)j < per_lane ? query[prog::head_element<KV>(lane, j)] : 0.0f;
         acc[j] = 0.0f;
     }
     float running_max = -INFINITY, running_sum = 0.0f;
@@ -231,7 +231,7 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
 #pragma unroll
     for (int j = 0; j < kPerLane; ++j) {
         if ((uint32_t)j < per_lane) {
-            merged[warp][lane + 32 * j] = acc[j];
+            merged[warp][prog::head_element<KV>(lane, j)] = acc[j];
         }
     }
     if (lane == 0) {
@@ -1126,6 +1126,9 @@ int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_deco
         if (s.kv_precision > 1) {
             // decoder_tests.rs:211-230: an unknown precision is an invalid argument, not a missing feature
             return fail(SYN_B200_INVALID_ARGUMENT, "unknown KV precision " + std::to_string(s.kv_precision) + " (0 = FP32, 1 = FP16)");
+        }
+        if (s.kv_precision == 1 && s.head_dim % 64 != 0) {
+            return fail(SYN_B200_UNAVAILABLE, "the FP16 KV cache needs a head_dim that is a multiple of 64");
         }
         if (s.rope_layout != 0 || s.activation != 0) {
             return fail(SYN_B200_UNAVAILABLE, "only the NeoX rotary layout and SwiGLU are implemented");

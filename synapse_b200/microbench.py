@@ -28,6 +28,9 @@ def main():
     parser.add_argument("--mode", default="xq8", choices=["xq8", "xf32", "gemm", "decode", "pair"],
                         help="pair: consecutive copies are the gate and up matrix of one launch that stores silu(gate . x) * (up . x)")
     parser.add_argument("--layers", type=int, default=4, help="decode mode: layers of the Qwen2.5-7B-shaped Q4_K_M model")
+    parser.add_argument("--context", type=int, default=64, help="decode mode: positions of the KV cache")
+    parser.add_argument("--position", type=int, default=0, help="decode mode: position of the first step (the cache before it holds zeros)")
+    parser.add_argument("--kv-fp16", action="store_true", help="decode mode: FP16 KV cache (kv_precision 1)")
     parser.add_argument("--no-repack", action="store_true")
     parser.add_argument("--fused-quantize", action="store_true", help="time quantise + product together (xq8)")
     parser.add_argument("--no-graph", action="store_true", help="launch from the host each time instead of replaying one CUDA graph")
@@ -116,10 +119,11 @@ def decode(args):
     from synapse_b200 import decoder as dec
     from synapse_b200 import synth
 
-    image = dec.ModelImage(**dict(dec.QWEN25_7B, layers=args.layers), context=64, matrix_types=dec.Q4KM_TYPES, embedding_type=synth.Q4_K,
+    image = dec.ModelImage(**dict(dec.QWEN25_7B, layers=args.layers), context=args.context, matrix_types=dec.Q4KM_TYPES, embedding_type=synth.Q4_K,
                            output_type=synth.Q4_K, seed=100)
+    image.kv_precision = 1 if args.kv_fp16 else 0
     with dec.Decoder(image) as model:
-        token, position = 5, 0
+        token, position = 5, args.position
         for _ in range(args.warmup):
             token = model.forward_argmax([(0, token, position, 0)])[0]
             position += 1
@@ -128,7 +132,8 @@ def decode(args):
             token = model.forward_argmax([(0, token, position, 0)])[0]
             position += 1
         seconds = time.perf_counter() - start
-    print(json.dumps({"mode": "decode", "layers": args.layers, "steps": args.reps, "ms_per_step": seconds / args.reps * 1e3,
+    print(json.dumps({"mode": "decode", "layers": args.layers, "steps": args.reps, "first_position": args.position, "kv": "fp16" if args.kv_fp16 else "fp32",
+                      "ms_per_step": seconds / args.reps * 1e3,
                       "weight_gbs": image.matrix_bytes * args.reps / seconds / 1e9, "last_token": token,
                       "device_faults": sb.library().device_faults()}))
 
