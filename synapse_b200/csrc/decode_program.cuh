@@ -593,8 +593,7 @@ __device__ __noinline__ void quantize_local(const Op *op, Shared &sh, uint32_t a
 
 // One warp's share of a head's attention: positions first, first + kAttentionWarps, ... up to `position`, online softmax in that
 // order (Qwen2CpuAttention.cs:82-173). BATCH positions are loaded at a time so that their latencies overlap (a warp far
-// into the context otherwise spends a load latency per position); the arithmetic and its order are exactly those of a
-// position-at-a-time loop, whatever BATCH is. `current_key/value` (may be null) replace the cache entry of `position`.
+// into the context otherwise spends a load latency per position) and enter the running softmax together. `current_key/value` (may be null) replace the cache entry of `position`.
 // KV is the cache's element type: float, or __half (DecoderDesc.kv_precision = 1, KvPrecision::F16 of the reference,
 // native/synapse-gpu/src/Features/GpuKernels/decoder.rs:43-58), whose values widen exactly.
 // Which element of a head lane `lane` holds in its j-th register. FP32 cache: lane + 32 j (a warp's load covers 128
@@ -680,22 +679,36 @@ __device__ __forceinline__ void attend_positions(const float *qv, uint32_t per_l
             }
             dots[b] = dot;
         }
+        // One softmax update per batch: the batch's maximum first, then one rescale of what has been accumulated and the
+        // batch's weights side by side (a position-at-a-time update is a chain of two exponentials per position that
+        // nothing else can overlap with; far into the context that chain, not the loads, set the pace).
+        float batch_max = running_max, scores[BATCH];
 #pragma unroll
         for (int b = 0; b < BATCH; ++b) {
-            if (p0 + kAttentionWarps * b <= position) {
-                const float score = dots[b] * scale;
-                const float next_max = fmaxf(running_max, score);
-                const float rescale = expf(running_max - next_max), weight = expf(score - next_max);
+            scores[b] = p0 + kAttentionWarps * b <= position ? dots[b] * scale : -INFINITY;
+            batch_max = fmaxf(batch_max, scores[b]);
+        }
+        // (position p0 is live, so batch_max is finite; exp(-inf) = 0 covers the first batch and the dead positions)
+        const float rescale = expf(running_max - batch_max);
+        float weights[BATCH], total = 0.0f;
 #pragma unroll
-                for (int j = 0; j < PER; ++j) {
-                    if ((uint32_t)j < per_lane) {
-                        acc[j] = fmaf(weight, v[b][j], acc[j] * rescale);
-                    }
+        for (int b = 0; b < BATCH; ++b) {
+            weights[b] = expf(scores[b] - batch_max);
+            total += weights[b];
+        }
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            if ((uint32_t)j < per_lane) {
+                float a = acc[j] * rescale;
+#pragma unroll
+                for (int b = 0; b < BATCH; ++b) {
+                    a = fmaf(weights[b], v[b][j], a);
                 }
-                running_sum = running_sum * rescale + weight;
-                running_max = next_max;
+                acc[j] = a;
             }
         }
+        running_sum = running_sum * rescale + total;
+        running_max = batch_max;
     }
 }
 // Heads of up to 128 values take four positions at a time, larger heads two (the loaded keys and values live in registers).
