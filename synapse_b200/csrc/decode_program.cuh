@@ -176,8 +176,9 @@ struct Shared {
     double square_sums[8];
     float norm_scale;
     int abort;  // set once a wait gave up: nobody waits any more
-    float merged[kAttentionWarps][256 + 2];
-    float query[256], key[256], value[256];
+    // (rows of a multiple of four floats and 16-byte aligned vectors: the attention walk moves them four values at a time)
+    alignas(16) float merged[kAttentionWarps][256 + 4];  // a warp's unnormalised sum, [256] its maximum, [257] its weight sum
+    alignas(16) float query[256], key[256], value[256];
     float best_value[kConsumerWarps];
     int best_index[kConsumerWarps];
     double quad_sums[kNormQuadsMax];                 // sums of squares of 128-value pieces of the vector being normalised
@@ -591,140 +592,180 @@ __device__ __noinline__ void quantize_local(const Op *op, Shared &sh, uint32_t a
     consumer_sync();
 }
 
-// One warp's share of a head's attention: positions first, first + kAttentionWarps, ... up to `position`, online softmax in that
-// order (Qwen2CpuAttention.cs:82-173). BATCH positions are loaded at a time so that their latencies overlap (a warp far
-// into the context otherwise spends a load latency per position) and enter the running softmax together. `current_key/value` (may be null) replace the cache entry of `position`.
+// One warp's share of a head's attention (Qwen2CpuAttention.cs:82-173, as a running softmax). Lane 8 g + e owns elements
+// [e * E, (e + 1) * E) of the head, E = head_dim / 8, in position stream 4 * warp + g: the warp walks four positions at
+// once, a position's dot product is reduced over eight lanes (three shuffles instead of five per position) and every
+// lane's loads are whole 16-byte pieces. A stream takes positions stream, stream + 4 * kAttentionWarps, ...; BATCH of them
+// are loaded at a time so that their latencies overlap, and enter the running softmax together: the batch's maximum
+// first, then one rescale of what has been accumulated and the batch's weights side by side. `current_key/value` (may
+// be null) replace the cache entry of `position`. The four streams of the warp are merged at the end; the warp leaves
+// its unnormalised sum in merged_row[0 .. head_dim), its maximum in [256] and its weight sum in [257].
 // KV is the cache's element type: float, or __half (DecoderDesc.kv_precision = 1, KvPrecision::F16 of the reference,
-// native/synapse-gpu/src/Features/GpuKernels/decoder.rs:43-58), whose values widen exactly.
-// Which element of a head lane `lane` holds in its j-th register. FP32 cache: lane + 32 j (a warp's load covers 128
-// consecutive bytes). FP16 cache: the lane takes PAIRS of consecutive values, (j / 2) * 64 + 2 * lane + j % 2, so that
-// one 4-byte load brings two of its values and a warp's load again covers 128 consecutive bytes (head_dim a multiple of 64).
-template <class KV>
-__device__ __forceinline__ uint32_t head_element(uint32_t lane, uint32_t j)
+// native/synapse-gpu/src/Features/GpuKernels/decoder.rs:43-58), whose values widen exactly; head_dim is then a multiple
+// of 64, so that a lane's E values are whole 16-byte pieces too.
+template <class KV, int E4, int BATCH>
+__device__ __forceinline__ void attend_streams(const float *query, uint32_t lane, uint32_t warp, int position, uint32_t head_dim, float scale,
+                                               const KV *keys, const KV *values, const float *current_key, const float *current_value,
+                                               float *merged_row)
 {
-    return sizeof(KV) == 2 ? (j >> 1) * 64 + 2 * lane + (j & 1) : lane + 32 * j;
-}
-
-template <int PER, int BATCH, class KV>
-__device__ __forceinline__ void attend_positions(const float *qv, uint32_t per_lane, uint32_t lane, int first, int position, uint32_t head_dim,
-                                                 float scale, const KV *keys, const KV *values, const float *current_key,
-                                                 const float *current_value, float *acc, float &running_max, float &running_sum)
-{
-    for (int p0 = first; p0 <= position; p0 += kAttentionWarps * BATCH) {
-        float k[BATCH][PER], v[BATCH][PER];
-        // FP16 cache: the loaded pairs stay as they are until every load of the batch has been issued (a conversion right
+    constexpr bool kHalf = sizeof(KV) == 2;
+    const uint32_t group = lane >> 3, part = lane & 7;
+    const uint32_t e4 = head_dim / 32;           // 16-byte pieces of FP32 per lane
+    const uint32_t first_element = part * (head_dim / 8);
+    float4 q[E4], acc[E4];
+#pragma unroll
+    for (int i = 0; i < E4; ++i) {
+        q[i] = (uint32_t)i < e4 ? *reinterpret_cast<const float4 *>(query + first_element + 4 * i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    float running_max = -INFINITY, running_sum = 0.0f;
+    const int stride = 4 * kAttentionWarps;
+    // The loop count must be the same for all lanes of the warp (the shuffles below name all of them): it runs over the
+    // warp's first stream, and a stream that has run out of positions takes part with weights of zero.
+    for (int base = (int)(4 * warp); base <= position; base += stride * BATCH) {
+        const int p0 = base + (int)group;
+        float4 k[BATCH][E4], v[BATCH][E4];
+        // FP16 cache: the loaded pieces stay as they are until every load of the batch has been issued (a conversion right
         // behind its load would hold the warp, and with it the next load, for the load's whole latency)
-        __half2 k_pairs[sizeof(KV) == 2 ? BATCH : 1][sizeof(KV) == 2 ? PER / 2 : 1], v_pairs[sizeof(KV) == 2 ? BATCH : 1][sizeof(KV) == 2 ? PER / 2 : 1];
+        uint4 k_raw[kHalf ? BATCH : 1][kHalf ? (E4 + 1) / 2 : 1], v_raw[kHalf ? BATCH : 1][kHalf ? (E4 + 1) / 2 : 1];
 #pragma unroll
         for (int b = 0; b < BATCH; ++b) {
-            const int p = p0 + kAttentionWarps * b;
+            const int p = p0 + stride * b;
             const bool live = p <= position;
             const bool current = current_key && p == position;
-            const KV *key = keys + (uint64_t)(live ? p : position) * head_dim;
-            const KV *value = values + (uint64_t)(live ? p : position) * head_dim;
-            if constexpr (sizeof(KV) == 2) {
+            const uint64_t row = (uint64_t)(live ? p : position) * head_dim + first_element;
+            if (current) {
 #pragma unroll
-                for (int j = 0; j < PER; j += 2) {
-                    // unconditional loads (registers past the head's width re-read its first pair and are zeroed later)
-                    const uint32_t element = head_element<KV>(lane, (uint32_t)j < per_lane ? j : 0);
-                    if (current) {
-                        // the current position's values were rounded to fp16 when they were put into shared memory
-                        k_pairs[b][j / 2] = __floats2half2_rn(current_key[element], current_key[element + 1]);
-                        v_pairs[b][j / 2] = __floats2half2_rn(current_value[element], current_value[element + 1]);
-                    } else {
-                        k_pairs[b][j / 2] = *reinterpret_cast<const __half2 *>(key + element);
-                        v_pairs[b][j / 2] = *reinterpret_cast<const __half2 *>(value + element);
-                    }
+                for (int i = 0; i < E4; ++i) {
+                    const uint32_t at = first_element + 4 * ((uint32_t)i < e4 ? i : 0);
+                    k[b][i] = *reinterpret_cast<const float4 *>(current_key + at);
+                    v[b][i] = *reinterpret_cast<const float4 *>(current_value + at);
                 }
-            } else if (current) {
+            } else if constexpr (kHalf) {
 #pragma unroll
-                for (int j = 0; j < PER; ++j) {
-                    k[b][j] = (uint32_t)j < per_lane ? current_key[lane + 32 * j] : 0.0f;
-                    v[b][j] = (uint32_t)j < per_lane ? current_value[lane + 32 * j] : 0.0f;
+                for (int i = 0; i < (E4 + 1) / 2; ++i) {
+                    const uint32_t at = 8 * ((uint32_t)(2 * i) < e4 ? i : 0);  // unconditional loads; unused pieces are zeroed below
+                    k_raw[b][i] = *reinterpret_cast<const uint4 *>(keys + row + at);
+                    v_raw[b][i] = *reinterpret_cast<const uint4 *>(values + row + at);
                 }
             } else {
 #pragma unroll
-                for (int j = 0; j < PER; ++j) {
-                    k[b][j] = (uint32_t)j < per_lane ? key[lane + 32 * j] : 0.0f;
-                    v[b][j] = (uint32_t)j < per_lane ? value[lane + 32 * j] : 0.0f;
+                for (int i = 0; i < E4; ++i) {
+                    const uint32_t at = 4 * ((uint32_t)i < e4 ? i : 0);
+                    k[b][i] = *reinterpret_cast<const float4 *>(keys + row + at);
+                    v[b][i] = *reinterpret_cast<const float4 *>(values + row + at);
                 }
             }
         }
-        if constexpr (sizeof(KV) == 2) {
+        if constexpr (kHalf) {
 #pragma unroll
             for (int b = 0; b < BATCH; ++b) {
+                if (!(current_key && p0 + stride * b == position)) {
 #pragma unroll
-                for (int j = 0; j < PER; j += 2) {
-                    const bool used = (uint32_t)j < per_lane;
-                    const float2 kk = __half22float2(k_pairs[b][j / 2]), vv = __half22float2(v_pairs[b][j / 2]);
-                    k[b][j] = used ? kk.x : 0.0f;
-                    k[b][j + 1] = used ? kk.y : 0.0f;
-                    v[b][j] = used ? vv.x : 0.0f;
-                    v[b][j + 1] = used ? vv.y : 0.0f;
+                    for (int i = 0; i < (E4 + 1) / 2; ++i) {
+                        const __half2 *kh = reinterpret_cast<const __half2 *>(&k_raw[b][i]), *vh = reinterpret_cast<const __half2 *>(&v_raw[b][i]);
+                        const float2 k0 = __half22float2(kh[0]), k1 = __half22float2(kh[1]), k2 = __half22float2(kh[2]), k3 = __half22float2(kh[3]);
+                        const float2 v0 = __half22float2(vh[0]), v1 = __half22float2(vh[1]), v2 = __half22float2(vh[2]), v3 = __half22float2(vh[3]);
+                        k[b][2 * i] = make_float4(k0.x, k0.y, k1.x, k1.y);
+                        v[b][2 * i] = make_float4(v0.x, v0.y, v1.x, v1.y);
+                        if (2 * i + 1 < E4) {
+                            k[b][2 * i + 1] = make_float4(k2.x, k2.y, k3.x, k3.y);
+                            v[b][2 * i + 1] = make_float4(v2.x, v2.y, v3.x, v3.y);
+                        }
+                    }
                 }
             }
         }
-        float dots[BATCH];
+        float scores[BATCH], batch_max = running_max;
 #pragma unroll
         for (int b = 0; b < BATCH; ++b) {
             float dot = 0.0f;
 #pragma unroll
-            for (int j = 0; j < PER; ++j) {
-                if ((uint32_t)j < per_lane) {
-                    dot = fmaf(qv[j], k[b][j], dot);
+            for (int i = 0; i < E4; ++i) {
+                if ((uint32_t)i < e4) {
+                    dot = fmaf(q[i].x, k[b][i].x, dot);
+                    dot = fmaf(q[i].y, k[b][i].y, dot);
+                    dot = fmaf(q[i].z, k[b][i].z, dot);
+                    dot = fmaf(q[i].w, k[b][i].w, dot);
                 }
             }
-            for (int offset = 16; offset > 0; offset >>= 1) {
-                dot += __shfl_xor_sync(kFull, dot, offset);
-            }
-            dots[b] = dot;
-        }
-        // One softmax update per batch: the batch's maximum first, then one rescale of what has been accumulated and the
-        // batch's weights side by side (a position-at-a-time update is a chain of two exponentials per position that
-        // nothing else can overlap with; far into the context that chain, not the loads, set the pace).
-        float batch_max = running_max, scores[BATCH];
-#pragma unroll
-        for (int b = 0; b < BATCH; ++b) {
-            scores[b] = p0 + kAttentionWarps * b <= position ? dots[b] * scale : -INFINITY;
+            dot += __shfl_xor_sync(kFull, dot, 1);
+            dot += __shfl_xor_sync(kFull, dot, 2);
+            dot += __shfl_xor_sync(kFull, dot, 4);
+            scores[b] = p0 + stride * b <= position ? dot * scale : -INFINITY;
             batch_max = fmaxf(batch_max, scores[b]);
         }
-        // (position p0 is live, so batch_max is finite; exp(-inf) = 0 covers the first batch and the dead positions)
-        const float rescale = expf(running_max - batch_max);
+        // (a stream with no live position yet has running_max = batch_max = -inf: nothing to rescale, all weights zero;
+        // exp(-inf) = 0 covers the first live batch and the dead positions of a live one)
+        const float rescale = running_max == batch_max ? 1.0f : expf(running_max - batch_max);
         float weights[BATCH], total = 0.0f;
 #pragma unroll
         for (int b = 0; b < BATCH; ++b) {
-            weights[b] = expf(scores[b] - batch_max);
+            weights[b] = scores[b] == -INFINITY ? 0.0f : expf(scores[b] - batch_max);
             total += weights[b];
         }
 #pragma unroll
-        for (int j = 0; j < PER; ++j) {
-            if ((uint32_t)j < per_lane) {
-                float a = acc[j] * rescale;
+        for (int i = 0; i < E4; ++i) {
+            if ((uint32_t)i < e4) {
+                float4 a = make_float4(acc[i].x * rescale, acc[i].y * rescale, acc[i].z * rescale, acc[i].w * rescale);
 #pragma unroll
                 for (int b = 0; b < BATCH; ++b) {
-                    a = fmaf(weights[b], v[b][j], a);
+                    a.x = fmaf(weights[b], v[b][i].x, a.x);
+                    a.y = fmaf(weights[b], v[b][i].y, a.y);
+                    a.z = fmaf(weights[b], v[b][i].z, a.z);
+                    a.w = fmaf(weights[b], v[b][i].w, a.w);
                 }
-                acc[j] = a;
+                acc[i] = a;
             }
         }
         running_sum = running_sum * rescale + total;
         running_max = batch_max;
     }
+    // the warp's four streams into one (a stream without positions has maximum -inf and weight sum 0)
+#pragma unroll
+    for (int offset = 8; offset <= 16; offset <<= 1) {
+        const float other_max = __shfl_xor_sync(kFull, running_max, offset), other_sum = __shfl_xor_sync(kFull, running_sum, offset);
+        const float joint = fmaxf(running_max, other_max);
+        const float mine = running_max == -INFINITY ? 0.0f : expf(running_max - joint), theirs = other_max == -INFINITY ? 0.0f : expf(other_max - joint);
+#pragma unroll
+        for (int i = 0; i < E4; ++i) {
+            const float ox = __shfl_xor_sync(kFull, acc[i].x, offset), oy = __shfl_xor_sync(kFull, acc[i].y, offset);
+            const float oz = __shfl_xor_sync(kFull, acc[i].z, offset), ow = __shfl_xor_sync(kFull, acc[i].w, offset);
+            // (lane and partner add the same two products, each its own first: the sums are equal)
+            acc[i] = make_float4(acc[i].x * mine + ox * theirs, acc[i].y * mine + oy * theirs, acc[i].z * mine + oz * theirs, acc[i].w * mine + ow * theirs);
+        }
+        running_sum = running_sum * mine + other_sum * theirs;
+        running_max = joint;
+    }
+    if (group == 0) {
+#pragma unroll
+        for (int i = 0; i < E4; ++i) {
+            if ((uint32_t)i < e4) {
+                *reinterpret_cast<float4 *>(merged_row + first_element + 4 * i) = acc[i];
+            }
+        }
+    }
+    if (lane == 0) {
+        merged_row[256] = running_max;
+        merged_row[257] = running_sum;
+    }
 }
-// Heads of up to 128 values take four positions at a time, larger heads two (the loaded keys and values live in registers).
+
+// Heads of up to 32 / 64 / 128 / 256 values: the wider the head, the fewer positions a stream keeps in flight (the loaded
+// keys and values live in registers).
 template <class KV>
-__device__ __forceinline__ void attend_head(const float *qv, uint32_t per_lane, uint32_t lane, int first, int position, uint32_t head_dim,
-                                            float scale, const KV *keys, const KV *values, const float *current_key,
-                                            const float *current_value, float *acc, float &running_max, float &running_sum)
+__device__ __forceinline__ void attend_head(const float *query, uint32_t lane, uint32_t warp, int position, uint32_t head_dim, float scale,
+                                            const KV *keys, const KV *values, const float *current_key, const float *current_value,
+                                            float *merged_row)
 {
-    // (an FP16 cache's loads are half as wide: twice the positions in flight)
-    constexpr int kDeeper = sizeof(KV) == 2 ? 2 : 1;
-    if (per_lane <= 4) {
-        attend_positions<4, 4 * kDeeper>(qv, per_lane, lane, first, position, head_dim, scale, keys, values, current_key, current_value, acc, running_max,
-                                         running_sum);
+    if (head_dim <= 32) {
+        attend_streams<KV, 1, 4>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row);
+    } else if (head_dim <= 64) {
+        attend_streams<KV, 2, 4>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row);
+    } else if (head_dim <= 128) {
+        attend_streams<KV, 4, 2>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row);
     } else {
-        attend_positions<8, 2 * kDeeper>(qv, per_lane, lane, first, position, head_dim, scale, keys, values, current_key, current_value, acc, running_max,
-                                         running_sum);
+        attend_streams<KV, 8, 1>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row);
     }
 }
 
@@ -766,27 +807,7 @@ __device__ __noinline__ void attention_local(const Op *op, const Params &P, Shar
     }
     consumer_sync();
     if (warp < (uint32_t)kAttentionWarps) {
-        constexpr int kPerLane = 8;
-        const uint32_t per_lane = head_dim / 32;
-        float qv[kPerLane], acc[kPerLane];
-#pragma unroll
-        for (int j = 0; j < kPerLane; ++j) {
-            qv[j] = (uint32_t)j < per_lane ? sh.query[lane + 32 * j] : 0.0f;
-            acc[j] = 0.0f;
-        }
-        float running_max = -INFINITY, running_sum = 0.0f;
-        attend_head(qv, per_lane, lane, (int)warp, token.position, head_dim, P.attention_scale, P.keys + base, P.values + base, sh.key, sh.value,
-                    acc, running_max, running_sum);
-#pragma unroll
-        for (int j = 0; j < kPerLane; ++j) {
-            if ((uint32_t)j < per_lane) {
-                sh.merged[warp][lane + 32 * j] = acc[j];
-            }
-        }
-        if (lane == 0) {
-            sh.merged[warp][256] = running_max;
-            sh.merged[warp][257] = running_sum;
-        }
+        attend_head(sh.query, lane, warp, token.position, head_dim, P.attention_scale, P.keys + base, P.values + base, sh.key, sh.value, sh.merged[warp]);
     }
     consumer_sync();
     if (threadIdx.x < head_dim) {

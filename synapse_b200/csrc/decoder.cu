@@ -180,14 +180,13 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
                  uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t layer, uint32_t layers, uint32_t context, float scale,
                  int8_t *__restrict__ codes, float *__restrict__ scales, int16_t *__restrict__ sums)
 {
-    constexpr int kPerLane = 8;  // head_dim / 32, at most
-    __shared__ float merged[prog::kAttentionWarps][256 + 2];
-    __shared__ float rotated_query[ROTATE ? 256 : 1], current_key[ROTATE ? 256 : 1], current_value[ROTATE ? 256 : 1];
+    __shared__ __align__(16) float merged[prog::kAttentionWarps][256 + 4];  // a warp's unnormalised sum, [256] its maximum, [257] its weight sum
+    __shared__ __align__(16) float rotated_query[ROTATE ? 256 : 4], current_key[ROTATE ? 256 : 4], current_value[ROTATE ? 256 : 4];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t t = blockIdx.y, head = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const BatchToken token = tokens[t];
-    const uint32_t group = heads / kv_heads, kh = head / group, per_lane = head_dim / 32, half = head_dim / 2;
+    const uint32_t group = heads / kv_heads, kh = head / group, half = head_dim / 2;
     const float *query = q + ((uint64_t)t * heads + head) * head_dim;
     const uint64_t base = (((uint64_t)token.slot * layers + layer) * kv_heads + kh) * context * head_dim;
     if (ROTATE) {
@@ -219,25 +218,8 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
         __syncthreads();
         query = rotated_query;
     }
-    float qv[kPerLane], acc[kPerLane];
-#pragma unroll
-    for (int j = 0; j < kPerLane; ++j) {
-        qv[j] = (uint32_t)j < per_lane ? query[prog::head_element<KV>(lane, j)] : 0.0f;
-        acc[j] = 0.0f;
-    }
-    float running_max = -INFINITY, running_sum = 0.0f;
-    prog::attend_head(qv, per_lane, lane, (int)warp, token.position, head_dim, scale, (const KV *)keys + base, (const KV *)values + base, ROTATE ? current_key : nullptr,
-                      ROTATE ? current_value : nullptr, acc, running_max, running_sum);
-#pragma unroll
-    for (int j = 0; j < kPerLane; ++j) {
-        if ((uint32_t)j < per_lane) {
-            merged[warp][prog::head_element<KV>(lane, j)] = acc[j];
-        }
-    }
-    if (lane == 0) {
-        merged[warp][256] = running_max;
-        merged[warp][257] = running_sum;
-    }
+    prog::attend_head(query, lane, warp, token.position, head_dim, scale, (const KV *)keys + base, (const KV *)values + base, ROTATE ? current_key : nullptr,
+                      ROTATE ? current_value : nullptr, merged[warp]);
     __syncthreads();
     float total_max = -INFINITY;
     for (int w = 0; w < prog::kAttentionWarps; ++w) {
