@@ -603,10 +603,11 @@ __device__ __noinline__ void quantize_local(const Op *op, Shared &sh, uint32_t a
 // KV is the cache's element type: float, or __half (DecoderDesc.kv_precision = 1, KvPrecision::F16 of the reference,
 // native/synapse-gpu/src/Features/GpuKernels/decoder.rs:43-58), whose values widen exactly; head_dim is then a multiple
 // of 64, so that a lane's E values are whole 16-byte pieces too.
+// `first_stream` / `streams`: the CTA's share when several CTAs split a head's positions (0 and 4 * kAttentionWarps for one).
 template <class KV, int E4, int BATCH>
 __device__ __forceinline__ void attend_streams(const float *query, uint32_t lane, uint32_t warp, int position, uint32_t head_dim, float scale,
                                                const KV *keys, const KV *values, const float *current_key, const float *current_value,
-                                               float *merged_row)
+                                               float *merged_row, int first_stream, int streams)
 {
     constexpr bool kHalf = sizeof(KV) == 2;
     const uint32_t group = lane >> 3, part = lane & 7;
@@ -619,10 +620,10 @@ __device__ __forceinline__ void attend_streams(const float *query, uint32_t lane
         acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
     float running_max = -INFINITY, running_sum = 0.0f;
-    const int stride = 4 * kAttentionWarps;
+    const int stride = streams;
     // The loop count must be the same for all lanes of the warp (the shuffles below name all of them): it runs over the
     // warp's first stream, and a stream that has run out of positions takes part with weights of zero.
-    for (int base = (int)(4 * warp); base <= position; base += stride * BATCH) {
+    for (int base = first_stream + (int)(4 * warp); base <= position; base += stride * BATCH) {
         const int p0 = base + (int)group;
         float4 k[BATCH][E4], v[BATCH][E4];
         // FP16 cache: the loaded pieces stay as they are until every load of the batch has been issued (a conversion right
@@ -756,16 +757,16 @@ __device__ __forceinline__ void attend_streams(const float *query, uint32_t lane
 template <class KV>
 __device__ __forceinline__ void attend_head(const float *query, uint32_t lane, uint32_t warp, int position, uint32_t head_dim, float scale,
                                             const KV *keys, const KV *values, const float *current_key, const float *current_value,
-                                            float *merged_row)
+                                            float *merged_row, int first_stream = 0, int streams = 4 * kAttentionWarps)
 {
     if (head_dim <= 32) {
-        attend_streams<KV, 1, 4>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row);
+        attend_streams<KV, 1, 4>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row, first_stream, streams);
     } else if (head_dim <= 64) {
-        attend_streams<KV, 2, 4>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row);
+        attend_streams<KV, 2, 4>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row, first_stream, streams);
     } else if (head_dim <= 128) {
-        attend_streams<KV, 4, 2>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row);
+        attend_streams<KV, 4, 2>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row, first_stream, streams);
     } else {
-        attend_streams<KV, 8, 1>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row);
+        attend_streams<KV, 8, 1>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row, first_stream, streams);
     }
 }
 

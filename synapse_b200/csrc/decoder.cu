@@ -173,14 +173,20 @@ __global__ void rope_store_kernel(const BatchToken *__restrict__ tokens, float *
 // tokens keep the separate rotation kernel: a prompt run's later tokens read the cache entries of its earlier ones.
 // KV: the cache's element type. With fp16 the current position is attended to with the values the cache holds for it
 // (rounded), as every later step will see them.
+// Caches of 1024 positions and more: gridDim.z CTAs share a head's positions (CTA z takes the streams z * 48 .. z * 48 + 47
+// of 48 * gridDim.z); each leaves its unnormalised sum, maximum and weight sum in `split_partial`, and the CTA that counts
+// itself in last (an arrival counter per token and head, reset for the next launch; no CTA waits for another) adds them
+// in split order and quantises. One CTA per head otherwise (split_partial null).
 template <bool ROTATE, class KV>
 __global__ void __launch_bounds__(32 * prog::kAttentionWarps)
 attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                  const float *__restrict__ cosines, const float *__restrict__ sines, KV *__restrict__ keys, KV *__restrict__ values,
                  uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t layer, uint32_t layers, uint32_t context, float scale,
-                 int8_t *__restrict__ codes, float *__restrict__ scales, int16_t *__restrict__ sums)
+                 int8_t *__restrict__ codes, float *__restrict__ scales, int16_t *__restrict__ sums, float *__restrict__ split_partial,
+                 uint32_t *__restrict__ split_arrivals)
 {
     __shared__ __align__(16) float merged[prog::kAttentionWarps][256 + 4];  // a warp's unnormalised sum, [256] its maximum, [257] its weight sum
+    __shared__ bool last_split;
     __shared__ __align__(16) float rotated_query[ROTATE ? 256 : 4], current_key[ROTATE ? 256 : 4], current_value[ROTATE ? 256 : 4];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -207,7 +213,7 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
             current_key[i + half] = cache_rounded(keys, second);
             current_value[i] = cache_rounded(values, v0);
             current_value[i + half] = cache_rounded(values, v1);
-            if (head % group == 0) {
+            if (head % group == 0 && blockIdx.z == 0) {
                 const uint64_t at = base + (uint64_t)token.position * head_dim;
                 cache_store(keys + at + i, first);
                 cache_store(keys + at + i + half, second);
@@ -218,8 +224,9 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
         __syncthreads();
         query = rotated_query;
     }
+    const int streams = 4 * prog::kAttentionWarps;
     prog::attend_head(query, lane, warp, token.position, head_dim, scale, (const KV *)keys + base, (const KV *)values + base, ROTATE ? current_key : nullptr,
-                      ROTATE ? current_value : nullptr, merged[warp]);
+                      ROTATE ? current_value : nullptr, merged[warp], (int)blockIdx.z * streams, (int)gridDim.z * streams);
     __syncthreads();
     float total_max = -INFINITY;
     for (int w = 0; w < prog::kAttentionWarps; ++w) {
@@ -227,16 +234,74 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
     }
     float total_sum = 0.0f;
     for (int w = 0; w < prog::kAttentionWarps; ++w) {
-        total_sum += merged[w][257] * expf(merged[w][256] - total_max);  // an idle warp has sum 0 and max -inf: exp(-inf) = 0
+        // an idle warp has sum 0 and max -inf: exp(-inf) = 0 (a CTA of a split that has no position at all: every warp is idle)
+        total_sum += merged[w][256] == -INFINITY ? 0.0f : merged[w][257] * expf(merged[w][256] - total_max);
     }
+    if (split_partial) {
+        // this CTA's share: element i unnormalised, then maximum and weight sum
+        const uint32_t splits = gridDim.z, width = head_dim + 4;
+        float *const mine = split_partial + (((uint64_t)t * heads + head) * splits + blockIdx.z) * width;
+        if (threadIdx.x < head_dim) {
+            float value = 0.0f;
+            for (int w = 0; w < prog::kAttentionWarps; ++w) {
+                value += merged[w][256] == -INFINITY ? 0.0f : merged[w][threadIdx.x] * expf(merged[w][256] - total_max);
+            }
+            mine[threadIdx.x] = value;
+        }
+        if (threadIdx.x == 0) {
+            mine[head_dim] = total_max;
+            mine[head_dim + 1] = total_sum;
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const uint32_t before = atomicAdd(split_arrivals + (uint64_t)t * heads + head, 1u);
+            last_split = before + 1 == splits;
+            if (last_split) {
+                split_arrivals[(uint64_t)t * heads + head] = 0;  // for the next launch
+            }
+        }
+        __syncthreads();
+        if (!last_split) {
+            return;
+        }
+        __threadfence();
+        // The last CTA in: the splits' shares in split order, into merged[0] as one "warp" so that the code below serves both forms.
+        const float *const shares = split_partial + ((uint64_t)t * heads + head) * splits * width;
+        float joint = -INFINITY;
+        for (uint32_t z = 0; z < splits; ++z) {
+            joint = fmaxf(joint, __ldcg(shares + z * width + head_dim));
+        }
+        float sum = 0.0f;
+        for (uint32_t z = 0; z < splits; ++z) {
+            const float m = __ldcg(shares + z * width + head_dim);
+            sum += m == -INFINITY ? 0.0f : __ldcg(shares + z * width + head_dim + 1) * expf(m - joint);
+        }
+        if (threadIdx.x < head_dim) {
+            float value = 0.0f;
+            for (uint32_t z = 0; z < splits; ++z) {
+                const float m = __ldcg(shares + z * width + head_dim);
+                value += m == -INFINITY ? 0.0f : __ldcg(shares + z * width + threadIdx.x) * expf(m - joint);
+            }
+            merged[0][threadIdx.x] = value;
+        }
+        __syncthreads();
+        total_max = joint;
+        total_sum = sum;
+    }
+    const bool joined = split_partial != nullptr;  // merged[0] already holds the head's unnormalised sum
     // The head's output is head_dim/32 whole Q8_0 blocks of the attention row: quantise them here (one warp per
     // block, same arithmetic as the activation quantiser) instead of storing FP32 and launching the quantiser.
     const uint32_t hidden = heads * head_dim;
     for (uint32_t block = warp; block < head_dim / 32; block += prog::kAttentionWarps) {
         const uint32_t i = block * 32 + lane;
         float value = 0.0f;
-        for (int w = 0; w < prog::kAttentionWarps; ++w) {
-            value += merged[w][i] * expf(merged[w][256] - total_max);
+        if (joined) {
+            value = merged[0][i];
+        } else {
+            for (int w = 0; w < prog::kAttentionWarps; ++w) {
+                value += merged[w][i] * expf(merged[w][256] - total_max);
+            }
         }
         value = value / total_sum;
         float amax = fabsf(value);
@@ -359,6 +424,10 @@ struct syn_b200_decoder {
     float *hidden = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attention = nullptr, *gate = nullptr, *ff = nullptr, *logits = nullptr;
     void *act_hidden = nullptr, *act_ffn = nullptr;
     float *keys = nullptr, *values = nullptr;
+    // attention of long caches: CTAs per head, their shares and arrival counters (null with one CTA per head)
+    uint32_t attention_splits = 1;
+    float *split_partial = nullptr;
+    uint32_t *split_arrivals = nullptr;
     syn::BatchToken *device_tokens = nullptr, *host_tokens = nullptr;
     int32_t *device_argmax = nullptr, *host_argmax = nullptr;
     float *argmax_value = nullptr;       // per logits row and slice: the slice's best value and its index
@@ -557,18 +626,18 @@ cudaError_t enqueue_step(syn_b200_decoder *d, uint32_t count, uint32_t logits_ro
                 float *const scales = reinterpret_cast<float *>(base + layout.scales);
                 int16_t *const sums = reinterpret_cast<int16_t *>(base + layout.sums);
                 if (count == 1) {
-                    return launch_kernel(attention_kernel<true, KV>, dim3(s.heads, count), dim3(32 * prog::kAttentionWarps), 0, d->stream,
+                    return launch_kernel(attention_kernel<true, KV>, dim3(s.heads, count, d->attention_splits), dim3(32 * prog::kAttentionWarps), 0, d->stream,
                                          (const BatchToken *)d->device_tokens, (const float *)d->q, (const float *)d->k, (const float *)d->v,
                                          (const float *)d->cosines, (const float *)d->sines, cache_keys, cache_values, s.heads, s.kv_heads, s.head_dim, l,
-                                         s.layer_count, s.context, scale, codes, scales, sums);
+                                         s.layer_count, s.context, scale, codes, scales, sums, d->split_partial, d->split_arrivals);
                 }
                 SYN_TRY(launch_kernel(rope_store_kernel<KV>, dim3(s.heads + s.kv_heads, count), dim3(s.head_dim / 2), 0, d->stream,
                                       (const BatchToken *)d->device_tokens, d->q, d->k, (const float *)d->v, (const float *)d->cosines,
                                       (const float *)d->sines, cache_keys, cache_values, s.heads, s.kv_heads, s.head_dim, l, s.layer_count, s.context));
-                return launch_kernel(attention_kernel<false, KV>, dim3(s.heads, count), dim3(32 * prog::kAttentionWarps), 0, d->stream,
+                return launch_kernel(attention_kernel<false, KV>, dim3(s.heads, count, d->attention_splits), dim3(32 * prog::kAttentionWarps), 0, d->stream,
                                      (const BatchToken *)d->device_tokens, (const float *)d->q, (const float *)d->k, (const float *)d->v,
                                      (const float *)d->cosines, (const float *)d->sines, cache_keys, cache_values, s.heads, s.kv_heads, s.head_dim, l,
-                                     s.layer_count, s.context, scale, codes, scales, sums);
+                                     s.layer_count, s.context, scale, codes, scales, sums, d->split_partial, d->split_arrivals);
             };
             if (s.kv_precision == 1) {
                 SYN_TRY(attend(reinterpret_cast<__half *>(d->keys), reinterpret_cast<__half *>(d->values)));
@@ -1181,6 +1250,12 @@ int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_deco
         const uint64_t cache_floats = s.kv_precision == 1 ? (cache + 1) / 2 : cache;
         if (status == SYN_B200_OK) status = device_alloc(d, &d->keys, cache_floats);
         if (status == SYN_B200_OK) status = device_alloc(d, &d->values, cache_floats);
+        // caches of 1024 positions and more: several CTAs per head (4, or 8 from 4096 positions on)
+        d->attention_splits = s.context >= 4096 ? 8 : s.context >= 1024 ? 4 : 1;
+        if (d->attention_splits > 1) {
+            if (status == SYN_B200_OK) status = device_alloc(d, &d->split_partial, T * s.heads * d->attention_splits * (s.head_dim + 4ull));
+            if (status == SYN_B200_OK) status = device_alloc(d, &d->split_arrivals, T * s.heads);
+        }
         if (status == SYN_B200_OK) status = device_alloc(d, &d->device_tokens, T);
         if (status == SYN_B200_OK) status = device_alloc(d, &d->device_argmax, T);
         if (status == SYN_B200_OK) status = device_alloc(d, &d->argmax_value, T * kArgmaxSlices);
@@ -1192,6 +1267,7 @@ int32_t syn_b200_decoder_create(const syn_b200_decoder_desc *desc, syn_b200_deco
         cudaError_t error = cudaMemcpy(d->cosines, s.rope_cosines, (uint64_t)s.context * half * 4, cudaMemcpyHostToDevice);
         if (error == cudaSuccess) error = cudaMemcpy(d->sines, s.rope_sines, (uint64_t)s.context * half * 4, cudaMemcpyHostToDevice);
         if (error == cudaSuccess) error = cudaMemset(d->argmax_arrivals, 0, T * sizeof(uint32_t));
+        if (error == cudaSuccess && d->split_arrivals) error = cudaMemset(d->split_arrivals, 0, T * s.heads * sizeof(uint32_t));
         if (error == cudaSuccess) error = cudaMemset(d->keys, 0, cache_floats * 4);
         if (error == cudaSuccess) error = cudaMemset(d->values, 0, cache_floats * 4);
         if (error == cudaSuccess) error = cudaHostAlloc(reinterpret_cast<void **>(&d->host_tokens), T * sizeof(syn::BatchToken), cudaHostAllocDefault);

@@ -88,6 +88,44 @@ def test_fp16_kv_cache(oracle, types, embedding, output):
     assert sb.library().device_faults() == 0
 
 
+@pytest.mark.parametrize("kv_precision", [0, 1])
+def test_long_cache_splits_a_heads_positions_over_several_ctas(oracle, kv_precision):
+    """Caches of 1024 positions and more give every head several CTAs, whose shares the last one to finish adds in a fixed
+    order. 300 positions into such a cache the logits must follow the oracle's step like anywhere else, single-token steps
+    and a prompt run in chunks of 64 must agree bit for bit, and a second pass over the same positions must reproduce the
+    first (the arrival counters start over)."""
+    image = dec.ModelImage(**dict(TINY, context=1088), matrix_types=dec.Q8_TYPES, embedding_type=synth.Q8_0, output_type=synth.Q8_0, seed=9,
+                           bias=True, step_tokens=64)
+    image.kv_precision = kv_precision
+    length = 300
+    tokens = [(7 * p + 3) % TINY["vocabulary"] for p in range(length)]
+    reference = oracle.Decoder(image.desc(), TINY["vocabulary"])
+    want = [reference.decode(token, position) for position, token in enumerate(tokens)]
+    reference.close()
+    with dec.Decoder(image) as stepwise, dec.Decoder(image) as chunked:
+        singles = [stepwise.decode(token, position) for position, token in enumerate(tokens)]
+        worst = 0.0
+        for position in range(length):
+            span = float(want[position].max() - want[position].min())
+            error = float(np.abs(singles[position] - want[position]).max()) / span
+            worst = max(worst, error)
+            top2 = np.sort(want[position])[-2:]
+            gap = float(top2[1] - top2[0]) / span
+            deficit = float(want[position].max() - want[position][int(np.argmax(singles[position]))]) / span
+            # (within the reference's bound between two executors, OptimizedQwen2Tests.cs:65-68: softmax sums over hundreds
+            # of positions in another order than the oracle's, re-quantised three layers deep in a random-init model)
+            assert error <= 5e-2, (position, error)
+            assert deficit == 0.0 or (gap <= 2 * error and deficit <= 2 * error), (position, error, gap, deficit)
+        print(f"kv_precision {kv_precision}: worst deviation over {length} positions {worst:.2e} of the logits range")
+        for repeat in range(2):
+            for first in range(0, length, 64):
+                run = [(0, tokens[p], p, p - first) for p in range(first, min(first + 64, length))]
+                logits = chunked.forward(run)
+                for row, (_, _, p, _) in enumerate(run):
+                    assert logits[row].tobytes() == singles[p].tobytes(), (repeat, p)
+    assert sb.library().device_faults() == 0
+
+
 def test_batched_steps_match_single_token_steps(oracle):
     """Tokens of two sessions sharing a step get the logits they would get alone (batch invariance,
     OptimizedQwen2Tests.cs:41-54)."""
