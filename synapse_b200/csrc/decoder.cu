@@ -177,8 +177,15 @@ __global__ void rope_store_kernel(const BatchToken *__restrict__ tokens, float *
 // of 48 * gridDim.z); each leaves its unnormalised sum, maximum and weight sum in `split_partial`, and the CTA that counts
 // itself in last (an arrival counter per token and head, reset for the next launch; no CTA waits for another) adds them
 // in split order and quantises. One CTA per head otherwise (split_partial null).
-template <bool ROTATE, class KV>
-__global__ void __launch_bounds__(32 * prog::kAttentionWarps)
+// E4: 16-byte pieces of FP32 per lane the walk is built for (1, 2, 4, 8 for heads of up to 32, 64, 128, 256 values);
+// SPLIT: whether several CTAs share a head. Both are template parameters so that a kernel holds one walk and nothing it
+// does not use: these CTAs live for a few microseconds, and a kernel that carried all four walks and the split code
+// spent a measurable part of that fetching instructions (1.5 us per layer at short contexts).
+// Two of these CTAs must fit an SM's registers (heads of up to 128 values): the kernel is launched as a programmatic
+// dependent of the q | k | v products, and only a CTA that fits beside theirs starts early; at 156 registers per thread
+// it did not, which cost a decode step 1.5 us per layer.
+template <bool ROTATE, class KV, int E4, bool SPLIT>
+__global__ void __launch_bounds__(32 * prog::kAttentionWarps, E4 <= 4 ? 2 : 1)
 attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                  const float *__restrict__ cosines, const float *__restrict__ sines, KV *__restrict__ keys, KV *__restrict__ values,
                  uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t layer, uint32_t layers, uint32_t context, float scale,
@@ -213,7 +220,7 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
             current_key[i + half] = cache_rounded(keys, second);
             current_value[i] = cache_rounded(values, v0);
             current_value[i + half] = cache_rounded(values, v1);
-            if (head % group == 0 && blockIdx.z == 0) {
+            if (head % group == 0 && (!SPLIT || blockIdx.z == 0)) {
                 const uint64_t at = base + (uint64_t)token.position * head_dim;
                 cache_store(keys + at + i, first);
                 cache_store(keys + at + i + half, second);
@@ -224,9 +231,10 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
         __syncthreads();
         query = rotated_query;
     }
-    const int streams = 4 * prog::kAttentionWarps;
-    prog::attend_head(query, lane, warp, token.position, head_dim, scale, (const KV *)keys + base, (const KV *)values + base, ROTATE ? current_key : nullptr,
-                      ROTATE ? current_value : nullptr, merged[warp], (int)blockIdx.z * streams, (int)gridDim.z * streams);
+    constexpr int kStreams = 4 * prog::kAttentionWarps, kBatch = E4 == 1 ? 4 : E4 == 2 ? 2 : 1;  // 32 registers of keys and of values in flight
+    prog::attend_streams<KV, E4, kBatch>(query, lane, warp, token.position, head_dim, scale, (const KV *)keys + base, (const KV *)values + base,
+                                         ROTATE ? current_key : nullptr, ROTATE ? current_value : nullptr, merged[warp],
+                                         SPLIT ? (int)blockIdx.z * kStreams : 0, SPLIT ? (int)gridDim.z * kStreams : kStreams);
     __syncthreads();
     float total_max = -INFINITY;
     for (int w = 0; w < prog::kAttentionWarps; ++w) {
@@ -237,7 +245,7 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
         // an idle warp has sum 0 and max -inf: exp(-inf) = 0 (a CTA of a split that has no position at all: every warp is idle)
         total_sum += merged[w][256] == -INFINITY ? 0.0f : merged[w][257] * expf(merged[w][256] - total_max);
     }
-    if (split_partial) {
+    if constexpr (SPLIT) {
         // this CTA's share: element i unnormalised, then maximum and weight sum
         const uint32_t splits = gridDim.z, width = head_dim + 4;
         float *const mine = split_partial + (((uint64_t)t * heads + head) * splits + blockIdx.z) * width;
@@ -289,7 +297,7 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
         total_max = joint;
         total_sum = sum;
     }
-    const bool joined = split_partial != nullptr;  // merged[0] already holds the head's unnormalised sum
+    constexpr bool joined = SPLIT;  // merged[0] already holds the head's unnormalised sum
     // The head's output is head_dim/32 whole Q8_0 blocks of the attention row: quantise them here (one warp per
     // block, same arithmetic as the activation quantiser) instead of storing FP32 and launching the quantiser.
     const uint32_t hidden = heads * head_dim;
@@ -625,19 +633,28 @@ cudaError_t enqueue_step(syn_b200_decoder *d, uint32_t count, uint32_t logits_ro
                 int8_t *const codes = reinterpret_cast<int8_t *>(base + layout.codes);
                 float *const scales = reinterpret_cast<float *>(base + layout.scales);
                 int16_t *const sums = reinterpret_cast<int16_t *>(base + layout.sums);
-                if (count == 1) {
-                    return launch_kernel(attention_kernel<true, KV>, dim3(s.heads, count, d->attention_splits), dim3(32 * prog::kAttentionWarps), 0, d->stream,
+                auto launch = [&](auto kernel) -> cudaError_t {
+                    return launch_kernel(kernel, dim3(s.heads, count, d->attention_splits), dim3(32 * prog::kAttentionWarps), 0, d->stream,
                                          (const BatchToken *)d->device_tokens, (const float *)d->q, (const float *)d->k, (const float *)d->v,
                                          (const float *)d->cosines, (const float *)d->sines, cache_keys, cache_values, s.heads, s.kv_heads, s.head_dim, l,
                                          s.layer_count, s.context, scale, codes, scales, sums, d->split_partial, d->split_arrivals);
+                };
+                // the kernel built for this head width, step form and number of CTAs per head
+                auto pick = [&](auto rotate, auto split) -> cudaError_t {
+                    constexpr bool kRotate = decltype(rotate)::value, kSplit = decltype(split)::value;
+                    if (s.head_dim <= 32) return launch(attention_kernel<kRotate, KV, 1, kSplit>);
+                    if (s.head_dim <= 64) return launch(attention_kernel<kRotate, KV, 2, kSplit>);
+                    if (s.head_dim <= 128) return launch(attention_kernel<kRotate, KV, 4, kSplit>);
+                    return launch(attention_kernel<kRotate, KV, 8, kSplit>);
+                };
+                const bool split = d->attention_splits > 1;
+                if (count == 1) {
+                    return split ? pick(std::true_type{}, std::true_type{}) : pick(std::true_type{}, std::false_type{});
                 }
                 SYN_TRY(launch_kernel(rope_store_kernel<KV>, dim3(s.heads + s.kv_heads, count), dim3(s.head_dim / 2), 0, d->stream,
                                       (const BatchToken *)d->device_tokens, d->q, d->k, (const float *)d->v, (const float *)d->cosines,
                                       (const float *)d->sines, cache_keys, cache_values, s.heads, s.kv_heads, s.head_dim, l, s.layer_count, s.context));
-                return launch_kernel(attention_kernel<false, KV>, dim3(s.heads, count, d->attention_splits), dim3(32 * prog::kAttentionWarps), 0, d->stream,
-                                     (const BatchToken *)d->device_tokens, (const float *)d->q, (const float *)d->k, (const float *)d->v,
-                                     (const float *)d->cosines, (const float *)d->sines, cache_keys, cache_values, s.heads, s.kv_heads, s.head_dim, l,
-                                     s.layer_count, s.context, scale, codes, scales, sums, d->split_partial, d->split_arrivals);
+                return split ? pick(std::false_type{}, std::true_type{}) : pick(std::false_type{}, std::false_type{});
             };
             if (s.kv_precision == 1) {
                 SYN_TRY(attend(reinterpret_cast<__half *>(d->keys), reinterpret_cast<__half *>(d->values)));
