@@ -722,27 +722,48 @@ __device__ __forceinline__ void attend_streams(const float *query, uint32_t lane
         running_sum = running_sum * rescale + total;
         running_max = batch_max;
     }
-    // the warp's four streams into one (a stream without positions has maximum -inf and weight sum 0)
+    if (first_stream + (int)(4 * warp) > position) {  // (same for all lanes) the warp had no position at all
+        if (lane == 0) {
+            merged_row[256] = -INFINITY;
+            merged_row[257] = 0.0f;
+        }
+        return;
+    }
+    // The warp's four streams into one (a stream without positions has maximum -inf and weight sum 0). Each step halves
+    // what a lane carries on: of the elements it still holds it keeps one half, hands the other half to its partner and
+    // takes the partner's share of the half it keeps, so that the four lanes of a part end with a quarter of its elements each.
+    float *const a = reinterpret_cast<float *>(acc);
+    uint32_t kept = 0;  // first element (of the part's 4 * E4) this lane still holds
 #pragma unroll
-    for (int offset = 8; offset <= 16; offset <<= 1) {
+    for (int step = 0; step < 2; ++step) {
+        const uint32_t offset = 8u << step;
+        const int count = (4 * E4) >> (step + 1);  // elements kept
+        const bool upper = lane & offset;
         const float other_max = __shfl_xor_sync(kFull, running_max, offset), other_sum = __shfl_xor_sync(kFull, running_sum, offset);
         const float joint = fmaxf(running_max, other_max);
         const float mine = running_max == -INFINITY ? 0.0f : expf(running_max - joint), theirs = other_max == -INFINITY ? 0.0f : expf(other_max - joint);
 #pragma unroll
-        for (int i = 0; i < E4; ++i) {
-            const float ox = __shfl_xor_sync(kFull, acc[i].x, offset), oy = __shfl_xor_sync(kFull, acc[i].y, offset);
-            const float oz = __shfl_xor_sync(kFull, acc[i].z, offset), ow = __shfl_xor_sync(kFull, acc[i].w, offset);
-            // (lane and partner add the same two products, each its own first: the sums are equal)
-            acc[i] = make_float4(acc[i].x * mine + ox * theirs, acc[i].y * mine + oy * theirs, acc[i].z * mine + oz * theirs, acc[i].w * mine + ow * theirs);
+        for (int j = 0; j < count; ++j) {
+            const float keep = upper ? a[count + j] : a[j], give = upper ? a[j] : a[count + j];
+            const float taken = __shfl_xor_sync(kFull, give, offset);
+            a[j] = __fmaf_rn(keep, mine, __fmul_rn(taken, theirs));
         }
-        running_sum = running_sum * mine + other_sum * theirs;
+        kept += upper ? count : 0;
+        running_sum = __fmaf_rn(running_sum, mine, __fmul_rn(other_sum, theirs));
         running_max = joint;
     }
-    if (group == 0) {
+    if constexpr (E4 % 4 == 0) {
 #pragma unroll
-        for (int i = 0; i < E4; ++i) {
-            if ((uint32_t)i < e4) {
-                *reinterpret_cast<float4 *>(merged_row + first_element + 4 * i) = acc[i];
+        for (int j = 0; j < E4; j += 4) {
+            if (kept + j < 4 * e4) {
+                *reinterpret_cast<float4 *>(merged_row + first_element + kept + j) = make_float4(a[j], a[j + 1], a[j + 2], a[j + 3]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < E4; ++j) {
+            if (kept + j < 4 * e4) {
+                merged_row[first_element + kept + j] = a[j];
             }
         }
     }
@@ -762,9 +783,9 @@ __device__ __forceinline__ void attend_head(const float *query, uint32_t lane, u
     if (head_dim <= 32) {
         attend_streams<KV, 1, 4>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row, first_stream, streams);
     } else if (head_dim <= 64) {
-        attend_streams<KV, 2, 4>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row, first_stream, streams);
+        attend_streams<KV, 2, 2>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row, first_stream, streams);
     } else if (head_dim <= 128) {
-        attend_streams<KV, 4, 2>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row, first_stream, streams);
+        attend_streams<KV, 4, 1>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row, first_stream, streams);
     } else {
         attend_streams<KV, 8, 1>(query, lane, warp, position, head_dim, scale, keys, values, current_key, current_value, merged_row, first_stream, streams);
     }
@@ -818,11 +839,11 @@ __device__ __noinline__ void attention_local(const Op *op, const Params &P, Shar
         }
         float total_sum = 0.0f;
         for (int w = 0; w < kAttentionWarps; ++w) {
-            total_sum += sh.merged[w][257] * expf(sh.merged[w][256] - total_max);
+            total_sum += sh.merged[w][256] == -INFINITY ? 0.0f : sh.merged[w][257] * expf(sh.merged[w][256] - total_max);
         }
         float value = 0.0f;
         for (int w = 0; w < kAttentionWarps; ++w) {
-            value += sh.merged[w][threadIdx.x] * expf(sh.merged[w][256] - total_max);
+            value += sh.merged[w][256] == -INFINITY ? 0.0f : sh.merged[w][threadIdx.x] * expf(sh.merged[w][256] - total_max);  // (an idle warp leaves its row unwritten)
         }
         P.attention[(uint64_t)head * head_dim + threadIdx.x] = value / total_sum;
     }

@@ -308,7 +308,7 @@ attention_kernel(const BatchToken *__restrict__ tokens, const float *__restrict_
             value = merged[0][i];
         } else {
             for (int w = 0; w < prog::kAttentionWarps; ++w) {
-                value += merged[w][i] * expf(merged[w][256] - total_max);
+                value += merged[w][256] == -INFINITY ? 0.0f : merged[w][i] * expf(merged[w][256] - total_max);  // (an idle warp leaves its row unwritten)
             }
         }
         value = value / total_sum;
