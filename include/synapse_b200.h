@@ -347,7 +347,9 @@ SYN_B200_API int32_t syn_b200_matvec_ex_dev(const syn_b200_matrix *matrix, uint6
                                             uint64_t out_stride, uint32_t mode, const syn_b200_epilogue *epilogue,
                                             void *scratch, uint64_t scratch_bytes, void *stream);
 
-/* Bytes of device scratch syn_b200_gemm_dev needs for `tokens` x `columns` activations (16-bit operands). */
+/* Bytes of device scratch syn_b200_gemm_dev needs for `tokens` x `columns` activations: the 16-bit operand tiles plus a
+ * fixed 21 MB in which products with fewer tiles than half the SMs (few weight rows, few tokens) leave the shares of the
+ * CTAs a tile's k range is dealt to; the shares are added in a fixed order, so results do not depend on timing. */
 SYN_B200_API uint64_t syn_b200_gemm_scratch_bytes(uint64_t tokens, uint64_t columns);
 
 /* Tensor-core product with device buffers. */

@@ -130,8 +130,15 @@ __device__ __forceinline__ uint32_t swizzled(uint32_t r, uint32_t c) { return r 
 // ------------------------------------------------------------------------------------------------------
 
 __global__ void convert_activations_kernel(const float *__restrict__ x, uint64_t tokens, uint64_t in_stride, uint32_t k_tiles,
-                                           uint32_t token_tiles, uint8_t *__restrict__ tiles, uint8_t *__restrict__ low_tiles)
+                                           uint32_t token_tiles, uint8_t *__restrict__ tiles, uint8_t *__restrict__ low_tiles,
+                                           uint32_t *__restrict__ arrivals, uint32_t arrival_words)
 {
+    // (the product that follows counts the CTAs of a tile that have finished their part of k: zero before it starts)
+    if (blockIdx.x == 0) {
+        for (uint32_t i = threadIdx.x; i < arrival_words; i += blockDim.x) {
+            arrivals[i] = 0;
+        }
+    }
     // `low_tiles` (null for plain fp16 operands) receives fp16(x - fp16(x)): with it an activation carries 22 bits.
     const uint64_t chunks = (uint64_t)token_tiles * k_tiles * kTileTokens * 8;
     for (uint64_t index = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; index < chunks; index += (uint64_t)gridDim.x * blockDim.x) {
@@ -451,6 +458,12 @@ struct GemmArgs {
     float *y;
     uint64_t out_stride;
     uint32_t *fault;
+    // Products with fewer tiles than half the SMs: the k steps of a tile are dealt to `k_parts` CTAs (`k_per_part` steps
+    // each); every CTA leaves its share in `partials`, and the CTA that counts itself in last (`arrivals`, one word per
+    // tile, zero before the launch) adds the shares in part order and stores the tile. k_parts = 1: none of that.
+    uint32_t k_parts, k_per_part;
+    float *partials;
+    uint32_t *arrivals;
 };
 
 __device__ __forceinline__ DequantQ4K::Row DequantQ4K::row_of(const GemmArgs &a, uint64_t row) { return Row{a.weights + row * a.row_bytes}; }
@@ -490,6 +503,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
     uint8_t *stages = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(shared_raw) + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) uint64_t barriers[2 * kMaxStages + 4];  // full[s], empty[s], acc_full[2], acc_empty[2]
     __shared__ uint32_t tmem_slot;
+    __shared__ uint32_t last_part;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(&barriers[0]), empty0 = smem_u32(&barriers[kMaxStages]);
     const uint32_t acc_full0 = smem_u32(&barriers[2 * kMaxStages]), acc_empty0 = smem_u32(&barriers[2 * kMaxStages + 2]);
@@ -513,16 +527,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
     const uint32_t token_groups = (a.token_tiles + TT - 1) / TT;  // CTA tiles along the tokens
-    const uint64_t tiles = (uint64_t)a.row_tiles * token_groups;
+    const uint32_t tiles = a.row_tiles * token_groups;
+    const uint32_t items = tiles * a.k_parts;  // item = part * tiles + tile: k steps [part * k_per_part, + k_per_part) of the tile
+    auto first_step = [&](uint32_t item) { return (item / tiles) * a.k_per_part; };
+    auto end_step = [&](uint32_t item) { return min(a.k_tiles, (item / tiles + 1) * a.k_per_part); };
 
     if (warp == kLoaderWarp) {
         // ---- loader: the activation tile of every (tile, k step) --------------------------------------
         if (lane == 0) {
             uint32_t s = 0, round = 0;
-            for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+            for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+                const uint32_t tile = item % tiles;
                 const uint64_t tt0 = (tile / a.row_tiles) * TT;
                 const uint32_t live = min((uint32_t)TT, a.token_tiles - (uint32_t)tt0);  // token tiles that exist
-                for (uint32_t kt = 0; kt < a.k_tiles; ++kt) {
+                for (uint32_t kt = first_step(item), k_end = end_step(item); kt < k_end; ++kt) {
                     if (round > 0) {
                         mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.fault);
                     }
@@ -546,15 +564,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
         // ---- MMA issuer -----------------------------------------------------------------------------------
         if (lane == 0) {
             uint32_t s = 0, phase = 0, local = 0;
-            for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+            for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++local) {
+                const uint32_t tile = item % tiles;
                 const uint32_t acc = local % kBuffers, use = local / kBuffers;
                 const uint32_t live = min((uint32_t)TT, a.token_tiles - (uint32_t)((tile / a.row_tiles) * TT));
+                const uint32_t k_begin = first_step(item), k_end = end_step(item);
                 if (use >= 1) {
                     mbar_wait(acc_empty0 + 8 * acc, (use - 1) & 1, a.fault);
                 }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * kMaxTileRows;  // token tile i of a TT = 2 tile sits at + i * 256 columns
-                for (uint32_t kt = 0; kt < a.k_tiles; ++kt) {
+                for (uint32_t kt = k_begin; kt < k_end; ++kt) {
                     mbar_wait(full0 + 8 * s, phase, a.fault);
                     tc_fence_after();
                     const uint32_t stage = smem_u32(stages + s * kStageBytes);
@@ -563,7 +583,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                         const uint64_t a_high = smem_desc(stage), a_low = smem_desc(stage + kTileABytes), b_low = smem_desc(stage + kTileBOffset + kTileABytes);
 #pragma unroll
                         for (uint32_t k = 0; k < kTileK / 16; ++k) {
-                            umma_f16(tmem_d, a_high + 2 * k, desc_b + 2 * k, instr_desc(N), (kt | k) != 0 ? 1u : 0u);
+                            umma_f16(tmem_d, a_high + 2 * k, desc_b + 2 * k, instr_desc(N), (kt != k_begin || k != 0) ? 1u : 0u);
                             umma_f16(tmem_d, a_low + 2 * k, desc_b + 2 * k, instr_desc(N), 1u);
                             umma_f16(tmem_d, a_high + 2 * k, b_low + 2 * k, instr_desc(N), 1u);
                         }
@@ -575,7 +595,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
 #pragma unroll
                             for (uint32_t k = 0; k < kTileK / 16; ++k) {
                                 // 16 fp16 = 32 bytes further along the swizzled row: +2 in the descriptor's 16-byte units
-                                umma_f16(tmem_d + i * kMaxTileRows, desc_a + 2 * k, desc_b + 2 * k, instr_desc(N), (kt | k) != 0 ? 1u : 0u);
+                                umma_f16(tmem_d + i * kMaxTileRows, desc_a + 2 * k, desc_b + 2 * k, instr_desc(N), (kt != k_begin || k != 0) ? 1u : 0u);
                             }
                         }
                     }
@@ -597,24 +617,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
         constexpr uint32_t kParts = 256 / kTileRows;               // threads per row
         constexpr int kAhead = Dequant::kAhead;                    // k steps whose raw blocks are in flight
         uint32_t s = 0, round = 0;
-        const uint32_t my_tiles = tiles > blockIdx.x ? (uint32_t)((tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
-        const uint64_t steps = (uint64_t)my_tiles * a.k_tiles;
+        uint32_t steps = 0;  // k steps of all of this CTA's items
+        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+            steps += end_step(item) - first_step(item);
+        }
         // The raw blocks of the next kAhead k steps (across tile boundaries) are fetched before the current ones are
         // expanded: with one token tile a k step is shorter than an L2 round trip, and one step of lookahead left the
         // dequantisers waiting for memory on every step.
         typename Dequant::Raw ahead[kAhead];
-        uint64_t fetch_tile = blockIdx.x;
-        uint32_t fetch_kt = 0;
-        uint64_t fetched = 0;
+        uint32_t fetch_item = blockIdx.x;
+        uint32_t fetch_kt = first_step(fetch_item), fetch_end = end_step(fetch_item);
+        bool fetch_new_row = true;
+        uint32_t fetched = 0;
         typename Dequant::Row fetch_row{};
         auto fetch = [&](typename Dequant::Raw &destination) {
-            if (fetch_kt == 0) {
-                fetch_row = Dequant::row_of(a, min((fetch_tile % a.row_tiles) * kTileRows + r, a.rows - 1));
+            if (fetch_new_row) {
+                fetch_row = Dequant::row_of(a, min((uint64_t)(((fetch_item % tiles) % a.row_tiles) * kTileRows + r), a.rows - 1));
+                fetch_new_row = false;
             }
             Dequant::load(fetch_row, fetch_kt, destination);
-            if (++fetch_kt == a.k_tiles) {
-                fetch_kt = 0;
-                fetch_tile += gridDim.x;
+            if (++fetch_kt == fetch_end) {
+                fetch_item += gridDim.x;
+                fetch_kt = first_step(fetch_item);
+                fetch_end = end_step(fetch_item);
+                fetch_new_row = true;
             }
             ++fetched;
         };
@@ -624,8 +650,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                 fetch(ahead[d]);
             }
         }
-        uint32_t kt = 0;
-        for (uint64_t step0 = 0; step0 < steps; step0 += kAhead) {
+        uint32_t item = blockIdx.x;
+        uint32_t kt = first_step(item), kt_end = end_step(item);
+        for (uint32_t step0 = 0; step0 < steps; step0 += kAhead) {
 #pragma unroll
             for (int d = 0; d < kAhead; ++d) {
                 if (step0 + d >= steps) {
@@ -675,15 +702,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                     s = 0;
                     ++round;
                 }
-                if (++kt == a.k_tiles) {
-                    kt = 0;
+                if (++kt == kt_end) {
+                    item += gridDim.x;
+                    kt = first_step(item);
+                    kt_end = end_step(item);
                 }
             }
         }
     } else {
         // ---- epilogue warps: warp q owns accumulator lanes (tokens) 32q .. 32q+31 ----------------------
         uint32_t local = 0;
-        for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+        const bool whole = a.k_parts == 1;  // the accumulator is the result (else: this CTA's share of it)
+        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++local) {
+            const uint32_t tile = item % tiles;
             const uint32_t acc = local % kBuffers, use = local / kBuffers;
             const uint64_t row0 = (tile % a.row_tiles) * kTileRows;
             const uint64_t tt0 = (tile / a.row_tiles) * TT;
@@ -692,25 +723,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
             tc_fence_after();
             for (uint32_t i = 0; i < live; ++i) {
                 const uint64_t token = (tt0 + i) * kTileTokens + warp * 32 + lane;
-                float *destination = a.y + token * a.out_stride + row0;
+                float *destination = whole ? a.y + token * a.out_stride + row0
+                                           : a.partials + ((item * TT + i) * kTileTokens + warp * 32 + lane) * kTileRows;
 #pragma unroll 1
                 for (uint32_t c = 0; c < kTileRows / 32; ++c) {
                     uint32_t v[32];
                     tmem_load32(tmem_base + ((warp * 32) << 16) + (acc + i) * kMaxTileRows + c * 32, v);
-                    if (token < a.tokens) {
-                        if (row0 + c * 32 + 32 <= a.rows && ((reinterpret_cast<uintptr_t>(destination) & 15) == 0)) {
+                    if (!whole || (token < a.tokens && row0 + c * 32 + 32 <= a.rows && ((reinterpret_cast<uintptr_t>(destination) & 15) == 0))) {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                reinterpret_cast<float4 *>(destination + c * 32)[j] =
-                                    make_float4(__uint_as_float(v[4 * j]) * (1.0f / kPrescale), __uint_as_float(v[4 * j + 1]) * (1.0f / kPrescale),
-                                                __uint_as_float(v[4 * j + 2]) * (1.0f / kPrescale), __uint_as_float(v[4 * j + 3]) * (1.0f / kPrescale));
-                            }
-                        } else {
+                        for (int j = 0; j < 8; ++j) {
+                            reinterpret_cast<float4 *>(destination + c * 32)[j] =
+                                make_float4(__uint_as_float(v[4 * j]) * (1.0f / kPrescale), __uint_as_float(v[4 * j + 1]) * (1.0f / kPrescale),
+                                            __uint_as_float(v[4 * j + 2]) * (1.0f / kPrescale), __uint_as_float(v[4 * j + 3]) * (1.0f / kPrescale));
+                        }
+                    } else if (token < a.tokens) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                if (row0 + c * 32 + j < a.rows) {
-                                    destination[c * 32 + j] = __uint_as_float(v[j]) * (1.0f / kPrescale);
-                                }
+                        for (int j = 0; j < 32; ++j) {
+                            if (row0 + c * 32 + j < a.rows) {
+                                destination[c * 32 + j] = __uint_as_float(v[j]) * (1.0f / kPrescale);
                             }
                         }
                     }
@@ -720,6 +750,47 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(acc_empty0 + 8 * acc);
+            }
+            if (!whole) {
+                // The tile's parts meet through a counter: whoever arrives last adds all shares, part 0 first, and
+                // stores the tile. Nobody waits for anybody.
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 0) {
+                    last_part = atomicAdd(a.arrivals + tile, 1u) + 1 == a.k_parts ? 1u : 0u;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (last_part) {
+                    __threadfence();
+                    constexpr uint32_t kShareFloats = TT * kTileTokens * kTileRows;
+                    const uint32_t quads = live * kTileTokens * kTileRows / 4;
+                    for (uint32_t f = threadIdx.x; f < quads; f += 128) {
+                        float4 sum = __ldcg(reinterpret_cast<const float4 *>(a.partials + tile * kShareFloats) + f);
+                        for (uint32_t part = 1; part < a.k_parts; ++part) {
+                            const float4 share = __ldcg(reinterpret_cast<const float4 *>(a.partials + (part * tiles + tile) * kShareFloats) + f);
+                            sum.x += share.x;
+                            sum.y += share.y;
+                            sum.z += share.z;
+                            sum.w += share.w;
+                        }
+                        const uint32_t column = (4 * f) % kTileRows;
+                        const uint64_t token = tt0 * kTileTokens + (4 * f) / kTileRows;
+                        if (token < a.tokens) {
+                            float *out = a.y + token * a.out_stride + row0 + column;
+                            if (row0 + column + 4 <= a.rows && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+                                *reinterpret_cast<float4 *>(out) = sum;
+                            } else {
+                                const float values[4] = {sum.x, sum.y, sum.z, sum.w};
+                                for (int j = 0; j < 4; ++j) {
+                                    if (row0 + column + j < a.rows) {
+                                        out[j] = values[j];
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // (last_part is written again for the CTA's next item)
             }
         }
     }
@@ -767,11 +838,23 @@ cudaError_t run_gemm(const GemmArgs &a, int n, int tt, uint64_t ctas, cudaStream
 
 }  // namespace
 
-uint64_t gemm_scratch_bytes(uint64_t tokens, uint64_t columns)
+// Scratch of a product whose k steps are dealt to several CTAs: at most kMaxShares shares of a 128-row tile with up to two
+// token tiles (one per CTA, and there are no more CTAs than SMs), then one arrival counter per tile.
+constexpr uint64_t kMaxShares = 160;
+constexpr uint64_t kShareBytes = 2ull * kTileTokens * 128 * sizeof(float);
+constexpr uint64_t kArrivalWords = kMaxShares / 2;
+constexpr uint64_t kPartsBytes = kMaxShares * kShareBytes + 4 * kArrivalWords;
+
+static uint64_t activation_tile_bytes(uint64_t tokens, uint64_t columns)
 {
     const uint64_t token_tiles = (tokens + kTileTokens - 1) / kTileTokens;
     const uint64_t k_tiles = (columns + kTileK - 1) / kTileK;
     return 2 * align_up(token_tiles * k_tiles * kTileABytes, 256);  // room for the low parts of two-part operands
+}
+
+uint64_t gemm_scratch_bytes(uint64_t tokens, uint64_t columns)
+{
+    return activation_tile_bytes(tokens, columns) + kPartsBytes;
 }
 
 int32_t launch_gemm(const syn_b200_matrix *m, const float *x, uint64_t tokens, uint64_t in_stride, float *y, uint64_t out_stride,
@@ -787,9 +870,11 @@ int32_t launch_gemm(const syn_b200_matrix *m, const float *x, uint64_t tokens, u
     if (m->columns % kTileK != 0) {
         return fail(SYN_B200_UNAVAILABLE, "the tensor-core product needs a row length that is a multiple of 64; this matrix has " + std::to_string(m->columns));
     }
-    const uint64_t need = gemm_scratch_bytes(tokens, m->columns);
+    // (a caller that brings the activation tiles' room only gets the product without the split along k)
+    const uint64_t need = activation_tile_bytes(tokens, m->columns);
     if (!scratch || scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255)) {
-        return fail(SYN_B200_INVALID_ARGUMENT, "tensor-core scratch must be 256-byte aligned and hold " + std::to_string(need) + " bytes");
+        return fail(SYN_B200_INVALID_ARGUMENT, "tensor-core scratch must be 256-byte aligned and hold " + std::to_string(need) + " bytes (" +
+                                                   std::to_string(need + kPartsBytes) + " for products that split along k)");
     }
     GemmArgs a{};
     const bool planar = m->layout == Layout::Planar;
@@ -816,6 +901,24 @@ int32_t launch_gemm(const syn_b200_matrix *m, const float *x, uint64_t tokens, u
     a.y = y;
     a.out_stride = out_stride;
     a.fault = fault_word_device();
+    // Fewer tiles than half the SMs (few weight rows, few tokens): deal every tile's k steps to as many CTAs as there are
+    // SMs per tile, no fewer than eight steps each. The shares are added in part order, so the result does not depend on
+    // which CTA finishes when.
+    const uint64_t tiles = (uint64_t)a.row_tiles * token_groups;
+    a.k_parts = 1;
+    a.k_per_part = a.k_tiles;
+    if (n == 128 && 2 * tiles <= sms && sms <= kMaxShares && tiles <= kArrivalWords && scratch_bytes >= need + kPartsBytes) {
+        uint64_t parts = sms / tiles;
+        if (parts > a.k_tiles / 8) {
+            parts = a.k_tiles / 8;
+        }
+        if (parts >= 2) {
+            a.k_per_part = (uint32_t)((a.k_tiles + parts - 1) / parts);
+            a.k_parts = (a.k_tiles + a.k_per_part - 1) / a.k_per_part;  // (no empty parts)
+            a.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(scratch) + need);
+            a.arrivals = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(scratch) + need + kMaxShares * kShareBytes);
+        }
+    }
 
     const uint64_t chunks = (uint64_t)a.token_tiles * a.k_tiles * kTileTokens * 8;
     uint64_t blocks = (chunks + 255) / 256;
@@ -823,13 +926,14 @@ int32_t launch_gemm(const syn_b200_matrix *m, const float *x, uint64_t tokens, u
         blocks = sms * 16;
     }
     convert_activations_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, tokens, in_stride, a.k_tiles, a.token_tiles, static_cast<uint8_t *>(scratch),
-                                                                   split ? static_cast<uint8_t *>(scratch) + need / 2 : nullptr);
+                                                                   split ? static_cast<uint8_t *>(scratch) + need / 2 : nullptr, a.arrivals,
+                                                                   a.k_parts > 1 ? (uint32_t)kArrivalWords : 0u);
     count_launch();
     cudaError_t error = cudaGetLastError();
     if (error != cudaSuccess) {
         return cuda_fail(error, "launching the activation conversion");
     }
-    uint64_t ctas = (uint64_t)a.row_tiles * token_groups;
+    uint64_t ctas = tiles * a.k_parts;
     if (ctas > sms) {
         ctas = sms;
     }

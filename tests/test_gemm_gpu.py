@@ -106,3 +106,42 @@ def test_two_part_operands_meet_the_reference_kernel_tolerance(oracle, ggml_type
           f"worst |y - exact| {fine[0]:.3e} against {fine[1]:.3e} with plain fp16 operands")
     assert fine[0] * (20 if columns <= 4096 else 4) < fine[1]
     assert np.all(np.isfinite(y)) and np.all(np.abs(y).sum(axis=1) > 0)
+
+
+K_PART_CASES = [  # type, rows, columns, tokens: fewer tiles than half the SMs, so the k steps of a tile go to several CTAs
+    (sb.Q6_K, 3584, 18944, 128), (sb.Q6_K, 300, 18944, 260), (sb.Q4_K, 512, 3584, 128), (sb.Q4_K, 1000, 8192, 77), (sb.Q8_0, 896, 4864, 260),
+]
+
+
+@pytest.mark.parametrize("ggml_type,rows,columns,tokens", K_PART_CASES)
+@pytest.mark.parametrize("precision", [sb.GEMM_F16, sb.GEMM_F16X2])
+def test_products_split_along_k_add_their_shares_in_a_fixed_order(ggml_type, rows, columns, tokens, precision):
+    """With the full scratch a small product deals each tile's k range to several CTAs; with room for the activation tiles
+    only it runs one CTA per tile. The two differ by the grouping of an FP32 sum and nothing else, and the split product
+    gives the same bits every time (the shares are added in part order by whichever CTA finishes last)."""
+    import torch
+
+    if precision == sb.GEMM_F16X2 and rows * columns > 40_000_000:
+        pytest.skip("the two-part product is covered on the smaller shapes")
+    lib = sb.library()
+    weights = synth.matrix(ggml_type, rows, columns, seed=71)
+    x = torch.from_numpy(synth.activations(tokens, columns, seed=72)).cuda()
+    full = lib.gemm_scratch_bytes(tokens, columns)
+    token_tiles, k_tiles = (tokens + 127) // 128, columns // 64
+    tiles_only = 2 * ((token_tiles * k_tiles * 16384 + 255) // 256 * 256)
+    assert tiles_only < full
+    work = torch.empty(full, dtype=torch.uint8, device="cuda")
+    work.fill_(0xFF)  # the arrival counters are zeroed by the call, not by the caller
+    results = []
+    with sb.QuantizedMatrix(weights, ggml_type, rows, columns) as matrix:
+        for scratch_bytes in (full, full, tiles_only):
+            y = torch.full((tokens, rows), float("nan"), device="cuda")
+            matrix.gemm_device(x.data_ptr(), tokens, columns, y.data_ptr(), rows, work.data_ptr(), scratch_bytes, precision=precision)
+            torch.cuda.synchronize()
+            results.append(y.cpu().numpy())
+        assert lib.device_faults() == 0
+    split, again, whole = results
+    assert np.all(np.isfinite(split)) and np.array_equal(split, again)
+    assert not np.array_equal(split, whole), "the full scratch did not change the summation: the split did not run"
+    span = whole.max(axis=1, keepdims=True) - whole.min(axis=1, keepdims=True)
+    assert np.all(np.abs(split - whole) <= 1e-4 * span)  # (1.3e-5 of the range at K = 18944: FP32 sums of 296 against 5 x 60 steps), f"worst difference {np.max(np.abs(split - whole) / span):.3e} of the output range"
