@@ -232,6 +232,7 @@ __device__ __forceinline__ void split_chunk(const float *w, uint4 &high, uint4 &
 
 struct DequantQ4K {
     static constexpr int kAhead = 3;  // k steps of raw blocks a dequant thread keeps in flight (12 registers each)
+    static constexpr int kStepsPerRaw = 1;
     struct Raw {
         uint4 header, q0, q1;
     };
@@ -294,11 +295,14 @@ struct DequantQ4K {
 // (GgufKQuantBlocks.cs:155-177). value = d * sc[8h + 4g + i/16] * (q - 32).
 template <bool PLANAR>
 struct DequantQ6K {
-    static constexpr int kAhead = 2;  // 26 registers per step
+    static constexpr int kAhead = 2;  // 27 registers per fetch
+    // The two k tiles of a half block (nibble g = 0, 1) are cut from the same 64 + 32 bytes: one fetch serves both steps,
+    // so two fetches in flight are four k steps of lookahead.
+    static constexpr int kStepsPerRaw = 2;
     struct Raw {
         uint4 ql[4], qh[2];
-        uint32_t scales;  // the four int8 scales of this k tile
-        uint32_t d;       // fp16 bits
+        uint2 scales;  // the four int8 scales of k tile g = 0, then those of g = 1
+        uint32_t d;    // fp16 bits
     };
     struct Row {
         const uint8_t *ql, *qh, *sc, *d;  // planar: per-plane row starts; file layout: all inside one block stream
@@ -306,18 +310,18 @@ struct DequantQ6K {
     static __device__ __forceinline__ Row row_of(const GemmArgs &a, uint64_t row);
     static __device__ __forceinline__ void load(const Row &r, uint32_t kt, Raw &raw)
     {
-        const uint32_t sb = kt >> 2, h = (kt >> 1) & 1, g = kt & 1;
+        const uint32_t sb = kt >> 2, h = (kt >> 1) & 1;  // (kt is even: the first step of the pair)
         const uint8_t *ql, *qh, *sc, *d;
         if (PLANAR) {
             ql = r.ql + (uint64_t)sb * 128 + h * 64;
             qh = r.qh + (uint64_t)sb * 64 + h * 32;
-            sc = r.sc + (uint64_t)sb * 16 + h * 8 + g * 4;
+            sc = r.sc + (uint64_t)sb * 16 + h * 8;
             d = r.d + (uint64_t)sb * 2;
         } else {
             const uint8_t *block = r.ql + (uint64_t)sb * 210;
             ql = block + h * 64;
             qh = block + 128 + h * 32;
-            sc = block + 192 + h * 8 + g * 4;
+            sc = block + 192 + h * 8;
             d = block + 208;
         }
 #pragma unroll
@@ -326,7 +330,8 @@ struct DequantQ6K {
         }
         raw.qh[0] = load16<PLANAR>(qh);
         raw.qh[1] = load16<PLANAR>(qh + 16);
-        raw.scales = PLANAR ? __ldg(reinterpret_cast<const uint32_t *>(sc)) : (load_u16(sc) | (load_u16(sc + 2) << 16));
+        raw.scales = PLANAR ? __ldg(reinterpret_cast<const uint2 *>(sc))
+                            : make_uint2(load_u16(sc) | (load_u16(sc + 2) << 16), load_u16(sc + 4) | (load_u16(sc + 6) << 16));
         raw.d = load_u16(d);
     }
     // part 0: tile values 0..31 (chunks 0..3), part 1: values 32..63 (chunks 4..7)
@@ -343,7 +348,7 @@ struct DequantQ6K {
         uint32_t v[16];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const int scale = (int)(signed char)((raw.scales >> (8 * (2 * part + j / 4))) & 0xff);
+            const int scale = (int)(signed char)(((g ? raw.scales.y : raw.scales.x) >> (8 * (2 * part + j / 4))) & 0xff);
             const __half2 a = __float2half2_rn(d * (float)scale);
             const uint32_t nibbles = (g ? (ql[j] >> 4) : ql[j]) & 0x0F0F0F0Fu;
             const uint32_t codes = nibbles | (((qh[j] >> high_shift) & 0x03030303u) << 4);
@@ -367,7 +372,7 @@ struct DequantQ6K {
         const uint32_t high_shift = 4 * g + 2 * part;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-            const int scale = (int)(signed char)((raw.scales >> (8 * (2 * part + i / 16))) & 0xff);
+            const int scale = (int)(signed char)(((g ? raw.scales.y : raw.scales.x) >> (8 * (2 * part + i / 16))) & 0xff);
             const uint32_t byte = (ql[i / 4] >> (8 * (i & 3))) & 0xff;
             const uint32_t nibble = g ? byte >> 4 : byte & 0xF;
             const uint32_t high = (qh[i / 4] >> (8 * (i & 3) + high_shift)) & 3;
@@ -380,6 +385,7 @@ struct DequantQ6K {
 template <bool PLANAR>
 struct DequantQ8 {
     static constexpr int kAhead = 3;
+    static constexpr int kStepsPerRaw = 1;
     struct Raw {
         uint4 codes[4];
         uint32_t d0, d1;  // fp16 bits of the two block scales
@@ -615,11 +621,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
         const uint32_t dq = threadIdx.x - 128;
         const uint32_t r = dq % kTileRows, part = dq / kTileRows;  // part is 0 when N = 256
         constexpr uint32_t kParts = 256 / kTileRows;               // threads per row
-        constexpr int kAhead = Dequant::kAhead;                    // k steps whose raw blocks are in flight
+        // fetches in flight (two-part operands expand to FP32 and have no registers to spare: one fetch of two steps)
+        constexpr int kAhead = SPLIT && Dequant::kStepsPerRaw == 2 ? 1 : Dequant::kAhead;
         uint32_t s = 0, round = 0;
-        uint32_t steps = 0;  // k steps of all of this CTA's items
+        constexpr uint32_t kSpan = Dequant::kStepsPerRaw;  // k steps one fetch serves (an item's first step and its step count are multiples of it)
+        uint32_t fetches = 0;  // over all of this CTA's items
         for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
-            steps += end_step(item) - first_step(item);
+            fetches += (end_step(item) - first_step(item)) / kSpan;
         }
         // The raw blocks of the next kAhead k steps (across tile boundaries) are fetched before the current ones are
         // expanded: with one token tile a k step is shorter than an L2 round trip, and one step of lookahead left the
@@ -636,7 +644,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                 fetch_new_row = false;
             }
             Dequant::load(fetch_row, fetch_kt, destination);
-            if (++fetch_kt == fetch_end) {
+            fetch_kt += kSpan;
+            if (fetch_kt == fetch_end) {
                 fetch_item += gridDim.x;
                 fetch_kt = first_step(fetch_item);
                 fetch_end = end_step(fetch_item);
@@ -646,63 +655,67 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
         };
 #pragma unroll
         for (int d = 0; d < kAhead; ++d) {
-            if (fetched < steps) {
+            if (fetched < fetches) {
                 fetch(ahead[d]);
             }
         }
         uint32_t item = blockIdx.x;
         uint32_t kt = first_step(item), kt_end = end_step(item);
-        for (uint32_t step0 = 0; step0 < steps; step0 += kAhead) {
+        for (uint32_t fetch0 = 0; fetch0 < fetches; fetch0 += kAhead) {
 #pragma unroll
             for (int d = 0; d < kAhead; ++d) {
-                if (step0 + d >= steps) {
+                if (fetch0 + d >= fetches) {
                     break;
                 }
                 const typename Dequant::Raw raw = ahead[d];
-                if (fetched < steps) {
+                if (fetched < fetches) {
                     fetch(ahead[d]);
                 }
-                uint4 v[2][4];
-                if (SPLIT) {
-                    float w[32];
-                    Dequant::expand_f32(raw, kt, part, w);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        split_chunk(w + 8 * c, v[0][c], v[1][c]);
-                    }
-                } else if (kParts == 1) {
-                    Dequant::expand(raw, kt, 0, v[0]);
-                    Dequant::expand(raw, kt, 1, v[1]);
-                } else {
-                    Dequant::expand(raw, kt, part, v[0]);
-                }
-                if (round > 0) {
-                    mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.fault);
-                }
-                uint8_t *tile_b = stages + s * kStageBytes + kTileBOffset;
-#pragma unroll
-                for (uint32_t c = 0; c < 4; ++c) {
+#pragma unroll 1
+                for (uint32_t span = 0; span < kSpan; ++span) {
+                    uint4 v[2][4];
                     if (SPLIT) {
-                        *reinterpret_cast<uint4 *>(tile_b + swizzled(r, 4 * part + c)) = v[0][c];
-                        *reinterpret_cast<uint4 *>(tile_b + kTileABytes + swizzled(r, 4 * part + c)) = v[1][c];
+                        float w[32];
+                        Dequant::expand_f32(raw, kt, part, w);
+    #pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            split_chunk(w + 8 * c, v[0][c], v[1][c]);
+                        }
                     } else if (kParts == 1) {
-                        *reinterpret_cast<uint4 *>(tile_b + swizzled(r, c)) = v[0][c];
-                        *reinterpret_cast<uint4 *>(tile_b + swizzled(r, 4 + c)) = v[1][c];
+                        Dequant::expand(raw, kt, 0, v[0]);
+                        Dequant::expand(raw, kt, 1, v[1]);
                     } else {
-                        *reinterpret_cast<uint4 *>(tile_b + swizzled(r, 4 * part + c)) = v[0][c];
+                        Dequant::expand(raw, kt, part, v[0]);
                     }
+                    if (round > 0) {
+                        mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.fault);
+                    }
+                    uint8_t *tile_b = stages + s * kStageBytes + kTileBOffset;
+    #pragma unroll
+                    for (uint32_t c = 0; c < 4; ++c) {
+                        if (SPLIT) {
+                            *reinterpret_cast<uint4 *>(tile_b + swizzled(r, 4 * part + c)) = v[0][c];
+                            *reinterpret_cast<uint4 *>(tile_b + kTileABytes + swizzled(r, 4 * part + c)) = v[1][c];
+                        } else if (kParts == 1) {
+                            *reinterpret_cast<uint4 *>(tile_b + swizzled(r, c)) = v[0][c];
+                            *reinterpret_cast<uint4 *>(tile_b + swizzled(r, 4 + c)) = v[1][c];
+                        } else {
+                            *reinterpret_cast<uint4 *>(tile_b + swizzled(r, 4 * part + c)) = v[0][c];
+                        }
+                    }
+                    // make the generic-proxy stores visible to the tensor core's (async proxy) reads
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(full0 + 8 * s);
+                    }
+                    if (++s == kStages) {
+                        s = 0;
+                        ++round;
+                    }
+                    ++kt;
                 }
-                // make the generic-proxy stores visible to the tensor core's (async proxy) reads
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(full0 + 8 * s);
-                }
-                if (++s == kStages) {
-                    s = 0;
-                    ++round;
-                }
-                if (++kt == kt_end) {
+                if (kt == kt_end) {
                     item += gridDim.x;
                     kt = first_step(item);
                     kt_end = end_step(item);
@@ -913,7 +926,7 @@ int32_t launch_gemm(const syn_b200_matrix *m, const float *x, uint64_t tokens, u
             parts = a.k_tiles / 8;
         }
         if (parts >= 2) {
-            a.k_per_part = (uint32_t)((a.k_tiles + parts - 1) / parts);
+            a.k_per_part = (uint32_t)((a.k_tiles + parts - 1) / parts + 3) & ~3u;  // whole Q6_K half blocks (pairs of steps share a fetch)
             a.k_parts = (a.k_tiles + a.k_per_part - 1) / a.k_per_part;  // (no empty parts)
             a.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(scratch) + need);
             a.arrivals = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(scratch) + need + kMaxShares * kShareBytes);
