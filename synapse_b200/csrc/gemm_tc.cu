@@ -622,7 +622,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
         const uint32_t r = dq % kTileRows, part = dq / kTileRows;  // part is 0 when N = 256
         constexpr uint32_t kParts = 256 / kTileRows;               // threads per row
         // fetches in flight (two-part operands expand to FP32 and have no registers to spare: one fetch of two steps)
-        constexpr int kAhead = SPLIT && Dequant::kStepsPerRaw == 2 ? 1 : Dequant::kAhead;
+        constexpr int kAhead = (SPLIT || N == 256) && Dequant::kStepsPerRaw == 2 ? 1 : Dequant::kAhead;
         uint32_t s = 0, round = 0;
         constexpr uint32_t kSpan = Dequant::kStepsPerRaw;  // k steps one fetch serves (an item's first step and its step count are multiples of it)
         uint32_t fetches = 0;  // over all of this CTA's items
