@@ -230,6 +230,16 @@ __device__ __forceinline__ void split_chunk(const float *w, uint4 &high, uint4 &
     low = make_uint4(l[0], l[1], l[2], l[3]);
 }
 
+// 128-row tiles give every weight row two dequant threads (`part` 0 and 1), neighbours in a warp. PAIRED loads fetch
+// each byte of the row once between the two -- a load instruction of the warp then touches 16 rows' lines instead of
+// 32, and the L1 pipeline, not DRAM, is what bounds these thread-per-row loads -- and `share` hands the partner the
+// pieces both need (executed by every lane of the warp).
+__device__ __forceinline__ uint4 from_partner(uint4 v)
+{
+    return make_uint4(__shfl_xor_sync(0xffffffffu, v.x, 1), __shfl_xor_sync(0xffffffffu, v.y, 1), __shfl_xor_sync(0xffffffffu, v.z, 1),
+                      __shfl_xor_sync(0xffffffffu, v.w, 1));
+}
+
 struct DequantQ4K {
     static constexpr int kAhead = 3;  // k steps of raw blocks a dequant thread keeps in flight (12 registers each)
     static constexpr int kStepsPerRaw = 1;
@@ -241,15 +251,27 @@ struct DequantQ4K {
     };
     static __device__ __forceinline__ Row row_of(const GemmArgs &a, uint64_t row);
     // k tile `kt` is chunk kt%4 of super-block kt/4.
-    static __device__ __forceinline__ void load(const Row &r, uint32_t kt, Raw &raw)
+    template <bool PAIRED>
+    static __device__ __forceinline__ void load(const Row &r, uint32_t kt, uint32_t part, Raw &raw)
     {
         const uint8_t *block = r.base + (uint64_t)(kt >> 2) * 144;
         raw.header = __ldg(reinterpret_cast<const uint4 *>(block));
-        raw.q0 = __ldg(reinterpret_cast<const uint4 *>(block + 16 + (kt & 3) * 32));
-        raw.q1 = __ldg(reinterpret_cast<const uint4 *>(block + 32 + (kt & 3) * 32));
+        if (PAIRED) {  // both threads expand the same 32 bytes (low and high nibbles): each fetches one half of them
+            raw.q0 = __ldg(reinterpret_cast<const uint4 *>(block + 16 + (kt & 3) * 32 + 16 * part));
+        } else {
+            raw.q0 = __ldg(reinterpret_cast<const uint4 *>(block + 16 + (kt & 3) * 32));
+            raw.q1 = __ldg(reinterpret_cast<const uint4 *>(block + 32 + (kt & 3) * 32));
+        }
+    }
+    static __device__ __forceinline__ void share(Raw &raw, uint32_t part)
+    {
+        const uint4 mine = raw.q0, other = from_partner(raw.q0);
+        raw.q0 = part ? other : mine;
+        raw.q1 = part ? mine : other;
     }
     // Chunks 4*half .. 4*half+3 of the k tile: half 0 = the low nibbles (sub-block 2c), half 1 = the high nibbles
     // (sub-block 2c+1), where c = kt%4.
+    template <bool PAIRED>
     static __device__ __forceinline__ void expand(const Raw &raw, uint32_t kt, uint32_t half, uint4 (&out)[4])
     {
         const float d = __half2float(__ushort_as_half((unsigned short)(raw.header.x & 0xffff))) * kPrescale;
@@ -274,6 +296,7 @@ struct DequantQ4K {
         }
     }
     // The same 32 weights in FP32, exactly as the reference decodes them: (d * sc) * q - dmin * m (GgufKQuantBlocks.cs:99-121).
+    template <bool PAIRED>
     static __device__ __forceinline__ void expand_f32(const Raw &raw, uint32_t kt, uint32_t half, float (&w)[32])
     {
         const float d = __half2float(__ushort_as_half((unsigned short)(raw.header.x & 0xffff)));
@@ -308,7 +331,8 @@ struct DequantQ6K {
         const uint8_t *ql, *qh, *sc, *d;  // planar: per-plane row starts; file layout: all inside one block stream
     };
     static __device__ __forceinline__ Row row_of(const GemmArgs &a, uint64_t row);
-    static __device__ __forceinline__ void load(const Row &r, uint32_t kt, Raw &raw)
+    template <bool PAIRED>
+    static __device__ __forceinline__ void load(const Row &r, uint32_t kt, uint32_t part, Raw &raw)
     {
         const uint32_t sb = kt >> 2, h = (kt >> 1) & 1;  // (kt is even: the first step of the pair)
         const uint8_t *ql, *qh, *sc, *d;
@@ -324,25 +348,37 @@ struct DequantQ6K {
             sc = block + 192 + h * 8;
             d = block + 208;
         }
+        if (PAIRED) {  // ql[0..1]: the thread's own 32 bytes; qh[0]: its half of the 32 bytes both threads need
+            raw.ql[0] = load16<PLANAR>(ql + 32 * part);
+            raw.ql[1] = load16<PLANAR>(ql + 32 * part + 16);
+            raw.qh[0] = load16<PLANAR>(qh + 16 * part);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            raw.ql[i] = load16<PLANAR>(ql + 16 * i);
+            for (int i = 0; i < 4; ++i) {
+                raw.ql[i] = load16<PLANAR>(ql + 16 * i);
+            }
+            raw.qh[0] = load16<PLANAR>(qh);
+            raw.qh[1] = load16<PLANAR>(qh + 16);
         }
-        raw.qh[0] = load16<PLANAR>(qh);
-        raw.qh[1] = load16<PLANAR>(qh + 16);
         raw.scales = PLANAR ? __ldg(reinterpret_cast<const uint2 *>(sc))
                             : make_uint2(load_u16(sc) | (load_u16(sc + 2) << 16), load_u16(sc + 4) | (load_u16(sc + 6) << 16));
         raw.d = load_u16(d);
     }
+    static __device__ __forceinline__ void share(Raw &raw, uint32_t part)
+    {
+        const uint4 mine = raw.qh[0], other = from_partner(raw.qh[0]);
+        raw.qh[0] = part ? other : mine;
+        raw.qh[1] = part ? mine : other;
+    }
     // part 0: tile values 0..31 (chunks 0..3), part 1: values 32..63 (chunks 4..7)
+    template <bool PAIRED>
     static __device__ __forceinline__ void expand(const Raw &raw, uint32_t kt, uint32_t part, uint4 (&out)[4])
     {
         const uint32_t g = kt & 1;
         const float d = __half2float(__ushort_as_half((unsigned short)raw.d)) * kPrescale;
         const __half2 k1056 = __float2half2_rn(1056.0f);  // 1024 from the exponent trick + the code offset 32
-        const uint32_t ql[8] = {part ? raw.ql[2].x : raw.ql[0].x, part ? raw.ql[2].y : raw.ql[0].y, part ? raw.ql[2].z : raw.ql[0].z,
-                                part ? raw.ql[2].w : raw.ql[0].w, part ? raw.ql[3].x : raw.ql[1].x, part ? raw.ql[3].y : raw.ql[1].y,
-                                part ? raw.ql[3].z : raw.ql[1].z, part ? raw.ql[3].w : raw.ql[1].w};
+        const uint4 first = PAIRED || !part ? raw.ql[0] : raw.ql[2], second = PAIRED || !part ? raw.ql[1] : raw.ql[3];
+        const uint32_t ql[8] = {first.x, first.y, first.z, first.w, second.x, second.y, second.z, second.w};
         const uint32_t qh[8] = {raw.qh[0].x, raw.qh[0].y, raw.qh[0].z, raw.qh[0].w, raw.qh[1].x, raw.qh[1].y, raw.qh[1].z, raw.qh[1].w};
         const uint32_t high_shift = 4 * g + 2 * part;
         uint32_t v[16];
@@ -361,13 +397,13 @@ struct DequantQ6K {
         }
     }
     // The same 32 weights in FP32 as the reference decodes them: (d * sc) * (q - 32) (GgufKQuantBlocks.cs:155-177).
+    template <bool PAIRED>
     static __device__ __forceinline__ void expand_f32(const Raw &raw, uint32_t kt, uint32_t part, float (&w)[32])
     {
         const uint32_t g = kt & 1;
         const float d = __half2float(__ushort_as_half((unsigned short)raw.d));
-        const uint32_t ql[8] = {part ? raw.ql[2].x : raw.ql[0].x, part ? raw.ql[2].y : raw.ql[0].y, part ? raw.ql[2].z : raw.ql[0].z,
-                                part ? raw.ql[2].w : raw.ql[0].w, part ? raw.ql[3].x : raw.ql[1].x, part ? raw.ql[3].y : raw.ql[1].y,
-                                part ? raw.ql[3].z : raw.ql[1].z, part ? raw.ql[3].w : raw.ql[1].w};
+        const uint4 first = PAIRED || !part ? raw.ql[0] : raw.ql[2], second = PAIRED || !part ? raw.ql[1] : raw.ql[3];
+        const uint32_t ql[8] = {first.x, first.y, first.z, first.w, second.x, second.y, second.z, second.w};
         const uint32_t qh[8] = {raw.qh[0].x, raw.qh[0].y, raw.qh[0].z, raw.qh[0].w, raw.qh[1].x, raw.qh[1].y, raw.qh[1].z, raw.qh[1].w};
         const uint32_t high_shift = 4 * g + 2 * part;
 #pragma unroll
@@ -394,7 +430,10 @@ struct DequantQ8 {
         const uint8_t *codes, *scales;
     };
     static __device__ __forceinline__ Row row_of(const GemmArgs &a, uint64_t row);
-    static __device__ __forceinline__ void load(const Row &r, uint32_t kt, Raw &raw)
+    // (every thread fetches the whole k tile: the file layout's blocks are only 2-byte aligned, and the planar
+    // layout's two threads of a row share nothing but the scale word)
+    template <bool PAIRED>
+    static __device__ __forceinline__ void load(const Row &r, uint32_t kt, uint32_t, Raw &raw)
     {
         if (PLANAR) {
             const uint8_t *codes = r.codes + (uint64_t)kt * 64;
@@ -415,7 +454,9 @@ struct DequantQ8 {
             raw.codes[3] = load16<false>(block + 52);
         }
     }
+    static __device__ __forceinline__ void share(Raw &, uint32_t) {}
     // part 0: the first block (chunks 0..3), part 1: the second (chunks 4..7)
+    template <bool PAIRED>
     static __device__ __forceinline__ void expand(const Raw &raw, uint32_t, uint32_t part, uint4 (&out)[4])
     {
         const float d = __half2float(__ushort_as_half((unsigned short)(part ? raw.d1 : raw.d0))) * kPrescale;
@@ -436,6 +477,7 @@ struct DequantQ8 {
         }
     }
     // The same 32 weights in FP32: d * code (GgufLegacyBlocks.cs:85-92).
+    template <bool PAIRED>
     static __device__ __forceinline__ void expand_f32(const Raw &raw, uint32_t, uint32_t part, float (&w)[32])
     {
         const float d = __half2float(__ushort_as_half((unsigned short)(part ? raw.d1 : raw.d0)));
@@ -619,8 +661,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
         // half (four of the eight 16-byte chunks) each. The raw blocks of the next k step are fetched before the
         // current ones are expanded, so the L2 latency is off the critical path.
         const uint32_t dq = threadIdx.x - 128;
-        const uint32_t r = dq % kTileRows, part = dq / kTileRows;  // part is 0 when N = 256
-        constexpr uint32_t kParts = 256 / kTileRows;               // threads per row
+        constexpr uint32_t kParts = 256 / kTileRows;  // threads per row: neighbours in a warp
+        constexpr bool kPaired = kParts == 2;
+        const uint32_t r = dq / kParts, part = dq % kParts;  // part is 0 when N = 256
         // fetches in flight (two-part operands expand to FP32 and have no registers to spare: one fetch of two steps)
         constexpr int kAhead = (SPLIT || N == 256) && Dequant::kStepsPerRaw == 2 ? 1 : Dequant::kAhead;
         uint32_t s = 0, round = 0;
@@ -643,7 +686,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                 fetch_row = Dequant::row_of(a, min((uint64_t)(((fetch_item % tiles) % a.row_tiles) * kTileRows + r), a.rows - 1));
                 fetch_new_row = false;
             }
-            Dequant::load(fetch_row, fetch_kt, destination);
+            Dequant::template load<kPaired>(fetch_row, fetch_kt, part, destination);
             fetch_kt += kSpan;
             if (fetch_kt == fetch_end) {
                 fetch_item += gridDim.x;
@@ -667,25 +710,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                 if (fetch0 + d >= fetches) {
                     break;
                 }
-                const typename Dequant::Raw raw = ahead[d];
+                typename Dequant::Raw raw = ahead[d];
                 if (fetched < fetches) {
                     fetch(ahead[d]);
+                }
+                if (kPaired) {
+                    Dequant::share(raw, part);
                 }
 #pragma unroll 1
                 for (uint32_t span = 0; span < kSpan; ++span) {
                     uint4 v[2][4];
                     if (SPLIT) {
                         float w[32];
-                        Dequant::expand_f32(raw, kt, part, w);
+                        Dequant::template expand_f32<kPaired>(raw, kt, part, w);
     #pragma unroll
                         for (int c = 0; c < 4; ++c) {
                             split_chunk(w + 8 * c, v[0][c], v[1][c]);
                         }
                     } else if (kParts == 1) {
-                        Dequant::expand(raw, kt, 0, v[0]);
-                        Dequant::expand(raw, kt, 1, v[1]);
+                        Dequant::template expand<kPaired>(raw, kt, 0, v[0]);
+                        Dequant::template expand<kPaired>(raw, kt, 1, v[1]);
                     } else {
-                        Dequant::expand(raw, kt, part, v[0]);
+                        Dequant::template expand<kPaired>(raw, kt, part, v[0]);
                     }
                     if (round > 0) {
                         mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.fault);
