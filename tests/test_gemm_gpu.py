@@ -145,3 +145,25 @@ def test_products_split_along_k_add_their_shares_in_a_fixed_order(ggml_type, row
     assert not np.array_equal(split, whole), "the full scratch did not change the summation: the split did not run"
     span = whole.max(axis=1, keepdims=True) - whole.min(axis=1, keepdims=True)
     assert np.all(np.abs(split - whole) <= 1e-4 * span)  # (1.3e-5 of the range at K = 18944: FP32 sums of 296 against 5 x 60 steps), f"worst difference {np.max(np.abs(split - whole) / span):.3e} of the output range"
+
+
+def test_split_product_stores_through_odd_strides_and_leaves_gaps_alone():
+    """The CTA that adds the shares stores rows of 4 floats at a time when the address allows it and single floats when it
+    does not (an output stride that is not a multiple of 4, a ragged last row tile): both against the dense result."""
+    import torch
+
+    rows, columns, tokens = 300, 4096, 150
+    lib = sb.library()
+    weights = synth.matrix(sb.Q4_K, rows, columns, seed=81)
+    x = torch.from_numpy(synth.activations(tokens, columns, seed=82)).cuda()
+    full = lib.gemm_scratch_bytes(tokens, columns)
+    work = torch.empty(full, dtype=torch.uint8, device="cuda")
+    with sb.QuantizedMatrix(weights, sb.Q4_K, rows, columns) as matrix:
+        dense = torch.empty((tokens, rows), device="cuda")
+        matrix.gemm_device(x.data_ptr(), tokens, columns, dense.data_ptr(), rows, work.data_ptr(), full)
+        for stride in (rows + 3, rows + 8):
+            strided = torch.full((tokens, stride), 12345.0, device="cuda")
+            matrix.gemm_device(x.data_ptr(), tokens, columns, strided.data_ptr(), stride, work.data_ptr(), full)
+            torch.cuda.synchronize()
+            assert torch.equal(strided[:, :rows], dense) and bool(torch.all(strided[:, rows:] == 12345.0))
+        assert lib.device_faults() == 0
