@@ -717,13 +717,41 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                 if (kPaired) {
                     Dequant::share(raw, part);
                 }
+                if constexpr (kSpan == 2 && kPaired && !SPLIT) {
+                    // Both steps of the fetch are expanded before either is handed over: two independent chains of
+                    // arithmetic for a warp that shares its scheduler with one other dequant warp.
+                    uint4 both[2][4];
+                    Dequant::template expand<true>(raw, kt, part, both[0]);
+                    Dequant::template expand<true>(raw, kt + 1, part, both[1]);
+#pragma unroll
+                    for (uint32_t span = 0; span < 2; ++span) {
+                        if (round > 0) {
+                            mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.fault);
+                        }
+                        uint8_t *tile_b = stages + s * kStageBytes + kTileBOffset;
+#pragma unroll
+                        for (uint32_t c = 0; c < 4; ++c) {
+                            *reinterpret_cast<uint4 *>(tile_b + swizzled(r, 4 * part + c)) = both[span][c];
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) {
+                            mbar_arrive(full0 + 8 * s);
+                        }
+                        if (++s == kStages) {
+                            s = 0;
+                            ++round;
+                        }
+                    }
+                    kt += 2;
+                } else
 #pragma unroll 1
                 for (uint32_t span = 0; span < kSpan; ++span) {
                     uint4 v[2][4];
                     if (SPLIT) {
                         float w[32];
                         Dequant::template expand_f32<kPaired>(raw, kt, part, w);
-    #pragma unroll
+#pragma unroll
                         for (int c = 0; c < 4; ++c) {
                             split_chunk(w + 8 * c, v[0][c], v[1][c]);
                         }
@@ -737,7 +765,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                         mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.fault);
                     }
                     uint8_t *tile_b = stages + s * kStageBytes + kTileBOffset;
-    #pragma unroll
+#pragma unroll
                     for (uint32_t c = 0; c < 4; ++c) {
                         if (SPLIT) {
                             *reinterpret_cast<uint4 *>(tile_b + swizzled(r, 4 * part + c)) = v[0][c];
