@@ -850,27 +850,45 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                 if (last_part) {
                     __threadfence();
                     constexpr uint32_t kShareFloats = TT * kTileTokens * kTileRows;
-                    const uint32_t quads = live * kTileTokens * kTileRows / 4;
-                    for (uint32_t f = threadIdx.x; f < quads; f += 128) {
-                        float4 sum = __ldcg(reinterpret_cast<const float4 *>(a.partials + tile * kShareFloats) + f);
-                        for (uint32_t part = 1; part < a.k_parts; ++part) {
-                            const float4 share = __ldcg(reinterpret_cast<const float4 *>(a.partials + (part * tiles + tile) * kShareFloats) + f);
-                            sum.x += share.x;
-                            sum.y += share.y;
-                            sum.z += share.z;
-                            sum.w += share.w;
+                    constexpr uint32_t kBatch = 8;  // outputs (of 4 floats) a thread adds at a time: their loads are in flight together
+                    const uint32_t quads = live * kTileTokens * kTileRows / 4;  // a multiple of 128 * kBatch
+                    for (uint32_t f0 = threadIdx.x; f0 < quads; f0 += 128 * kBatch) {
+                        float4 sum[kBatch];
+#pragma unroll
+                        for (uint32_t j = 0; j < kBatch; ++j) {
+                            sum[j] = __ldcg(reinterpret_cast<const float4 *>(a.partials + tile * kShareFloats) + f0 + 128 * j);
                         }
-                        const uint32_t column = (4 * f) % kTileRows;
-                        const uint64_t token = tt0 * kTileTokens + (4 * f) / kTileRows;
-                        if (token < a.tokens) {
-                            float *out = a.y + token * a.out_stride + row0 + column;
-                            if (row0 + column + 4 <= a.rows && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
-                                *reinterpret_cast<float4 *>(out) = sum;
-                            } else {
-                                const float values[4] = {sum.x, sum.y, sum.z, sum.w};
-                                for (int j = 0; j < 4; ++j) {
-                                    if (row0 + column + j < a.rows) {
-                                        out[j] = values[j];
+#pragma unroll 2
+                        for (uint32_t part = 1; part < a.k_parts; ++part) {
+                            const float4 *share = reinterpret_cast<const float4 *>(a.partials + (part * tiles + tile) * kShareFloats);
+                            float4 v[kBatch];
+#pragma unroll
+                            for (uint32_t j = 0; j < kBatch; ++j) {
+                                v[j] = __ldcg(share + f0 + 128 * j);
+                            }
+#pragma unroll
+                            for (uint32_t j = 0; j < kBatch; ++j) {
+                                sum[j].x += v[j].x;
+                                sum[j].y += v[j].y;
+                                sum[j].z += v[j].z;
+                                sum[j].w += v[j].w;
+                            }
+                        }
+#pragma unroll
+                        for (uint32_t j = 0; j < kBatch; ++j) {
+                            const uint32_t f = f0 + 128 * j;
+                            const uint32_t column = (4 * f) % kTileRows;
+                            const uint64_t token = tt0 * kTileTokens + (4 * f) / kTileRows;
+                            if (token < a.tokens) {
+                                float *out = a.y + token * a.out_stride + row0 + column;
+                                if (row0 + column + 4 <= a.rows && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+                                    *reinterpret_cast<float4 *>(out) = sum[j];
+                                } else {
+                                    const float values[4] = {sum[j].x, sum[j].y, sum[j].z, sum[j].w};
+                                    for (int e = 0; e < 4; ++e) {
+                                        if (row0 + column + e < a.rows) {
+                                            out[e] = values[e];
+                                        }
                                     }
                                 }
                             }
