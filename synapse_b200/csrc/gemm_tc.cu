@@ -269,6 +269,44 @@ struct DequantQ4K {
         raw.q0 = part ? other : mine;
         raw.q1 = part ? mine : other;
     }
+    // 128-row tiles, fp16 operands: a fetch brings a whole block (four k steps) -- the header and this thread's half of each
+    // of the four 32-byte pieces. One burst of 144 contiguous bytes per row and four steps instead of a 48-byte visit per
+    // step: with some 19,000 rows being walked at once, every visit finds its DRAM page closed again.
+    static constexpr bool kHasWide = true;
+    struct WideRaw {
+        uint4 header, q[4];
+    };
+    struct WideFull {
+        uint4 header, q[8];  // q[2c], q[2c + 1]: the 32 bytes of k step c
+    };
+    static __device__ __forceinline__ void load_wide(const Row &r, uint32_t kt, uint32_t part, WideRaw &raw)
+    {
+        const uint8_t *block = r.base + (uint64_t)(kt >> 2) * 144;
+        raw.header = __ldg(reinterpret_cast<const uint4 *>(block));
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            raw.q[c] = __ldg(reinterpret_cast<const uint4 *>(block + 16 + c * 32 + 16 * part));
+        }
+    }
+    static __device__ __forceinline__ void complete_wide(const WideRaw &raw, uint32_t part, WideFull &full)
+    {
+        full.header = raw.header;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint4 other = from_partner(raw.q[c]);
+            full.q[2 * c] = part ? other : raw.q[c];
+            full.q[2 * c + 1] = part ? raw.q[c] : other;
+        }
+    }
+    // k step `step` (0..3) of the block
+    static __device__ __forceinline__ void expand_wide(const WideFull &full, int step, uint32_t half, uint4 (&out)[4])
+    {
+        Raw one;
+        one.header = full.header;
+        one.q0 = full.q[2 * step];
+        one.q1 = full.q[2 * step + 1];
+        expand<true>(one, (uint32_t)step, half, out);
+    }
     // Chunks 4*half .. 4*half+3 of the k tile: half 0 = the low nibbles (sub-block 2c), half 1 = the high nibbles
     // (sub-block 2c+1), where c = kt%4.
     template <bool PAIRED>
@@ -322,6 +360,7 @@ struct DequantQ6K {
     // The two k tiles of a half block (nibble g = 0, 1) are cut from the same 64 + 32 bytes: one fetch serves both steps,
     // so two fetches in flight are four k steps of lookahead.
     static constexpr int kStepsPerRaw = 2;
+    static constexpr bool kHasWide = false;
     struct Raw {
         uint4 ql[4], qh[2];
         uint2 scales;  // the four int8 scales of k tile g = 0, then those of g = 1
@@ -422,6 +461,7 @@ template <bool PLANAR>
 struct DequantQ8 {
     static constexpr int kAhead = 3;
     static constexpr int kStepsPerRaw = 1;
+    static constexpr bool kHasWide = false;
     struct Raw {
         uint4 codes[4];
         uint32_t d0, d1;  // fp16 bits of the two block scales
@@ -664,9 +704,74 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
         constexpr uint32_t kParts = 256 / kTileRows;  // threads per row: neighbours in a warp
         constexpr bool kPaired = kParts == 2;
         const uint32_t r = dq / kParts, part = dq % kParts;  // part is 0 when N = 256
+        uint32_t s = 0, round = 0;
+        // Hands one k step's share of the weight tile (128-row tiles, fp16 operands: chunks 4 * part .. + 3 of row r) to the MMA.
+        auto hand_over = [&](const uint4 (&chunks)[4]) {
+            if (round > 0) {
+                mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.fault);
+            }
+            uint8_t *tile_b = stages + s * kStageBytes + kTileBOffset;
+#pragma unroll
+            for (uint32_t c = 0; c < 4; ++c) {
+                *reinterpret_cast<uint4 *>(tile_b + swizzled(r, 4 * part + c)) = chunks[c];
+            }
+            // make the generic-proxy stores visible to the tensor core's (async proxy) reads
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(full0 + 8 * s);
+            }
+            if (++s == kStages) {
+                s = 0;
+                ++round;
+            }
+        };
+        if constexpr (Dequant::kHasWide && kPaired && !SPLIT) {
+            // ---- whole blocks per fetch (four k steps), one fetch in flight: issued when the block before it is taken up
+            uint32_t fetches = 0;
+            for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+                fetches += (end_step(item) - first_step(item)) / 4;  // (first step and step count of an item are multiples of 4)
+            }
+            typename Dequant::WideRaw next;
+            uint32_t fetch_item = blockIdx.x, fetch_kt = first_step(fetch_item), fetch_end = end_step(fetch_item);
+            bool fetch_new_row = true;
+            typename Dequant::Row fetch_row{};
+            auto fetch = [&]() {
+                if (fetch_new_row) {
+                    fetch_row = Dequant::row_of(a, min((uint64_t)(((fetch_item % tiles) % a.row_tiles) * kTileRows + r), a.rows - 1));
+                    fetch_new_row = false;
+                }
+                Dequant::load_wide(fetch_row, fetch_kt, part, next);
+                fetch_kt += 4;
+                if (fetch_kt == fetch_end) {
+                    fetch_item += gridDim.x;
+                    fetch_kt = first_step(fetch_item);
+                    fetch_end = end_step(fetch_item);
+                    fetch_new_row = true;
+                }
+            };
+            if (fetches > 0) {
+                fetch();
+            }
+            for (uint32_t n = 0; n < fetches; ++n) {
+                const typename Dequant::WideRaw taken = next;
+                if (n + 1 < fetches) {
+                    fetch();
+                }
+                typename Dequant::WideFull block;
+                Dequant::complete_wide(taken, part, block);
+#pragma unroll
+                for (int step = 0; step < 4; step += 2) {
+                    uint4 both[2][4];  // two independent chains of arithmetic before either is handed over
+                    Dequant::expand_wide(block, step, part, both[0]);
+                    Dequant::expand_wide(block, step + 1, part, both[1]);
+                    hand_over(both[0]);
+                    hand_over(both[1]);
+                }
+            }
+        } else {
         // fetches in flight (two-part operands expand to FP32 and have no registers to spare: one fetch of two steps)
         constexpr int kAhead = (SPLIT || N == 256) && Dequant::kStepsPerRaw == 2 ? 1 : Dequant::kAhead;
-        uint32_t s = 0, round = 0;
         constexpr uint32_t kSpan = Dequant::kStepsPerRaw;  // k steps one fetch serves (an item's first step and its step count are multiples of it)
         uint32_t fetches = 0;  // over all of this CTA's items
         for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
@@ -723,26 +828,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                     uint4 both[2][4];
                     Dequant::template expand<true>(raw, kt, part, both[0]);
                     Dequant::template expand<true>(raw, kt + 1, part, both[1]);
-#pragma unroll
-                    for (uint32_t span = 0; span < 2; ++span) {
-                        if (round > 0) {
-                            mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.fault);
-                        }
-                        uint8_t *tile_b = stages + s * kStageBytes + kTileBOffset;
-#pragma unroll
-                        for (uint32_t c = 0; c < 4; ++c) {
-                            *reinterpret_cast<uint4 *>(tile_b + swizzled(r, 4 * part + c)) = both[span][c];
-                        }
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0) {
-                            mbar_arrive(full0 + 8 * s);
-                        }
-                        if (++s == kStages) {
-                            s = 0;
-                            ++round;
-                        }
-                    }
+                    hand_over(both[0]);
+                    hand_over(both[1]);
                     kt += 2;
                 } else
 #pragma unroll 1
@@ -795,6 +882,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                     kt_end = end_step(item);
                 }
             }
+        }
         }
     } else {
         // ---- epilogue warps: warp q owns accumulator lanes (tokens) 32q .. 32q+31 ----------------------
