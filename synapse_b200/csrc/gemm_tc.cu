@@ -360,7 +360,7 @@ struct DequantQ6K {
     // The two k tiles of a half block (nibble g = 0, 1) are cut from the same 64 + 32 bytes: one fetch serves both steps,
     // so two fetches in flight are four k steps of lookahead.
     static constexpr int kStepsPerRaw = 2;
-    static constexpr bool kHasWide = false;
+    static constexpr bool kHasWide = true;
     struct Raw {
         uint4 ql[4], qh[2];
         uint2 scales;  // the four int8 scales of k tile g = 0, then those of g = 1
@@ -408,6 +408,69 @@ struct DequantQ6K {
         const uint4 mine = raw.qh[0], other = from_partner(raw.qh[0]);
         raw.qh[0] = part ? other : mine;
         raw.qh[1] = part ? mine : other;
+    }
+    // 128-row tiles, fp16 operands: a fetch brings the thread's share of a whole block (four k steps): of each half its own
+    // 32 bytes of low nibbles and one 16-byte piece of the high bits, the sixteen scales and d.
+    struct WideRaw {
+        uint4 ql[4], qh[2], scales;  // ql[2h], ql[2h + 1] and qh[h]: half h
+        uint32_t d;
+    };
+    struct WideFull {
+        uint4 ql[4], qh[4], scales;  // qh[2h], qh[2h + 1]: the 32 bytes of half h
+        uint32_t d;
+    };
+    static __device__ __forceinline__ void load_wide(const Row &r, uint32_t kt, uint32_t part, WideRaw &raw)
+    {
+        const uint32_t sb = kt >> 2;
+        const uint8_t *ql, *qh, *sc, *d;
+        if (PLANAR) {
+            ql = r.ql + (uint64_t)sb * 128;
+            qh = r.qh + (uint64_t)sb * 64;
+            sc = r.sc + (uint64_t)sb * 16;
+            d = r.d + (uint64_t)sb * 2;
+        } else {
+            const uint8_t *block = r.ql + (uint64_t)sb * 210;
+            ql = block;
+            qh = block + 128;
+            sc = block + 192;
+            d = block + 208;
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            raw.ql[2 * h] = load16<PLANAR>(ql + 64 * h + 32 * part);
+            raw.ql[2 * h + 1] = load16<PLANAR>(ql + 64 * h + 32 * part + 16);
+            raw.qh[h] = load16<PLANAR>(qh + 32 * h + 16 * part);
+        }
+        raw.scales = load16<PLANAR>(sc);
+        raw.d = load_u16(d);
+    }
+    static __device__ __forceinline__ void complete_wide(const WideRaw &raw, uint32_t part, WideFull &full)
+    {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            full.ql[i] = raw.ql[i];
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 other = from_partner(raw.qh[h]);
+            full.qh[2 * h] = part ? other : raw.qh[h];
+            full.qh[2 * h + 1] = part ? raw.qh[h] : other;
+        }
+        full.scales = raw.scales;
+        full.d = raw.d;
+    }
+    // k step `step` (0..3) of the block: half step / 2, nibble step % 2
+    static __device__ __forceinline__ void expand_wide(const WideFull &full, int step, uint32_t part, uint4 (&out)[4])
+    {
+        const int h = step >> 1;
+        Raw one;
+        one.ql[0] = full.ql[2 * h];
+        one.ql[1] = full.ql[2 * h + 1];
+        one.qh[0] = full.qh[2 * h];
+        one.qh[1] = full.qh[2 * h + 1];
+        one.scales = h ? make_uint2(full.scales.z, full.scales.w) : make_uint2(full.scales.x, full.scales.y);
+        one.d = full.d;
+        expand<true>(one, (uint32_t)step, part, out);
     }
     // part 0: tile values 0..31 (chunks 0..3), part 1: values 32..63 (chunks 4..7)
     template <bool PAIRED>
