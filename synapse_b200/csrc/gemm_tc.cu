@@ -654,11 +654,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
     uint8_t *stages = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(shared_raw) + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) uint64_t barriers[2 * kMaxStages + 4];  // full[s], empty[s], acc_full[2], acc_empty[2]
     __shared__ uint32_t tmem_slot;
-    __shared__ uint32_t last_part;
+    __shared__ int last_tile;  // the tile whose shares this CTA adds at its end (it was the last to arrive), or -1
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(&barriers[0]), empty0 = smem_u32(&barriers[kMaxStages]);
     const uint32_t acc_full0 = smem_u32(&barriers[2 * kMaxStages]), acc_empty0 = smem_u32(&barriers[2 * kMaxStages + 2]);
     if (threadIdx.x == 0) {
+        last_tile = -1;
         for (uint32_t s = 0; s < kStages; ++s) {
             mbar_init(full0 + 8 * s, 1 + kDequantWarps);  // the loader's expect_tx arrival + one arrival per dequant warp
             mbar_init(empty0 + 8 * s, 1);     // tcgen05.commit
@@ -990,63 +991,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
                 mbar_arrive(acc_empty0 + 8 * acc);
             }
             if (!whole) {
-                // The tile's parts meet through a counter: whoever arrives last adds all shares, part 0 first, and
-                // stores the tile. Nobody waits for anybody.
+                // The tile's parts meet through a counter: the CTA that arrives last adds all shares (below, with all of its
+                // warps) and stores the tile. Nobody waits for anybody. (A split product gives every CTA exactly one item.)
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (threadIdx.x == 0) {
-                    last_part = atomicAdd(a.arrivals + tile, 1u) + 1 == a.k_parts ? 1u : 0u;
+                if (threadIdx.x == 0 && atomicAdd(a.arrivals + tile, 1u) + 1 == a.k_parts) {
+                    last_tile = (int)tile;
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (last_part) {
-                    __threadfence();
-                    constexpr uint32_t kShareFloats = TT * kTileTokens * kTileRows;
-                    constexpr uint32_t kBatch = 8;  // outputs (of 4 floats) a thread adds at a time: their loads are in flight together
-                    const uint32_t quads = live * kTileTokens * kTileRows / 4;  // a multiple of 128 * kBatch
-                    for (uint32_t f0 = threadIdx.x; f0 < quads; f0 += 128 * kBatch) {
-                        float4 sum[kBatch];
-#pragma unroll
-                        for (uint32_t j = 0; j < kBatch; ++j) {
-                            sum[j] = __ldcg(reinterpret_cast<const float4 *>(a.partials + tile * kShareFloats) + f0 + 128 * j);
-                        }
-#pragma unroll 2
-                        for (uint32_t part = 1; part < a.k_parts; ++part) {
-                            const float4 *share = reinterpret_cast<const float4 *>(a.partials + (part * tiles + tile) * kShareFloats);
-                            float4 v[kBatch];
-#pragma unroll
-                            for (uint32_t j = 0; j < kBatch; ++j) {
-                                v[j] = __ldcg(share + f0 + 128 * j);
-                            }
-#pragma unroll
-                            for (uint32_t j = 0; j < kBatch; ++j) {
-                                sum[j].x += v[j].x;
-                                sum[j].y += v[j].y;
-                                sum[j].z += v[j].z;
-                                sum[j].w += v[j].w;
-                            }
-                        }
-#pragma unroll
-                        for (uint32_t j = 0; j < kBatch; ++j) {
-                            const uint32_t f = f0 + 128 * j;
-                            const uint32_t column = (4 * f) % kTileRows;
-                            const uint64_t token = tt0 * kTileTokens + (4 * f) / kTileRows;
-                            if (token < a.tokens) {
-                                float *out = a.y + token * a.out_stride + row0 + column;
-                                if (row0 + column + 4 <= a.rows && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
-                                    *reinterpret_cast<float4 *>(out) = sum[j];
-                                } else {
-                                    const float values[4] = {sum[j].x, sum[j].y, sum[j].z, sum[j].w};
-                                    for (int e = 0; e < 4; ++e) {
-                                        if (row0 + column + e < a.rows) {
-                                            out[e] = values[e];
-                                        }
-                                    }
-                                }
-                            }
-                        }
-                    }
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");  // (last_part is written again for the CTA's next item)
             }
         }
     }
@@ -1055,6 +1006,61 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
     tc_fence_after();
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    }
+    if (a.k_parts > 1 && last_tile >= 0) {
+        // The shares of the tile, part 0 first. Every thread of the CTA takes outputs (of 4 floats) eight at a time and two
+        // shares per round of loads: what bounds this is the number of L2 round trips in a row, not the bytes.
+        __threadfence();
+        const uint32_t tile = (uint32_t)last_tile;
+        const uint64_t row0 = (uint64_t)(tile % a.row_tiles) * kTileRows;
+        const uint64_t tt0 = (uint64_t)(tile / a.row_tiles) * TT;
+        const uint32_t live = min((uint32_t)TT, a.token_tiles - (uint32_t)tt0);
+        constexpr uint32_t kShareFloats = TT * kTileTokens * kTileRows;
+        constexpr uint32_t kBatch = 8;
+        const uint32_t quads = live * kTileTokens * kTileRows / 4;
+        for (uint32_t f0 = threadIdx.x; f0 < quads; f0 += kGemmThreads * kBatch) {
+            float4 sum[kBatch];
+#pragma unroll
+            for (uint32_t j = 0; j < kBatch; ++j) {
+                const uint32_t f = min(f0 + kGemmThreads * j, quads - 1);
+                sum[j] = __ldcg(reinterpret_cast<const float4 *>(a.partials + tile * kShareFloats) + f);
+            }
+#pragma unroll 2
+            for (uint32_t part = 1; part < a.k_parts; ++part) {
+                const float4 *share = reinterpret_cast<const float4 *>(a.partials + (part * tiles + tile) * kShareFloats);
+                float4 v[kBatch];
+#pragma unroll
+                for (uint32_t j = 0; j < kBatch; ++j) {
+                    v[j] = __ldcg(share + min(f0 + kGemmThreads * j, quads - 1));
+                }
+#pragma unroll
+                for (uint32_t j = 0; j < kBatch; ++j) {
+                    sum[j].x += v[j].x;
+                    sum[j].y += v[j].y;
+                    sum[j].z += v[j].z;
+                    sum[j].w += v[j].w;
+                }
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < kBatch; ++j) {
+                const uint32_t f = f0 + kGemmThreads * j;
+                const uint32_t column = (4 * f) % kTileRows;
+                const uint64_t token = tt0 * kTileTokens + (4 * f) / kTileRows;
+                if (f < quads && token < a.tokens) {
+                    float *out = a.y + token * a.out_stride + row0 + column;
+                    if (row0 + column + 4 <= a.rows && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+                        *reinterpret_cast<float4 *>(out) = sum[j];
+                    } else {
+                        const float values[4] = {sum[j].x, sum[j].y, sum[j].z, sum[j].w};
+                        for (int e = 0; e < 4; ++e) {
+                            if (row0 + column + e < a.rows) {
+                                out[e] = values[e];
+                            }
+                        }
+                    }
+                }
+            }
+        }
     }
 }
 
