@@ -1155,8 +1155,11 @@ int32_t launch_gemm(const syn_b200_matrix *m, const float *x, uint64_t tokens, u
     const uint64_t sms = (uint64_t)sm_count(m->device);
     const int tt = a.token_tiles >= 2 && !split ? 2 : 1;
     const uint64_t token_groups = (a.token_tiles + tt - 1) / tt;
-    const uint64_t tiles256 = ((m->rows + 255) / 256) * token_groups;
-    const int n = tiles256 >= sms && !split ? 256 : 128;
+    // 256-row tiles when they give every SM work, and also when they fill fewer SMs but in fewer waves: a k step of a
+    // 256-row tile takes about 1.7 times that of a 128-row tile (112 tiles of 256 rows in one wave beat 224 of 128 in two).
+    const uint64_t tiles256 = ((m->rows + 255) / 256) * token_groups, tiles128 = ((m->rows + 127) / 128) * token_groups;
+    const uint64_t waves256 = (tiles256 + sms - 1) / sms, waves128 = (tiles128 + sms - 1) / sms;
+    const int n = !split && (tiles256 >= sms || 17 * waves256 < 10 * waves128) ? 256 : 128;
     a.row_tiles = (uint32_t)((m->rows + n - 1) / n);
     a.x_tiles = static_cast<const uint8_t *>(scratch);
     a.x_tiles_low = split ? a.x_tiles + need / 2 : nullptr;
