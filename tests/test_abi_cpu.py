@@ -126,3 +126,15 @@ def test_without_a_b200_calls_fail_loudly_not_silently(lib):
         sb.QuantizedMatrix(np.zeros(34 * 4, np.uint8), sb.Q8_0, 4, 32)
     with pytest.raises(sb.BackendUnavailableError):
         sb.quantize_row(np.zeros(32, np.float32))
+
+
+def test_scratch_sizes_are_plain_arithmetic(lib):
+    """The scratch queries need no device: the activation scratch of the quantised products (codes, scales, sums per 16, each
+    rounded up to 256 bytes) and the tensor-core product's scratch (two sets of 16-bit activation tiles of 128 tokens x 64
+    values, plus the fixed room in which small products split along k)."""
+    assert lib.activation_scratch_bytes(1, 3584) == 4608  # codes at 0 (3584), 112 scales at 3584 (448), 224 sums at 4096 (448), end rounded up
+    tiles = lambda tokens, columns: 2 * (-(-tokens // 128) * (columns // 64) * 16384)
+    split_room = lib.gemm_scratch_bytes(1, 64) - tiles(1, 64)
+    assert split_room == 160 * 2 * 128 * 128 * 4 + 4 * 80
+    for tokens, columns in ((128, 3584), (129, 3584), (4096, 18944)):
+        assert lib.gemm_scratch_bytes(tokens, columns) == tiles(tokens, columns) + split_room
