@@ -762,8 +762,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(GemmArgs a)
         }
     } else if (warp >= 4) {
         // ---- dequant warps: 256 threads over the tile's N rows; with N = 128 two threads share a row, one nibble
-        // half (four of the eight 16-byte chunks) each. The raw blocks of the next k step are fetched before the
-        // current ones are expanded, so the L2 latency is off the critical path.
+        // half (four of the eight 16-byte chunks) each. Raw blocks are fetched ahead of their expansion, so the memory
+        // latency is off the critical path. Two loops: K-quants with 128-row tiles and fp16 operands fetch a whole
+        // block (four k steps) at a time; every other variant fetches one or two k steps at a time, one to three
+        // fetches ahead.
         const uint32_t dq = threadIdx.x - 128;
         constexpr uint32_t kParts = 256 / kTileRows;  // threads per row: neighbours in a warp
         constexpr bool kPaired = kParts == 2;
